@@ -1,0 +1,401 @@
+"""Benchmark of the KMeans hot path: Lloyd iterations/s on the n=10M, d=128, k=1024 fp32
+configuration (synthetic blobs), on N GPUs of one box.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # CPU restatement of the reference, host cores
+
+A step is one full Lloyd iteration over all samples: fused E-step + centroid accumulation,
+merge of accumulator copies, all-reduce (N > 1), finalize, 32-byte status read.  Rows are
+split into contiguous shards over the ranks (total work fixed: strong scaling).  Rank 0
+prints one JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (n, d, k, dtype, cluster std, offset std, seed, description)
+    "c3": dict(n=10_000_000, d=128, k=1024, dtype="f32", noise=1.0, spread=2.0, seed=2,
+               desc="KMeans fp32 n=10M d=128 k=1024, x~N(0,1)+offset[cluster], offsets~N(0,4), "
+                    "random-row init seed 2, tol=0"),
+    "c2": dict(n=5_000_000, d=14, k=256, dtype="f32", noise=1.5, spread=None, seed=1,
+               desc="KMeans fp32 n=5M d=14 k=256, blobs centres~U[-10,10] std 1.5, random-row "
+                    "init seed 1, tol=0"),
+    "c4": dict(n=2_000_000, d=32, k=64, dtype="f64", noise=None, spread=None, seed=3,
+               desc="KMeans fp64 n=2M d=32 k=64, U[0,1] data, random-row init seed 3, tol=0"),
+    "c1": dict(n=50_000, d=14, k=127, dtype="f32", noise=1.0, spread=None, seed=0,
+               desc="KMeans fp32 n=50k d=14 k=127 blobs"),
+}
+CHUNK = 1 << 20
+
+
+def algorithmic_flops(n, d, k):
+    return 2.0 * n * d * k
+
+
+def algorithmic_bytes(n, d, k, s):
+    # X once, labels read + written, centroids read + written, counts
+    return n * d * s + 2 * 4 * n + 2 * k * d * s + k * s
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="MEASURED_PEAKS.json")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- data
+def cluster_offsets(cfg, torch, device):
+    g = torch.Generator(device="cpu").manual_seed(cfg["seed"] * 7919 + 1)
+    d, k = cfg["d"], cfg["k"]
+    if cfg["spread"] is not None:
+        off = torch.randn((k, d), generator=g) * cfg["spread"]
+    else:
+        off = torch.rand((k, d), generator=g) * 20.0 - 10.0
+    return off.to(device)
+
+
+def generate_rows(cfg, start, stop, torch, device, dtype):
+    """Rows [start, stop) of the synthetic data set; any rank can materialise any block
+    because every CHUNK of rows has its own seed."""
+    d, k = cfg["d"], cfg["k"]
+    out = torch.empty((stop - start, d), dtype=dtype, device=device)
+    offsets = cluster_offsets(cfg, torch, device).to(dtype)
+    c0 = start // CHUNK
+    pos = 0
+    while start + pos < stop:
+        chunk = (start + pos) // CHUNK
+        lo, hi = chunk * CHUNK, min((chunk + 1) * CHUNK, cfg["n"])
+        g = torch.Generator(device=device).manual_seed(cfg["seed"] * 1_000_003 + chunk)
+        if cfg["noise"] is None:
+            block = torch.rand((hi - lo, d), generator=g, device=device, dtype=dtype)
+        else:
+            ids = torch.randint(0, k, (hi - lo,), generator=g, device=device)
+            block = torch.randn((hi - lo, d), generator=g, device=device, dtype=dtype) * cfg["noise"]
+            block += offsets[ids]
+        a, b = max(start, lo) - lo, min(stop, hi) - lo
+        out[pos:pos + (b - a)] = block[a:b]
+        pos += b - a
+        del block
+    return out
+
+
+def initial_centres(cfg, X_shard, start, stop, torch, dist_mod):
+    """Random distinct rows (numpy RandomState(seed).choice, the engine's "random" init);
+    each rank contributes the rows it owns, one all-reduce assembles them."""
+    idx = np.random.RandomState(cfg["seed"]).choice(cfg["n"], size=cfg["k"], replace=False)
+    C = torch.zeros((cfg["k"], cfg["d"]), dtype=X_shard.dtype, device=X_shard.device)
+    mine = np.nonzero((idx >= start) & (idx < stop))[0]
+    if mine.size:
+        C[torch.as_tensor(mine, device=C.device)] = X_shard[torch.as_tensor(idx[mine] - start,
+                                                                           device=C.device)]
+    dist_mod.all_reduce_sum_(C)
+    return C
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fh = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = fh.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)], stdout=fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------- CPU baseline
+def cpu_reference_sample(cfg, sample_rows, iters):
+    """Times the C restatement of the reference's Lloyd iteration (all host threads) on a
+    row sample of the workload and scales linearly in n to whole-job iterations/s."""
+    from oracle import c_oracle
+
+    rng = np.random.default_rng(cfg["seed"])
+    d, k = cfg["d"], cfg["k"]
+    dt = np.float32 if cfg["dtype"] == "f32" else np.float64
+    if cfg["noise"] is None:
+        X = rng.random((sample_rows, d)).astype(dt)
+    else:
+        spread = cfg["spread"]
+        off = (rng.standard_normal((k, d)) * spread if spread is not None
+               else rng.uniform(-10, 10, (k, d)))
+        X = (off[rng.integers(0, k, sample_rows)] + cfg["noise"] * rng.standard_normal((sample_rows, d))).astype(dt)
+    C = X[rng.choice(sample_rows, size=k, replace=False)].copy()
+    c_oracle.lloyd_iteration(X, None, C)  # warm-up
+    times, threads = [], 1
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        _, sums, counts, threads = c_oracle.lloyd_iteration(X, None, C)
+        times.append(time.perf_counter() - t0)
+        nz = counts > 0
+        C[nz] = sums[nz] / counts[nz, None]
+    per_iter_full = float(np.mean(times)) * (cfg["n"] / sample_rows)
+    return dict(value=1.0 / per_iter_full, unit="iterations/s", cores=int(threads), kind="port",
+                sample=f"{sample_rows} rows of the same distribution, {iters} iterations of the C "
+                       f"restatement, time scaled by n/{sample_rows}"), times
+
+
+def run_reference_arm(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_rows = max(cfg["k"] * 4, min(cfg["n"], args.cpu_sample_rows))
+    for _ in range(max(args.warmup, 0)):
+        cpu_reference_sample(cfg, sample_rows, 1)
+    base, times = cpu_reference_sample(cfg, sample_rows, max(args.steps, 1))
+    ms = float(np.mean(times)) * (cfg["n"] / sample_rows) * 1e3
+    line = {"impl": "reference", "metric": "Lloyd iterations/s", "value": base["value"],
+            "unit": "iterations/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": cfg["dtype"], "data": "synthetic",
+            "config": {"workload": cfg["desc"], "n": cfg["n"], "d": cfg["d"], "k": cfg["k"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "iterations/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args, cfg):
+    import torch
+    import torch.distributed as tdist
+
+    from sklearn_numba_dpex_b200 import dist as kdist
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState, lloyd
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        tdist.init_process_group("nccl", device_id=device)
+        kdist.enable()
+    dtype = torch.float32 if cfg["dtype"] == "f32" else torch.float64
+    esize = 4 if cfg["dtype"] == "f32" else 8
+    n, d, k = cfg["n"], cfg["d"], cfg["k"]
+    start, stop = kdist.shard_bounds(n, rank, world)
+    X = generate_rows(cfg, start, stop, torch, device, dtype)
+    C0 = initial_centres(cfg, X, start, stop, torch, kdist)
+    state = LloydState(X, None, C0, args.algo)
+    algo_name = {0: "auto", 1: "cuda_core", 2: "tf32x3"}[state.algo]
+
+    def barrier():
+        if world > 1:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        state.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = state.kernel_launches
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(args.steps)]
+    orig_launch = state.launch_step
+
+    step_idx = {"i": 0}
+    from sklearn_numba_dpex_b200._cabi import check, lib, ptr, stream_ptr
+
+    def timed_launch_step():
+        # same sequence as LloydState.launch_step with events around the fused kernel
+        dev = state.X.device
+        a, b = kev[step_idx["i"]]
+        a.record()
+        check(lib.kmb_lloyd_step(state.dtype, state.algo, ptr(state.X), ptr(state.w), ptr(state.C),
+                                 ptr(state.h), ptr(state.labels) if state.have_prev else None,
+                                 ptr(state.labels_new), ptr(state.acc), state.n_copies, state.n,
+                                 state.d, state.k, ptr(state.ws), state.ws_bytes, stream_ptr(dev)))
+        b.record()
+        state.kernel_launches += 1
+        if state.n_copies > 1:
+            check(lib.kmb_lloyd_merge_copies(state.dtype, ptr(state.acc), state.n_copies,
+                                             state.acc_len, ptr(state.packed), stream_ptr(dev)))
+            state.kernel_launches += 1
+        kdist.all_reduce_sum_(state.packed)
+        state._finalize()
+        step_idx["i"] += 1
+
+    state.launch_step = timed_launch_step
+    ev0.record()
+    for _ in range(args.steps):
+        state.step()
+    ev1.record()
+    barrier()
+    state.launch_step = orig_launch
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = ev0.elapsed_time(ev1)
+    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
+    launches = state.kernel_launches - launches0
+    t = torch.tensor([elapsed_ms, kernel_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+    elapsed_ms, kernel_ms = float(t[0]), float(t[1])
+    ms_per_step = elapsed_ms / args.steps
+    value = 1e3 / ms_per_step
+
+    # ---- end to end through the driver API, host buffers in, host results out
+    e2e = None
+    if not args.skip_e2e:
+        Xh = torch.empty(X.shape, dtype=dtype).pin_memory()
+        Xh.copy_(X)
+        Ch = C0.cpu().pin_memory()
+        wh = torch.ones(X.shape[0], dtype=dtype).pin_memory()
+        del state
+        del X
+        torch.cuda.empty_cache()
+        e2e_iters = args.steps
+        barrier()
+        t0 = time.perf_counter()
+        Xd = Xh.to(device, non_blocking=True)
+        wd = wh.to(device, non_blocking=True)
+        Cd = Ch.to(device, non_blocking=True)
+        labels, inertia, C_t, n_iter = lloyd(Xd.T, wd, Cd.T, True, e2e_iters, False, 0.0,
+                                             algo=args.algo)
+        labels_h = labels.cpu()
+        centres_h = C_t.T.contiguous().cpu()
+        torch.cuda.synchronize()
+        dt_e2e = time.perf_counter() - t0
+        t = torch.tensor([dt_e2e], dtype=torch.float64, device=device)
+        if world > 1:
+            tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        dt_e2e = float(t[0])
+        assert n_iter == e2e_iters, (n_iter, e2e_iters)
+        h2d = (Xh.numel() + wh.numel() + Ch.numel()) * esize * world
+        d2h = labels_h.numel() * 4 * world + centres_h.numel() * esize + esize
+        e2e = {"value": e2e_iters / dt_e2e, "unit": "iterations/s",
+               "h2d_bytes_per_step": int(h2d // e2e_iters), "d2h_bytes_per_step": int(d2h // e2e_iters),
+               "what": f"one lloyd() call of {e2e_iters} iterations + final assignment and inertia, "
+                       "X/weights/centres from pinned host memory, labels/centres/inertia back to host"}
+
+    if rank == 0:
+        peaks = load_peaks()
+        n_local = stop - start
+        flops = algorithmic_flops(n_local, d, k)
+        abytes = algorithmic_bytes(n_local, d, k, esize)
+        tf_achieved = flops / (kernel_ms * 1e-3) / 1e12
+        gb_achieved = abytes / (kernel_ms * 1e-3) / 1e9
+        if algo_name == "tf32x3":
+            # TF32 issues at half the bf16 rate and each product pair costs three MMAs
+            peak = peaks["bf16_tflops_sustained"] / 6.0
+            roofline = {"bound": "tensor", "achieved": tf_achieved, "peak": peak, "unit": "TFLOP/s",
+                        "frac": tf_achieved / peak, "traffic": None,
+                        "peak_source": f"{peaks['source']} bf16_tflops_sustained / 6 (TF32 = half "
+                                       "the bf16 rate, 3 MMAs per product: 3xTF32)",
+                        "hbm_frac": gb_achieved / peaks["hbm_gbs"]}
+        else:
+            roofline = {"bound": "hbm", "achieved": gb_achieved, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": gb_achieved / peaks["hbm_gbs"], "traffic": None,
+                        "peak_source": peaks["source"] + " hbm_gbs",
+                        "fp32_tflops_achieved": tf_achieved}
+        roofline["kernel_ms"] = kernel_ms
+        line = {"metric": "Lloyd iterations/s", "value": value, "unit": "iterations/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+                "config": {"workload": cfg["desc"], "n": n, "d": d, "k": k, "algo": algo_name,
+                           "rows_per_gpu": n_local,
+                           "l2": "inputs larger than L2: every step streams this rank's X shard "
+                                 f"({n_local * d * esize / 1e9:.2f} GB)"},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline}
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.skip_cpu:
+            line["cpu_baseline"], _ = cpu_reference_sample(cfg, min(n, args.cpu_sample_rows), 3)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        tdist.barrier()
+        tdist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
+    ap.add_argument("--n", type=int, default=None, help="override the number of samples")
+    ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
+    ap.add_argument("--cpu-sample-rows", type=int, default=200_000)
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    if args.n:
+        cfg["n"] = args.n
+        cfg["desc"] += f" [n overridden to {args.n}]"
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+    else:
+        run_gpu_arm(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

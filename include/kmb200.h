@@ -1,0 +1,234 @@
+/*
+ * kmb200 — C ABI of the B200 (sm_100a) KMeans kernels.
+ *
+ * The reference (soda-inria/sklearn-numba-dpex) has no foreign-function boundary:
+ * its drivers call numba_dpex kernel objects directly.  Each entry point below
+ * replaces one such kernel (or a fixed short sequence of them) and cites the
+ * reference kernel factory it stands for, path relative to the reference root.
+ *
+ * Conventions
+ *  - every function returns KMB_OK (0) or a negative kmb_status; it never throws,
+ *    never exits; kmb_last_error() gives the message of the calling thread's last
+ *    failure;
+ *  - all array arguments are DEVICE pointers owned by the caller unless a comment
+ *    says "host"; nothing is allocated or freed inside the library; scratch comes
+ *    from a caller-provided workspace (see kmb_workspace_bytes);
+ *  - `dtype` is KMB_F32 or KMB_F64 and names the type of every `void*` array of
+ *    floating-point data in that call;
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued, not awaited;
+ *  - layout: samples are rows.  X is (n, d) row-major, centroids C are (k, d)
+ *    row-major (the reference holds the transposes X_t (d, n), centroids_t (d, k));
+ *    labels are uint32 (n); weights (n) may be NULL, meaning all ones.
+ */
+#ifndef KMB200_H
+#define KMB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { KMB_F32 = 0, KMB_F64 = 1 } kmb_dtype;
+
+typedef enum {
+  KMB_OK = 0,
+  KMB_ERR_INVALID = -1,     /* bad argument (shape, dtype, NULL, alignment)          */
+  KMB_ERR_CUDA = -2,        /* a CUDA runtime / driver call failed                   */
+  KMB_ERR_UNSUPPORTED = -3, /* valid request this build / device cannot serve        */
+  KMB_ERR_WORKSPACE = -4    /* caller's workspace is too small                       */
+} kmb_status;
+
+/* Which contraction the fused step / label assignment uses. */
+typedef enum {
+  KMB_ALGO_AUTO = 0,      /* tensor cores when the shape qualifies, else CUDA cores  */
+  KMB_ALGO_CUDA_CORE = 1, /* register-tiled FMA kernel (fp32 and fp64)               */
+  KMB_ALGO_TF32X3 = 2     /* tcgen05 kind::tf32, 3 products per pair (fp32 only)     */
+} kmb_algo;
+
+/* Record written by kmb_lloyd_finalize (device memory, 32 bytes). */
+typedef struct {
+  int32_t n_empty;     /* clusters whose weight sum is exactly 0                      */
+  int32_t changed;     /* 1 if any label differs from the previous labels, else 0     */
+  double shift_total;  /* sum_j sum_f (C_old - C_new)^2                               */
+  double inertia;      /* reserved (0)                                                */
+  double reserved;
+} kmb_lloyd_status;
+
+const char* kmb_last_error(void);
+int kmb_version(void);
+/* SM count and compute capability of `device` (host outputs). */
+int kmb_device_info(int device, int* sm_count, int* cc_major, int* cc_minor);
+
+/* Bytes of scratch that is enough for ANY call below on these sizes. */
+size_t kmb_workspace_bytes(int64_t n, int d, int k);
+
+/* Length, in elements of `dtype`, of one accumulator copy used by kmb_lloyd_step:
+ * [ sums k*d | counts k | changed 1 | padding ] rounded up to a multiple of 64. */
+int64_t kmb_lloyd_acc_len(int d, int k);
+/* Number of accumulator copies kmb_lloyd_step wants for this shape and algo. */
+int kmb_lloyd_acc_copies(int dtype, int algo, int64_t n, int d, int k);
+/* The algo KMB_ALGO_AUTO resolves to for this shape. */
+int kmb_lloyd_resolve_algo(int dtype, int algo, int64_t n, int d, int k);
+
+/* half_norms[j] = (sum_f C[j,f]^2) / 2.
+ * Replaces make_half_l2_norm_2d_axis0_kernel, sklearn_numba_dpex/common/kernels.py:117-145. */
+int kmb_half_l2_norm(int dtype, const void* C, void* half_norms, int k, int d, void* stream);
+
+/* One fused Lloyd step over n samples: label_i = argmin_j (half_norms[j] - x_i.c_j)
+ * (lowest j on ties), labels written, number of labels differing from prev_labels
+ * counted (prev_labels may be NULL: counts n), and w_i*x_i / w_i accumulated into
+ * copy (blockIdx % n_copies) of `acc` (n_copies x kmb_lloyd_acc_len).  `acc` is
+ * cleared by this call.
+ * Replaces make_lloyd_single_step_fixed_window_kernel,
+ * sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:35-424, and the two
+ * make_initialize_to_zeros_kernel launches of kmeans/drivers.py:195-196. */
+int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void* C,
+                   const void* half_norms, const uint32_t* prev_labels, uint32_t* labels,
+                   void* acc, int n_copies, int64_t n, int d, int k, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/* out[e] = sum over copies of acc[c][e], copies added in ascending order.
+ * Replaces the private-copy summation of make_reduce_centroid_data_kernel,
+ * sklearn_numba_dpex/kmeans/kernels/utils.py:130-157. */
+int kmb_lloyd_merge_copies(int dtype, const void* acc, int n_copies, int64_t acc_len,
+                           void* out, void* stream);
+
+/* From one merged accumulator (kmb_lloyd_acc_len elements): C_new = sums / counts,
+ * half norms of C_new, total squared shift against C_old, ascending list of empty
+ * clusters, and the status record.  `shifts` is k elements of scratch in `dtype`.
+ * Replaces make_reduce_centroid_data_kernel's empty-cluster list (utils.py:159-167),
+ * make_broadcast_division_1d_2d_axis0_kernel (common/kernels.py:61-82),
+ * make_centroid_shifts_kernel (kmeans/kernels/utils.py:80-110) with its sum
+ * reduction, and make_half_l2_norm_2d_axis0_kernel of the next iteration. */
+int kmb_lloyd_finalize(int dtype, const void* acc, const void* C_old, void* C_new,
+                       void* half_norms_new, void* shifts, uint32_t* empty_list,
+                       kmb_lloyd_status* status, int k, int d, void* stream);
+
+/* labels only.  Replaces make_label_assignment_fixed_window_kernel,
+ * sklearn_numba_dpex/kmeans/kernels/compute_labels.py:19-185. */
+int kmb_assign_labels(int dtype, int algo, const void* X, const void* C,
+                      const void* half_norms, uint32_t* labels, int64_t n, int d, int k,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* per_sample[i] = w_i * sum_f (X[i,f] - C[labels[i],f])^2 (per_sample may be NULL);
+ * total (may be NULL) receives the sum over i as one element of `dtype`, summed in
+ * float64 in a fixed order.
+ * Replaces make_compute_inertia_kernel, kmeans/kernels/compute_inertia.py:9-42, and the
+ * make_sum_reduction_2d_kernel that follows it (kmeans/drivers.py:379-391). */
+int kmb_inertia(int dtype, const void* X, const void* w, const void* C,
+                const uint32_t* labels, void* per_sample, void* total, int64_t n, int d,
+                int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* out_t[j*n + i] = sqrt(sum_f (Y[j,f] - X[i,f])^2): the (k, n) array whose transpose
+ * the reference returns.  Replaces make_compute_euclidean_distances_fixed_window_kernel,
+ * kmeans/kernels/compute_euclidean_distances.py:16-161. */
+int kmb_euclidean_distances(int dtype, const void* X, const void* Y, void* out_t,
+                            int64_t n, int d, int k, void* stream);
+
+/* Empty-cluster relocation on un-normalised sums: for i < n_reloc, j = empty_list[i],
+ * q = far_idx[i]: sums[label_q] -= w_q x_q; sums[j] = w_q x_q; counts likewise;
+ * per_sample[q] = 0 (per_sample may be NULL).  `acc` is one merged accumulator.
+ * Replaces make_relocate_empty_clusters_kernel, kmeans/kernels/utils.py:12-76. */
+int kmb_relocate_empty_clusters(int dtype, const void* X, const void* w,
+                                const uint32_t* labels, const int64_t* far_idx,
+                                const uint32_t* empty_list, int n_reloc, void* per_sample,
+                                void* acc, int d, int k, void* stream);
+
+/* Row-wise k largest of `values` (n_rows, n_cols) by radix select.  out_values
+ * (n_rows, k) and/or out_idx (n_rows, k) int64 may be NULL.  Output is ordered by
+ * descending value, ties by ascending index (the reference leaves both undefined).
+ * Replaces topk / topk_idx, sklearn_numba_dpex/common/topk.py:112-270 and the kernels
+ * at :621-771, :1003-1093, :1143-1365. */
+int kmb_topk(int dtype, const void* values, int n_rows, int64_t n_cols, int k,
+             void* out_values, int64_t* out_idx, void* workspace, size_t workspace_bytes,
+             void* stream);
+size_t kmb_topk_workspace_bytes(int n_rows, int64_t n_cols, int k);
+
+/* ---- k-means++ (kmeans/drivers.py:735-910) ---------------------------------------- */
+/* Rows per partial-sum block used by the k-means++ kernels. */
+int kmb_kpp_block_rows(void);
+
+/* closest[i] = w_i * ||X[i] - X[first]||^2, bsum[b] = float64 sum of block b,
+ * centers row 0 = X[first], indices[0] = first.
+ * Replaces make_kmeansplusplus_init_kernel, kmeans/kernels/kmeans_plusplus.py:16-58, and
+ * the potential sum of drivers.py:844. */
+int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, void* closest,
+                 double* bsum, void* centers, int32_t* indices, int64_t n, int d,
+                 void* stream);
+
+/* For each trial tau < t: r = u[tau] * total, cand[tau] = first i whose inclusive prefix
+ * sum of closest reaches r (0 if r <= 0, n-1 if never).  closest is row *best of
+ * M (.., n) and its block sums row *best of bsum (.., nb); the prefix is taken in
+ * float64.  Replaces make_sample_center_candidates_kernel,
+ * kmeans/kernels/kmeans_plusplus.py:61-103 (a sequential running sum there). */
+int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
+                   const void* total, const void* u, int t, int32_t* cand, int64_t n,
+                   void* stream);
+
+/* out[tau, :] = X[ids[tau], :]  (ids on device). */
+int kmb_gather_rows(int dtype, const void* X, const int32_t* ids, int t, int d, void* out,
+                    void* stream);
+
+/* M_out[tau, i] = min(w_i * ||cand_rows[tau] - X[i]||^2, closest[i]) and
+ * bsum_out[tau, b] = float64 block sums, closest = row *best of M_prev.
+ * Replaces make_kmeansplusplus_single_step_fixed_window_kernel,
+ * kmeans/kernels/kmeans_plusplus.py:106-262, and the row sums of drivers.py:895. */
+int kmb_kpp_step(int dtype, const void* X, const void* w, const void* cand_rows,
+                 const void* M_prev, const int32_t* best_prev, void* M_out,
+                 double* bsum_out, int64_t n, int d, int t, void* stream);
+
+/* pots[tau] = sum_b bsum[tau, b] (fixed order, rounded to dtype); *best = argmin (lowest
+ * tau on ties); *total = pots[*best]; centers row c = cand_rows[*best];
+ * indices[c] = cand[*best].  Replaces make_argmin_reduction_1d_kernel
+ * (common/reductions.py:18-209) and the host steps of drivers.py:897-908. */
+int kmb_kpp_select(int dtype, const double* bsum, int t, int64_t nb, void* pots,
+                   int32_t* best, void* total, const void* cand_rows, const int32_t* cand,
+                   void* centers, int32_t* indices, int c, int d, void* stream);
+
+/* ---- data preparation (kmeans/drivers.py:436-589) --------------------------------- */
+/* out[f] = sum_i X[i,f] in float64 (d doubles). Replaces make_sum_reduction_2d_kernel
+ * axis=1 (common/reductions.py:214-393) at drivers.py:478. */
+int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* workspace,
+                 size_t workspace_bytes, void* stream);
+/* *out = sum_i v[i] (square=0) or sum_i v[i]^2 (square=1), float64, fixed order.
+ * Replaces the 1-D make_sum_reduction_2d_kernel uses at drivers.py:470-476, 516-524,
+ * 533-540. */
+int kmb_sum(int dtype, const void* v, int64_t len, int square, double* out, void* workspace,
+            size_t workspace_bytes, void* stream);
+/* X[i,f] += sign * vec[f].  Replaces make_broadcast_ops_1d_2d_axis1_kernel,
+ * common/kernels.py:86-113. */
+int kmb_add_row_vector(int dtype, void* X, int64_t n, int d, const void* vec, double sign,
+                       void* stream);
+
+/* ---- label utilities (kmeans/kernels/utils.py:199-279) ---------------------------- */
+/* *result = 1 if the two labelings are equal up to a permutation of label values.
+ * map_scratch: k int32.  Replaces make_is_same_clustering_kernel. */
+int kmb_same_clustering(const uint32_t* labels1, const uint32_t* labels2, int64_t n, int k,
+                        int32_t* map_scratch, int32_t* result, void* stream);
+/* *out = number of distinct label values. seen_scratch: k int32.
+ * Replaces make_get_nb_distinct_clusters_kernel. */
+int kmb_count_distinct(const uint32_t* labels, int64_t n, int k, int32_t* seen_scratch,
+                       int32_t* out, void* stream);
+
+/* ---- RNG, host only (sklearn_numba_dpex/common/random.py:29-292) ------------------- */
+/* states: host uint64[n_states][2].  SplitMix64 seeding then 2^64 jumps. */
+int kmb_xoroshiro_init(uint64_t* states, int n_states, uint64_t seed, int subsequence_start);
+/* next raw value of states[idx]; advances that state. */
+uint64_t kmb_xoroshiro_next(uint64_t* states, int idx);
+/* uint64 -> [0,1): (x>>40)*2^-24 as float, (x>>11)*2^-53 as double. */
+float kmb_u64_to_unit_f32(uint64_t x);
+double kmb_u64_to_unit_f64(uint64_t x);
+
+/* Test hook for the distance contraction alone: out[i,j] = sum_f X[i,f]*Y[j,f] with the
+ * named algo's arithmetic (m, n multiples of nothing in particular).  Stands for
+ * make_matmul_2d_kernel, sklearn_numba_dpex/common/matmul.py:13-489, which the KMeans
+ * path itself never calls. */
+int kmb_matmul_nt(int dtype, int algo, const void* X, const void* Y, void* out, int64_t m,
+                  int n, int kdim, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KMB200_H */

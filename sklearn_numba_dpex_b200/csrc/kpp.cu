@@ -1,0 +1,341 @@
+// k-means++ seeding kernels.  One round = sample (t CTAs) -> gather candidate rows ->
+// step (one pass over X) -> select (1 CTA); nothing returns to the host inside a round.
+//
+// Every pass over the samples also leaves float64 sums of blocks of KPP_BLOCK rows, so the
+// next round's sampler only has to walk the block sums and then one block of elements.
+// Stands for the kernels of sklearn_numba_dpex/kmeans/kernels/kmeans_plusplus.py and the
+// host loop of kmeans/drivers.py:847-908.
+#include "kmb_common.cuh"
+
+namespace kmb {
+
+constexpr int KPP_BLOCK = 2048;   // rows per partial-sum block
+constexpr int KPP_THREADS = 256;
+constexpr int KPP_MAX_T = 16;     // 2 + ln(k) stays below 16 for k < 1.2e6
+
+__device__ __forceinline__ double group_sum_kpp(double v, int G) {
+  for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// closest[i] = w_i * ||x_i - x_first||^2 ; bsum[block] = float64 sum.
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_init_kernel(const T* __restrict__ X, const T* __restrict__ w, int64_t first,
+                T* __restrict__ closest, double* __restrict__ bsum, T* __restrict__ centers,
+                int32_t* __restrict__ indices, int64_t n, int d, int G) {
+  __shared__ double red[32];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  T* c = reinterpret_cast<T*>(dyn_smem);
+  for (int f = threadIdx.x; f < d; f += KPP_THREADS) c[f] = X[first * (int64_t)d + f];
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers[f] = c[f];
+    if (threadIdx.x == 0) indices[0] = (int32_t)first;
+  }
+  const int rows_per_pass = KPP_THREADS / G;
+  const int g = threadIdx.x / G, l = threadIdx.x % G;
+  const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
+  double acc = 0.0;
+  for (int r = 0; r < KPP_BLOCK; r += rows_per_pass) {
+    const int64_t i = b0 + r + g;
+    T s = T(0);
+    if (i < n) {
+      const T* x = X + i * (int64_t)d;
+      for (int f = l; f < d; f += G) {
+        const T diff = x[f] - c[f];
+        s = fma(diff, diff, s);
+      }
+    }
+    const double sd = group_sum_kpp((double)s, G);
+    if (i < n && l == 0) {
+      const T v = (T)sd * (w ? w[i] : T(1));
+      closest[i] = v;
+      acc += (double)v;
+    }
+  }
+  const double tot = block_sum(acc, red);
+  if (threadIdx.x == 0) bsum[blockIdx.x] = tot;
+}
+
+// One CTA per trial.  r = u * total; walk the block sums, then the elements of the block
+// where the float64 inclusive prefix first reaches r.
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
+                  const int32_t* __restrict__ best, const T* __restrict__ total,
+                  const T* __restrict__ u, int32_t* __restrict__ cand, int64_t n, int64_t nb) {
+  __shared__ double scan_s[KPP_THREADS];
+  __shared__ double carry_s;
+  __shared__ unsigned long long found_s;  // smallest matching index, ~0 = none
+  const int tid = threadIdx.x;
+  const int b = best ? *best : 0;
+  const T* closest = M + (int64_t)b * n;
+  const double* bs = bsum + (int64_t)b * nb;
+  const T r_t = u[blockIdx.x] * total[0];
+  const double r = (double)r_t;
+  if (!(r > 0.0)) {
+    if (tid == 0) cand[blockIdx.x] = 0;
+    return;
+  }
+  if (tid == 0) {
+    carry_s = 0.0;
+    found_s = ~0ull;
+  }
+  __syncthreads();
+  // --- level 1: first block whose inclusive prefix >= r
+  for (int64_t c0 = 0; c0 < nb; c0 += KPP_THREADS) {
+    const int64_t j = c0 + tid;
+    scan_s[tid] = (j < nb) ? bs[j] : 0.0;
+    __syncthreads();
+    for (int o = 1; o < KPP_THREADS; o <<= 1) {
+      const double add = (tid >= o) ? scan_s[tid - o] : 0.0;
+      __syncthreads();
+      scan_s[tid] += add;
+      __syncthreads();
+    }
+    const double incl = carry_s + scan_s[tid];
+    const double excl = (tid == 0) ? carry_s : carry_s + scan_s[tid - 1];
+    if (j < nb && incl >= r && !(excl >= r)) atomicMin(&found_s, (unsigned long long)j);
+    __syncthreads();
+    if (found_s != ~0ull) break;
+    if (tid == 0) carry_s += scan_s[KPP_THREADS - 1];
+    __syncthreads();
+  }
+  if (found_s == ~0ull) {  // r beyond the last prefix: the running sum never reaches it
+    if (tid == 0) cand[blockIdx.x] = (int32_t)(n - 1);
+    return;
+  }
+  const int64_t blk = (int64_t)found_s;
+  // prefix before the block: carry_s (chunks before) + exclusive part inside the chunk
+  __syncthreads();
+  const int in_chunk = (int)(blk % KPP_THREADS);
+  const double before = carry_s + (in_chunk == 0 ? 0.0 : scan_s[in_chunk - 1]);
+  __syncthreads();
+  // --- level 2: elements of block blk, KPP_THREADS at a time
+  const int64_t e0 = blk * KPP_BLOCK;
+  const int64_t e1 = (e0 + KPP_BLOCK < n) ? (e0 + KPP_BLOCK) : n;
+  if (tid == 0) {
+    carry_s = before;
+    found_s = ~0ull;
+  }
+  __syncthreads();
+  for (int64_t c0 = e0; c0 < e1; c0 += KPP_THREADS) {
+    const int64_t i = c0 + tid;
+    scan_s[tid] = (i < e1) ? (double)closest[i] : 0.0;
+    __syncthreads();
+    for (int o = 1; o < KPP_THREADS; o <<= 1) {
+      const double add = (tid >= o) ? scan_s[tid - o] : 0.0;
+      __syncthreads();
+      scan_s[tid] += add;
+      __syncthreads();
+    }
+    const double incl = carry_s + scan_s[tid];
+    const double excl = (tid == 0) ? carry_s : carry_s + scan_s[tid - 1];
+    if (i < e1 && incl >= r && !(excl >= r)) atomicMin(&found_s, (unsigned long long)i);
+    __syncthreads();
+    if (found_s != ~0ull) break;
+    if (tid == 0) carry_s += scan_s[KPP_THREADS - 1];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    // rounding between the two levels can leave r just past the block's last prefix
+    const int64_t res = (found_s != ~0ull) ? (int64_t)found_s : (e1 - 1);
+    cand[blockIdx.x] = (int32_t)res;
+  }
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ X, const int32_t* __restrict__ ids, int d,
+                                   T* __restrict__ out) {
+  const int64_t row = ids[blockIdx.x];
+  for (int f = threadIdx.x; f < d; f += blockDim.x)
+    out[(int64_t)blockIdx.x * d + f] = X[row * (int64_t)d + f];
+}
+
+// M_out[tau, i] = min(w_i * ||cand_tau - x_i||^2, closest_i); bsum_out[tau, block].
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_step_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ cand_rows,
+                const T* __restrict__ M_prev, const int32_t* __restrict__ best_prev,
+                T* __restrict__ M_out, double* __restrict__ bsum_out, int64_t n, int d, int t,
+                int64_t nb, int G) {
+  __shared__ double red[32];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  T* c = reinterpret_cast<T*>(dyn_smem);  // t x d
+  for (int e = threadIdx.x; e < t * d; e += KPP_THREADS) c[e] = cand_rows[e];
+  __syncthreads();
+  const T* closest = M_prev + (int64_t)(best_prev ? *best_prev : 0) * n;
+  const int rows_per_pass = KPP_THREADS / G;
+  const int g = threadIdx.x / G, l = threadIdx.x % G;
+  const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
+  double acc[KPP_MAX_T];
+#pragma unroll
+  for (int tau = 0; tau < KPP_MAX_T; ++tau) acc[tau] = 0.0;
+
+  for (int r = 0; r < KPP_BLOCK; r += rows_per_pass) {
+    const int64_t i = b0 + r + g;
+    T s[KPP_MAX_T];
+#pragma unroll
+    for (int tau = 0; tau < KPP_MAX_T; ++tau) s[tau] = T(0);
+    if (i < n) {
+      const T* x = X + i * (int64_t)d;
+      for (int f = l; f < d; f += G) {
+        const T xv = x[f];
+#pragma unroll
+        for (int tau = 0; tau < KPP_MAX_T; ++tau) {
+          if (tau < t) {
+            const T diff = c[tau * d + f] - xv;
+            s[tau] = fma(diff, diff, s[tau]);
+          }
+        }
+      }
+    }
+    const T wi = (i < n) ? (w ? w[i] : T(1)) : T(0);
+    const T cl = (i < n) ? closest[i] : T(0);
+#pragma unroll
+    for (int tau = 0; tau < KPP_MAX_T; ++tau) {
+      if (tau < t) {
+        const double sd = group_sum_kpp((double)s[tau], G);
+        if (i < n && l == 0) {
+          T v = (T)sd * wi;
+          v = (v < cl) ? v : cl;
+          M_out[(int64_t)tau * n + i] = v;
+          acc[tau] += (double)v;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int tau = 0; tau < KPP_MAX_T; ++tau) {
+    if (tau < t) {
+      const double tot = block_sum(acc[tau], red);
+      if (threadIdx.x == 0) bsum_out[(int64_t)tau * nb + blockIdx.x] = tot;
+    }
+  }
+}
+
+// Single CTA: potentials in fixed order, argmin (lowest trial on ties), commit the centre.
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_select_kernel(const double* __restrict__ bsum, int t, int64_t nb, T* __restrict__ pots,
+                  int32_t* __restrict__ best, T* __restrict__ total,
+                  const T* __restrict__ cand_rows, const int32_t* __restrict__ cand,
+                  T* __restrict__ centers, int32_t* __restrict__ indices, int c, int d) {
+  __shared__ double red[32];
+  __shared__ T pots_s[KPP_MAX_T];
+  __shared__ int best_s;
+  for (int tau = 0; tau < t; ++tau) {
+    double s = 0.0;
+    for (int64_t b = threadIdx.x; b < nb; b += KPP_THREADS) s += bsum[(int64_t)tau * nb + b];
+    const double tot = block_sum(s, red);
+    if (threadIdx.x == 0) pots_s[tau] = (T)tot;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int bi = 0;
+    T bv = pots_s[0];
+    for (int tau = 1; tau < t; ++tau)
+      if (pots_s[tau] < bv) {
+        bv = pots_s[tau];
+        bi = tau;
+      }
+    best_s = bi;
+    *best = bi;
+    *total = bv;
+    if (pots)
+      for (int tau = 0; tau < t; ++tau) pots[tau] = pots_s[tau];
+    if (indices && cand) indices[c] = cand[bi];
+  }
+  __syncthreads();
+  if (centers && cand_rows)
+    for (int f = threadIdx.x; f < d; f += KPP_THREADS)
+      centers[(int64_t)c * d + f] = cand_rows[(int64_t)best_s * d + f];
+}
+
+}  // namespace kmb
+
+using namespace kmb;
+
+extern "C" {
+
+int kmb_kpp_block_rows(void) { return KPP_BLOCK; }
+
+int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, void* closest,
+                 double* bsum, void* centers, int32_t* indices, int64_t n, int d, void* stream) {
+  KMB_REQUIRE(X && closest && bsum && centers && indices, "kmb_kpp_init: NULL argument");
+  KMB_REQUIRE(n > 0 && d > 0 && first >= 0 && first < n, "kmb_kpp_init: bad sizes");
+  KMB_REQUIRE(n < (1ll << 31), "kmb_kpp_init: n must be below 2^31 (int32 candidate ids)");
+  const int G = lanes_per_row(d);
+  const int64_t nb = ceil_div(n, KPP_BLOCK);
+  KMB_DISPATCH_DTYPE(dtype, {
+    const size_t dyn = (size_t)d * sizeof(T);
+    KMB_REQUIRE(dyn <= 48 * 1024, "kmb_kpp_init: d too large (%d)", d);
+    kpp_init_kernel<T><<<(unsigned)nb, KPP_THREADS, dyn, (cudaStream_t)stream>>>(
+        (const T*)X, (const T*)w, first, (T*)closest, bsum, (T*)centers, indices, n, d, G);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
+                   const void* total, const void* u, int t, int32_t* cand, int64_t n,
+                   void* stream) {
+  KMB_REQUIRE(M && bsum && total && u && cand, "kmb_kpp_sample: NULL argument");
+  KMB_REQUIRE(n > 0 && t > 0 && t <= KPP_MAX_T, "kmb_kpp_sample: bad sizes");
+  const int64_t nb = ceil_div(n, KPP_BLOCK);
+  KMB_DISPATCH_DTYPE(dtype, {
+    kpp_sample_kernel<T><<<t, KPP_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)M, bsum, best, (const T*)total, (const T*)u, cand, n, nb);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_gather_rows(int dtype, const void* X, const int32_t* ids, int t, int d, void* out,
+                    void* stream) {
+  KMB_REQUIRE(X && ids && out && t > 0 && d > 0, "kmb_gather_rows: bad arguments");
+  KMB_DISPATCH_DTYPE(dtype, {
+    gather_rows_kernel<T><<<t, 128, 0, (cudaStream_t)stream>>>((const T*)X, ids, d, (T*)out);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_kpp_step(int dtype, const void* X, const void* w, const void* cand_rows, const void* M_prev,
+                 const int32_t* best_prev, void* M_out, double* bsum_out, int64_t n, int d, int t,
+                 void* stream) {
+  KMB_REQUIRE(X && cand_rows && M_prev && M_out && bsum_out, "kmb_kpp_step: NULL argument");
+  KMB_REQUIRE(n > 0 && d > 0 && t > 0 && t <= KPP_MAX_T, "kmb_kpp_step: bad sizes (t <= %d)",
+              KPP_MAX_T);
+  const int G = lanes_per_row(d);
+  const int64_t nb = ceil_div(n, KPP_BLOCK);
+  KMB_DISPATCH_DTYPE(dtype, {
+    const size_t dyn = (size_t)t * d * sizeof(T);
+    KMB_REQUIRE(dyn <= 96 * 1024, "kmb_kpp_step: t*d too large (%d x %d)", t, d);
+    auto kern = kpp_step_kernel<T>;
+    if (dyn > 48 * 1024)
+      KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    kern<<<(unsigned)nb, KPP_THREADS, dyn, (cudaStream_t)stream>>>(
+        (const T*)X, (const T*)w, (const T*)cand_rows, (const T*)M_prev, best_prev, (T*)M_out,
+        bsum_out, n, d, t, nb, G);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_kpp_select(int dtype, const double* bsum, int t, int64_t nb, void* pots, int32_t* best,
+                   void* total, const void* cand_rows, const int32_t* cand, void* centers,
+                   int32_t* indices, int c, int d, void* stream) {
+  KMB_REQUIRE(bsum && best && total, "kmb_kpp_select: NULL argument");
+  KMB_REQUIRE(t > 0 && t <= KPP_MAX_T && nb > 0 && c >= 0 && d > 0, "kmb_kpp_select: bad sizes");
+  KMB_DISPATCH_DTYPE(dtype, {
+    kpp_select_kernel<T><<<1, KPP_THREADS, 0, (cudaStream_t)stream>>>(
+        bsum, t, nb, (T*)pots, best, (T*)total, (const T*)cand_rows, cand, (T*)centers, indices, c,
+        d);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,396 @@
+// Single-pass row kernels, all bound by HBM bandwidth: inertia, euclidean distances,
+// column sums / sums of squares, row-vector add (centring), relocation, label utilities.
+//
+// Row kernels give each sample row to a group of G lanes (G = smallest power of two >= d,
+// at most 32): lane l of the group reads features l, l+G, ... so a warp reads whole rows
+// back to back, and the group folds its partial sums with shuffles in a fixed order.
+#include "kmb_common.cuh"
+
+namespace kmb {
+
+constexpr int RS_THREADS = 256;
+constexpr int RS_MAX_BLOCKS = 2048;  // fixed-order partial sums: one float64 per block
+
+__device__ __forceinline__ double group_sum(double v, int G) {
+  for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// per_sample[i] = w_i * sum_f (x - c[label])^2 ; partial[b] = float64 block sum.
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ C,
+               const uint32_t* __restrict__ labels, T* __restrict__ per_sample,
+               double* __restrict__ partial, int64_t n, int d, int G) {
+  __shared__ double red[32];
+  const int rows_per_block = RS_THREADS / G;
+  const int g = threadIdx.x / G, l = threadIdx.x % G;
+  double block_acc = 0.0;
+  for (int64_t row0 = (int64_t)blockIdx.x * rows_per_block; row0 < n;
+       row0 += (int64_t)gridDim.x * rows_per_block) {
+    const int64_t i = row0 + g;
+    T s = T(0);
+    if (i < n) {
+      const T* x = X + i * (int64_t)d;
+      const T* c = C + (int64_t)labels[i] * d;
+      for (int f = l; f < d; f += G) {
+        const T diff = x[f] - c[f];
+        s = fma(diff, diff, s);
+      }
+    }
+    double sd = group_sum((double)s, G);
+    if (i < n && l == 0) {
+      const T v = (T)sd * (w ? w[i] : T(1));
+      if (per_sample) per_sample[i] = v;
+      block_acc += (double)v;
+    }
+  }
+  const double tot = block_sum(block_acc, red);
+  if (threadIdx.x == 0 && partial) partial[blockIdx.x] = tot;
+}
+
+// out[q] = sum_b partial[q * stride + b] in ascending b, one block per q; written as T
+// when out_t is given, as float64 when out_d is given.
+template <typename T>
+__global__ void sum_partials_kernel(const double* __restrict__ partial, int count, int stride,
+                                    T* __restrict__ out_t, double* __restrict__ out_d) {
+  __shared__ double red[32];
+  const double* p = partial + (int64_t)blockIdx.x * stride;
+  double s = 0.0;
+  for (int b = threadIdx.x; b < count; b += blockDim.x) s += p[b];
+  const double tot = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    if (out_t) out_t[blockIdx.x] = (T)tot;
+    if (out_d) out_d[blockIdx.x] = tot;
+  }
+}
+
+// out_t[j*n + i] = sqrt(sum_f (Y[j,f] - X[i,f])^2).  One thread per (i, j-chunk): the
+// sample row sits in registers/L1, centroids of the chunk stream through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+distances_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict__ out_t,
+                 int64_t n, int d, int k, int jchunk) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  T* Ys = reinterpret_cast<T*>(dyn_smem);  // jchunk x d
+  const int j0 = blockIdx.y * jchunk;
+  const int nj = (k - j0 < jchunk) ? (k - j0) : jchunk;
+  for (int e = threadIdx.x; e < nj * d; e += RS_THREADS) Ys[e] = Y[(int64_t)j0 * d + e];
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x;
+  if (i >= n) return;
+  const T* x = X + i * (int64_t)d;
+  for (int j = 0; j < nj; ++j) {
+    T s = T(0);
+    for (int f = 0; f < d; ++f) {
+      const T diff = Ys[j * d + f] - x[f];
+      s = fma(diff, diff, s);
+    }
+    out_t[(int64_t)(j0 + j) * n + i] = sqrt(s);
+  }
+}
+
+// partial[b*d + f] = float64 sum over the block's rows of X[i, f].
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+col_sums_kernel(const T* __restrict__ X, double* __restrict__ partial, int64_t n, int d,
+                int64_t rows_per_block) {
+  // thread t owns features t, t+blockDim, ...; consecutive threads read consecutive floats.
+  const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t r1 = (r0 + rows_per_block < n) ? (r0 + rows_per_block) : n;
+  for (int f = threadIdx.x; f < d; f += RS_THREADS) {
+    double s = 0.0;
+    for (int64_t i = r0; i < r1; ++i) s += (double)X[i * (int64_t)d + f];
+    partial[(int64_t)f * gridDim.x + blockIdx.x] = s;
+  }
+}
+
+// Narrow rows (d < 32): flat sweep, each thread strides by a multiple of d so that it
+// always meets the same feature.
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+col_sums_flat_kernel(const T* __restrict__ X, double* __restrict__ partial, int64_t n, int d,
+                     int slots) {
+  // slots = largest multiple of d that is <= RS_THREADS; threads >= slots idle.
+  __shared__ double sh[RS_THREADS];
+  const int t = threadIdx.x;
+  double s = 0.0;
+  const int64_t total = n * (int64_t)d;
+  if (t < slots) {
+    for (int64_t e = (int64_t)blockIdx.x * slots + t; e < total; e += (int64_t)gridDim.x * slots)
+      s += (double)X[e];
+  }
+  sh[t] = s;
+  __syncthreads();
+  if (t < d) {
+    double acc = 0.0;
+    for (int u = t; u < slots; u += d) acc += sh[u];
+    partial[(int64_t)t * gridDim.x + blockIdx.x] = acc;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+sum_kernel(const T* __restrict__ v, int64_t len, int square, double* __restrict__ partial) {
+  __shared__ double red[32];
+  double s = 0.0;
+  for (int64_t e = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x; e < len;
+       e += (int64_t)gridDim.x * RS_THREADS) {
+    const double x = (double)v[e];
+    s += square ? x * x : x;
+  }
+  const double tot = block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = tot;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+add_row_vector_kernel(T* __restrict__ X, int64_t total, int d, const T* __restrict__ vec, T sign) {
+  for (int64_t e = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * RS_THREADS)
+    X[e] = X[e] + sign * vec[e % d];
+}
+
+// One block per relocated cluster (kmeans/kernels/utils.py:21-76 of the reference).
+template <typename T>
+__global__ void relocate_kernel(const T* __restrict__ X, const T* __restrict__ w,
+                                const uint32_t* __restrict__ labels,
+                                const int64_t* __restrict__ far_idx,
+                                const uint32_t* __restrict__ empty_list, T* __restrict__ per_sample,
+                                T* __restrict__ acc, int d, int k) {
+  const int r = blockIdx.x;
+  const uint32_t j = empty_list[r];
+  const int64_t q = far_idx[r];
+  const uint32_t donor = labels[q];
+  const T wq = w ? w[q] : T(1);
+  for (int f = threadIdx.x; f < d; f += blockDim.x) {
+    const T addend = X[q * (int64_t)d + f] * wq;
+    atomicAdd(&acc[(int64_t)donor * d + f], -addend);
+    acc[(int64_t)j * d + f] = addend;
+  }
+  if (threadIdx.x == 0) {
+    if (per_sample) per_sample[q] = T(0);
+    atomicAdd(&acc[(int64_t)k * d + donor], -wq);
+    acc[(int64_t)k * d + j] = wq;
+  }
+}
+
+__global__ void fill_i32_kernel(int32_t* p, int len, int32_t v) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < len) p[e] = v;
+}
+
+__global__ void build_mapping_kernel(const uint32_t* __restrict__ l1,
+                                     const uint32_t* __restrict__ l2, int64_t n, int k,
+                                     int32_t* __restrict__ mapping) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t a = l1[i];
+    if (a < (uint32_t)k) mapping[a] = (int32_t)l2[i];
+  }
+}
+
+__global__ void check_mapping_kernel(const uint32_t* __restrict__ l1,
+                                     const uint32_t* __restrict__ l2, int64_t n, int k,
+                                     const int32_t* __restrict__ mapping,
+                                     int32_t* __restrict__ result) {
+  bool bad = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t a = l1[i];
+    if (a >= (uint32_t)k || mapping[a] != (int32_t)l2[i]) bad = true;
+  }
+  if (bad) *result = 0;
+}
+
+__global__ void mark_seen_kernel(const uint32_t* __restrict__ labels, int64_t n, int k,
+                                 int32_t* __restrict__ seen) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t a = labels[i];
+    if (a < (uint32_t)k && seen[a] == 0) seen[a] = 1;
+  }
+}
+
+__global__ void count_seen_kernel(const int32_t* __restrict__ seen, int k, int32_t* out) {
+  __shared__ double red[32];
+  double s = 0.0;
+  for (int j = threadIdx.x; j < k; j += blockDim.x) s += seen[j] ? 1.0 : 0.0;
+  const double tot = block_sum(s, red);
+  if (threadIdx.x == 0) *out = (int32_t)tot;
+}
+
+static inline int scan_grid(int64_t items_per_block_unit, int64_t n_units) {
+  int64_t g = ceil_div(n_units, items_per_block_unit);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (g > cap) g = cap;
+  if (g > RS_MAX_BLOCKS) g = RS_MAX_BLOCKS;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace kmb
+
+using namespace kmb;
+
+extern "C" {
+
+int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const uint32_t* labels,
+                void* per_sample, void* total, int64_t n, int d, int k, void* workspace,
+                size_t workspace_bytes, void* stream) {
+  KMB_REQUIRE(X && C && labels, "kmb_inertia: NULL argument");
+  KMB_REQUIRE(n >= 0 && d > 0 && k > 0, "kmb_inertia: bad sizes");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int G = lanes_per_row(d);
+  const int grid = scan_grid(RS_THREADS / G, n > 0 ? n : 1);
+  if (total) {
+    if (workspace == nullptr || workspace_bytes < (size_t)grid * sizeof(double)) {
+      set_error("kmb_inertia: workspace of %zu bytes needed, %zu given",
+                (size_t)grid * sizeof(double), workspace_bytes);
+      return KMB_ERR_WORKSPACE;
+    }
+  }
+  KMB_DISPATCH_DTYPE(dtype, {
+    inertia_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (const T*)w, (const T*)C, labels,
+                                                  (T*)per_sample, total ? (double*)workspace : nullptr,
+                                                  n, d, G);
+    KMB_CHECK_LAUNCH();
+    if (total) {
+      sum_partials_kernel<T><<<1, 256, 0, s>>>((const double*)workspace, grid, grid, (T*)total,
+                                               nullptr);
+      KMB_CHECK_LAUNCH();
+    }
+  });
+  return KMB_OK;
+}
+
+int kmb_euclidean_distances(int dtype, const void* X, const void* Y, void* out_t, int64_t n, int d,
+                            int k, void* stream) {
+  KMB_REQUIRE(X && Y && out_t, "kmb_euclidean_distances: NULL argument");
+  KMB_REQUIRE(n >= 0 && d > 0 && k > 0, "kmb_euclidean_distances: bad sizes");
+  if (n == 0) return KMB_OK;
+  const size_t esize = dtype == KMB_F32 ? 4 : 8;
+  KMB_REQUIRE((size_t)d * esize <= 32 * 1024, "kmb_euclidean_distances: d too large (%d)", d);
+  int jchunk = (int)((32 * 1024) / ((size_t)d * esize));
+  if (jchunk > k) jchunk = k;
+  if (jchunk > 64) jchunk = 64;
+  const int64_t gy = ceil_div(k, jchunk);
+  KMB_REQUIRE(gy <= 65535, "kmb_euclidean_distances: too many centroid chunks");
+  KMB_DISPATCH_DTYPE(dtype, {
+    dim3 grid((unsigned)ceil_div(n, RS_THREADS), (unsigned)gy);
+    distances_kernel<T><<<grid, RS_THREADS, (size_t)jchunk * d * sizeof(T), (cudaStream_t)stream>>>(
+        (const T*)X, (const T*)Y, (T*)out_t, n, d, k, jchunk);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+  KMB_REQUIRE(X && out && n >= 0 && d > 0, "kmb_col_sums: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  int grid;
+  const bool flat = d <= 32;
+  const int slots = flat ? (RS_THREADS / d) * d : 0;
+  if (flat) {
+    grid = scan_grid(slots, n * (int64_t)d > 0 ? n * (int64_t)d : 1);
+  } else {
+    grid = scan_grid(64, n > 0 ? n : 1);
+  }
+  const size_t need = (size_t)grid * d * sizeof(double);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("kmb_col_sums: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return KMB_ERR_WORKSPACE;
+  }
+  KMB_DISPATCH_DTYPE(dtype, {
+    if (flat) {
+      col_sums_flat_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (double*)workspace, n, d, slots);
+    } else {
+      const int64_t rpb = ceil_div(n > 0 ? n : 1, grid);
+      col_sums_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (double*)workspace, n, d, rpb);
+    }
+    KMB_CHECK_LAUNCH();
+    sum_partials_kernel<T><<<d, 256, 0, s>>>((const double*)workspace, grid, grid, nullptr, out);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_sum(int dtype, const void* v, int64_t len, int square, double* out, void* workspace,
+            size_t workspace_bytes, void* stream) {
+  KMB_REQUIRE(out && len >= 0 && (v || len == 0), "kmb_sum: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = scan_grid(RS_THREADS * 8, len > 0 ? len : 1);
+  const size_t need = (size_t)grid * sizeof(double);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("kmb_sum: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return KMB_ERR_WORKSPACE;
+  }
+  KMB_DISPATCH_DTYPE(dtype, {
+    sum_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)v, len, square, (double*)workspace);
+    KMB_CHECK_LAUNCH();
+    sum_partials_kernel<T><<<1, 256, 0, s>>>((const double*)workspace, grid, grid, nullptr, out);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_add_row_vector(int dtype, void* X, int64_t n, int d, const void* vec, double sign,
+                       void* stream) {
+  KMB_REQUIRE(X && vec && n >= 0 && d > 0, "kmb_add_row_vector: bad arguments");
+  if (n == 0) return KMB_OK;
+  const int64_t total = n * (int64_t)d;
+  const int grid = scan_grid(RS_THREADS * 4, total);
+  KMB_DISPATCH_DTYPE(dtype, {
+    add_row_vector_kernel<T><<<grid, RS_THREADS, 0, (cudaStream_t)stream>>>((T*)X, total, d,
+                                                                            (const T*)vec, (T)sign);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_relocate_empty_clusters(int dtype, const void* X, const void* w, const uint32_t* labels,
+                                const int64_t* far_idx, const uint32_t* empty_list, int n_reloc,
+                                void* per_sample, void* acc, int d, int k, void* stream) {
+  KMB_REQUIRE(X && labels && far_idx && empty_list && acc, "kmb_relocate_empty_clusters: NULL argument");
+  KMB_REQUIRE(n_reloc >= 0 && n_reloc <= k && d > 0, "kmb_relocate_empty_clusters: bad sizes");
+  if (n_reloc == 0) return KMB_OK;
+  KMB_DISPATCH_DTYPE(dtype, {
+    relocate_kernel<T><<<n_reloc, 128, 0, (cudaStream_t)stream>>>(
+        (const T*)X, (const T*)w, labels, far_idx, empty_list, (T*)per_sample, (T*)acc, d, k);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_same_clustering(const uint32_t* labels1, const uint32_t* labels2, int64_t n, int k,
+                        int32_t* map_scratch, int32_t* result, void* stream) {
+  KMB_REQUIRE(labels1 && labels2 && map_scratch && result && k > 0 && n >= 0,
+              "kmb_same_clustering: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  fill_i32_kernel<<<(unsigned)ceil_div(k, 256), 256, 0, s>>>(map_scratch, k, -1);
+  fill_i32_kernel<<<1, 32, 0, s>>>(result, 1, 1);
+  KMB_CHECK_LAUNCH();
+  if (n == 0) return KMB_OK;
+  const int grid = scan_grid(256 * 4, n);
+  build_mapping_kernel<<<grid, 256, 0, s>>>(labels1, labels2, n, k, map_scratch);
+  check_mapping_kernel<<<grid, 256, 0, s>>>(labels1, labels2, n, k, map_scratch, result);
+  KMB_CHECK_LAUNCH();
+  return KMB_OK;
+}
+
+int kmb_count_distinct(const uint32_t* labels, int64_t n, int k, int32_t* seen_scratch,
+                       int32_t* out, void* stream) {
+  KMB_REQUIRE(labels && seen_scratch && out && k > 0 && n >= 0, "kmb_count_distinct: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  fill_i32_kernel<<<(unsigned)ceil_div(k, 256), 256, 0, s>>>(seen_scratch, k, 0);
+  if (n > 0) {
+    const int grid = scan_grid(256 * 4, n);
+    mark_seen_kernel<<<grid, 256, 0, s>>>(labels, n, k, seen_scratch);
+  }
+  count_seen_kernel<<<1, 256, 0, s>>>(seen_scratch, k, out);
+  KMB_CHECK_LAUNCH();
+  return KMB_OK;
+}
+
+}  // extern "C"

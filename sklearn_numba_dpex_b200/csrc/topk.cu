@@ -1,0 +1,221 @@
+// Row-wise top-k by MSB-first radix select (8-bit digits, shared-memory histograms).
+//
+// The key of element i is (order-preserving unsigned image of the value) followed by the
+// 32-bit complement of i, so all keys of a row are distinct: the select needs no tie
+// budget, and "largest value first, lowest index first among equals" falls out of the
+// key order.  Stands for topk / topk_idx of sklearn_numba_dpex/common/topk.py:112-270
+// (histogram kernel :621-771, threshold search :1003-1093, gather :1143-1365), which leave
+// the order of the output and the choice among ties undefined.
+#include "kmb_common.cuh"
+
+namespace kmb {
+
+typedef unsigned __int128 u128;
+
+constexpr int TK_THREADS = 256;
+constexpr int TK_RADIX_BITS = 8;
+constexpr int TK_BINS = 1 << TK_RADIX_BITS;
+
+struct TkState {          // per row
+  unsigned long long prefix_hi, prefix_lo;  // digits decided so far (right-aligned)
+  long long k_rem;                          // how many of the matching items are wanted
+  unsigned long long cursor;                // gather cursor
+};
+
+template <typename T>
+struct TkKey;
+template <>
+struct TkKey<float> {
+  static constexpr int BITS = 64;
+  __device__ static __forceinline__ u128 make(float v, int64_t i) {
+    uint32_t b = __float_as_uint(v);
+    b ^= (b >> 31) ? 0xffffffffu : 0x80000000u;
+    return ((u128)b << 32) | (u128)(0xffffffffu - (uint32_t)i);
+  }
+};
+template <>
+struct TkKey<double> {
+  static constexpr int BITS = 96;
+  __device__ static __forceinline__ u128 make(double v, int64_t i) {
+    unsigned long long b = (unsigned long long)__double_as_longlong(v);
+    b ^= (b >> 63) ? 0xffffffffffffffffull : 0x8000000000000000ull;
+    return ((u128)b << 32) | (u128)(0xffffffffu - (uint32_t)i);
+  }
+};
+
+__global__ void topk_init_kernel(TkState* st, unsigned int* hist, int n_rows, int k,
+                                 size_t hist_len) {
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < hist_len) hist[e] = 0u;
+  if (e < (size_t)n_rows) {
+    st[e].prefix_hi = 0ull;
+    st[e].prefix_lo = 0ull;
+    st[e].k_rem = k;
+    st[e].cursor = 0ull;
+  }
+}
+
+// Histogram of the digit at `shift` over the items whose higher digits equal the prefix.
+template <typename T>
+__global__ void __launch_bounds__(TK_THREADS)
+topk_hist_kernel(const T* __restrict__ values, int64_t n_cols, const TkState* __restrict__ st,
+                 unsigned int* __restrict__ hist, int shift, int first_pass) {
+  __shared__ unsigned int sh[TK_BINS];
+  const int row = blockIdx.y;
+  const T* v = values + (int64_t)row * n_cols;
+  sh[threadIdx.x] = 0u;
+  __syncthreads();
+  const u128 prefix = ((u128)st[row].prefix_hi << 64) | (u128)st[row].prefix_lo;
+  for (int64_t i = (int64_t)blockIdx.x * TK_THREADS + threadIdx.x; i < n_cols;
+       i += (int64_t)gridDim.x * TK_THREADS) {
+    const u128 key = TkKey<T>::make(v[i], i);
+    if (first_pass || (key >> (shift + TK_RADIX_BITS)) == prefix)
+      atomicAdd(&sh[(unsigned)(key >> shift) & (TK_BINS - 1)], 1u);
+  }
+  __syncthreads();
+  const unsigned int c = sh[threadIdx.x];
+  if (c) atomicAdd(&hist[(size_t)row * TK_BINS + threadIdx.x], c);
+}
+
+// One warp per row: walk the bins from the top until k_rem items are covered.
+__global__ void topk_advance_kernel(TkState* __restrict__ st, const unsigned int* __restrict__ hist,
+                                    int n_rows) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n_rows) return;
+  const unsigned int* h = hist + (size_t)row * TK_BINS;
+  long long k_rem = st[row].k_rem;
+  int digit = 0;
+  for (int b = TK_BINS - 1; b >= 0; --b) {
+    const long long c = (long long)h[b];
+    if (c >= k_rem) {
+      digit = b;
+      break;
+    }
+    k_rem -= c;
+  }
+  u128 prefix = ((u128)st[row].prefix_hi << 64) | (u128)st[row].prefix_lo;
+  prefix = (prefix << TK_RADIX_BITS) | (u128)digit;
+  st[row].prefix_hi = (unsigned long long)(prefix >> 64);
+  st[row].prefix_lo = (unsigned long long)prefix;
+  st[row].k_rem = k_rem;
+}
+
+// Emit the items whose key is >= the k-th largest key (exactly k per row), unordered.
+template <typename T>
+__global__ void __launch_bounds__(TK_THREADS)
+topk_gather_kernel(const T* __restrict__ values, int64_t n_cols, TkState* __restrict__ st, int k,
+                   int64_t* __restrict__ tmp_idx) {
+  const int row = blockIdx.y;
+  const T* v = values + (int64_t)row * n_cols;
+  const u128 kth = ((u128)st[row].prefix_hi << 64) | (u128)st[row].prefix_lo;
+  for (int64_t i = (int64_t)blockIdx.x * TK_THREADS + threadIdx.x; i < n_cols;
+       i += (int64_t)gridDim.x * TK_THREADS) {
+    const u128 key = TkKey<T>::make(v[i], i);
+    if (key >= kth) {
+      const unsigned long long pos = atomicAdd(&st[row].cursor, 1ull);
+      if (pos < (unsigned long long)k) tmp_idx[(int64_t)row * k + pos] = i;
+    }
+  }
+}
+
+// Rank sort of the k winners of a row: position = number of winners with a larger key.
+template <typename T>
+__global__ void __launch_bounds__(TK_THREADS)
+topk_sort_kernel(const T* __restrict__ values, int64_t n_cols, int k,
+                 const int64_t* __restrict__ tmp_idx, T* __restrict__ out_values,
+                 int64_t* __restrict__ out_idx) {
+  const int row = blockIdx.y;
+  const int e = blockIdx.x * TK_THREADS + threadIdx.x;
+  if (e >= k) return;
+  const T* v = values + (int64_t)row * n_cols;
+  const int64_t* mine = tmp_idx + (int64_t)row * k;
+  const int64_t i = mine[e];
+  const T vi = v[i];
+  const u128 key = TkKey<T>::make(vi, i);
+  int rank = 0;
+  for (int o = 0; o < k; ++o) {
+    const int64_t j = mine[o];
+    rank += (TkKey<T>::make(v[j], j) > key) ? 1 : 0;
+  }
+  if (out_values) out_values[(int64_t)row * k + rank] = vi;
+  if (out_idx) out_idx[(int64_t)row * k + rank] = i;
+}
+
+template <typename T>
+int topk_run(const T* values, int n_rows, int64_t n_cols, int k, T* out_values, int64_t* out_idx,
+             void* workspace, cudaStream_t s) {
+  unsigned char* ws = (unsigned char*)workspace;
+  constexpr int n_passes = TkKey<T>::BITS / TK_RADIX_BITS;
+  TkState* st = (TkState*)ws;
+  size_t off = ((size_t)n_rows * sizeof(TkState) + 255) / 256 * 256;
+  unsigned int* hist = (unsigned int*)(ws + off);
+  const size_t hist_len = (size_t)n_passes * n_rows * TK_BINS;
+  off += (hist_len * sizeof(unsigned int) + 255) / 256 * 256;
+  int64_t* tmp_idx = (int64_t*)(ws + off);
+
+  const size_t init_items = hist_len > (size_t)n_rows ? hist_len : (size_t)n_rows;
+  topk_init_kernel<<<(unsigned)ceil_div((int64_t)init_items, 256), 256, 0, s>>>(st, hist, n_rows, k,
+                                                                               hist_len);
+  KMB_CHECK_LAUNCH();
+  int64_t gx = ceil_div(n_cols, (int64_t)TK_THREADS * 8);
+  const int64_t cap = ceil_div((int64_t)sm_count() * 8, n_rows);
+  if (gx > cap) gx = cap;
+  if (gx < 1) gx = 1;
+  dim3 grid((unsigned)gx, (unsigned)n_rows);
+  for (int p = 0; p < n_passes; ++p) {
+    const int shift = TkKey<T>::BITS - (p + 1) * TK_RADIX_BITS;
+    unsigned int* h = hist + (size_t)p * n_rows * TK_BINS;
+    topk_hist_kernel<T><<<grid, TK_THREADS, 0, s>>>(values, n_cols, st, h, shift, p == 0);
+    KMB_CHECK_LAUNCH();
+    topk_advance_kernel<<<(unsigned)ceil_div(n_rows, 128), 128, 0, s>>>(st, h, n_rows);
+    KMB_CHECK_LAUNCH();
+  }
+  topk_gather_kernel<T><<<grid, TK_THREADS, 0, s>>>(values, n_cols, st, k, tmp_idx);
+  KMB_CHECK_LAUNCH();
+  dim3 sgrid((unsigned)ceil_div(k, TK_THREADS), (unsigned)n_rows);
+  topk_sort_kernel<T><<<sgrid, TK_THREADS, 0, s>>>(values, n_cols, k, tmp_idx, out_values, out_idx);
+  KMB_CHECK_LAUNCH();
+  return KMB_OK;
+}
+
+}  // namespace kmb
+
+using namespace kmb;
+
+extern "C" {
+
+size_t kmb_topk_workspace_bytes(int n_rows, int64_t n_cols, int k) {
+  (void)n_cols;
+  if (n_rows < 1) n_rows = 1;
+  if (k < 1) k = 1;
+  const size_t n_passes = 96 / TK_RADIX_BITS;
+  size_t b = ((size_t)n_rows * sizeof(TkState) + 255) / 256 * 256;
+  b += (n_passes * (size_t)n_rows * TK_BINS * sizeof(unsigned int) + 255) / 256 * 256;
+  b += (size_t)n_rows * (size_t)k * sizeof(int64_t);
+  return b + 256;
+}
+
+int kmb_topk(int dtype, const void* values, int n_rows, int64_t n_cols, int k, void* out_values,
+             int64_t* out_idx, void* workspace, size_t workspace_bytes, void* stream) {
+  KMB_REQUIRE(values && (out_values || out_idx), "kmb_topk: NULL argument");
+  KMB_REQUIRE(n_rows >= 1 && n_rows <= 65535, "kmb_topk: n_rows must be in [1, 65535]");
+  KMB_REQUIRE(k >= 1, "kmb_topk: k must be >= 1");
+  if (n_cols < k) {
+    set_error("Expected k to be greater than or equal to the number of items in the search space, "
+              "but got k=%d and %lld items in the search space.", k, (long long)n_cols);
+    return KMB_ERR_INVALID;
+  }
+  KMB_REQUIRE(n_cols < (1ll << 32), "kmb_topk: n_cols must be below 2^32");
+  const size_t need = kmb_topk_workspace_bytes(n_rows, n_cols, k);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("kmb_topk: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return KMB_ERR_WORKSPACE;
+  }
+  KMB_REQUIRE(((uintptr_t)workspace & 15) == 0, "kmb_topk: workspace must be 16-byte aligned");
+  KMB_DISPATCH_DTYPE(dtype, {
+    return topk_run<T>((const T*)values, n_rows, n_cols, k, (T*)out_values, out_idx, workspace,
+                       (cudaStream_t)stream);
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+"""Row sharding over the GPUs of one box: one process per GPU, torch.distributed plumbing.
+
+The reference is single-device (it has no collective call sites); sharding is an addition
+of this engine.  Samples are split into contiguous row blocks, centroids are replicated, and
+per Lloyd iteration ONE all-reduce of the packed accumulator
+``[sums k*d | counts k | changed 1]`` is issued on the compute stream.  Everything here works
+on CPU tensors with the gloo backend as well, which is how the multi-rank logic is tested
+without GPUs.
+"""
+import contextlib
+
+import torch
+import torch.distributed as tdist
+
+_STATE = {"enabled": False, "group": None}
+
+
+def enable(group=None):
+    """Treat the X handed to the drivers as THIS rank's row shard from now on."""
+    if not tdist.is_initialized():
+        raise RuntimeError("torch.distributed is not initialised")
+    _STATE["enabled"] = True
+    _STATE["group"] = group
+
+
+def disable():
+    _STATE["enabled"] = False
+    _STATE["group"] = None
+
+
+@contextlib.contextmanager
+def sharded_rows(group=None):
+    enable(group)
+    try:
+        yield
+    finally:
+        disable()
+
+
+def active():
+    return _STATE["enabled"] and tdist.is_initialized() and world_size() > 1
+
+
+def world_size():
+    return tdist.get_world_size(_STATE["group"]) if tdist.is_initialized() else 1
+
+
+def rank():
+    return tdist.get_rank(_STATE["group"]) if tdist.is_initialized() else 0
+
+
+def shard_bounds(n, r=None, world=None):
+    """Contiguous block [start, stop) of rank r among `world` ranks: the first n % world
+    ranks hold one extra row."""
+    r = rank() if r is None else r
+    world = world_size() if world is None else world
+    base, extra = divmod(int(n), int(world))
+    start = r * base + min(r, extra)
+    return start, start + base + (1 if r < extra else 0)
+
+
+def all_reduce_sum_(t):
+    """In-place sum over ranks (no-op when sharding is off)."""
+    if active():
+        tdist.all_reduce(t, op=tdist.ReduceOp.SUM, group=_STATE["group"])
+    return t
+
+
+def all_gather_cat(t):
+    """Concatenation over ranks along dim 0 of equally shaped tensors."""
+    if not active():
+        return t
+    out = [torch.empty_like(t) for _ in range(world_size())]
+    tdist.all_gather(out, t.contiguous(), group=_STATE["group"])
+    return torch.cat(out, dim=0)
+
+
+def all_gather_object(obj):
+    if not active():
+        return [obj]
+    out = [None] * world_size()
+    tdist.all_gather_object(out, obj, group=_STATE["group"])
+    return out
+
+
+def broadcast_(t, src):
+    if active():
+        tdist.broadcast(t, src=src, group=_STATE["group"])
+    return t
+
+
+def check_same_across_ranks(**named_values):
+    """Host-side guard run before a sharded loop: every rank must agree on these values
+    (shapes, dtypes, seeds).  Raises ValueError on every rank when they do not."""
+    if not active():
+        return
+    gathered = all_gather_object(named_values)
+    first = gathered[0]
+    for r, other in enumerate(gathered):
+        if other != first:
+            raise ValueError(
+                f"ranks disagree on {sorted(named_values)}: rank 0 has {first}, rank {r} has {other}"
+            )
+
+
+def merge_topk(values, global_idx, m):
+    """Global top-m out of per-rank candidates.  `values` (c,) and `global_idx` (c,) are this
+    rank's candidates (c may differ per rank only through padding with -inf).  Returns the
+    positions, in the gathered candidate list, of the m winners ordered by descending value
+    then ascending global index, together with the gathered arrays."""
+    vals = all_gather_cat(values)
+    idx = all_gather_cat(global_idx)
+    # descending value, ascending index: stable sort on index first, then on value
+    order = torch.argsort(idx, stable=True)
+    order = order[torch.argsort(vals[order], descending=True, stable=True)]
+    return order[:m], vals, idx

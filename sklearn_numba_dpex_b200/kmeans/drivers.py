@@ -1,0 +1,509 @@
+"""Host-side drivers of the KMeans engine: same entry points, argument meaning and return
+values as sklearn_numba_dpex/kmeans/drivers.py of the reference, on torch CUDA tensors.
+
+Layout.  The reference's signatures take the transposes ``X_t (n_features, n_samples)`` and
+``centroids_t (n_features, n_clusters)``.  They are kept, but the kernels want samples as
+contiguous rows: a ``X_t`` that is the ``.T`` view of a row-major ``X`` (what the engine
+passes) costs nothing; a C-contiguous ``X_t`` is transposed into a new buffer once.
+
+Every O(n) operation is a kmb200 kernel called through the C ABI; torch is used for
+memory, streams and the collectives.
+"""
+import math
+
+import numpy as np
+import torch
+
+from .. import dist
+from .._cabi import (ALGO_AUTO, ALGO_NAMES, STATUS_DTYPE, c_void_p, check, dtype_code, lib, ptr,
+                     stream_ptr, workspace_for)
+
+
+# ----------------------------------------------------------------------------- helpers
+def _rows(X_t, name="X_t"):
+    """(n, d) contiguous row view/copy of a logical (d, n) tensor."""
+    if not isinstance(X_t, torch.Tensor) or not X_t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if X_t.dim() != 2:
+        raise ValueError(f"{name} must be 2-dimensional")
+    X = X_t.T
+    return X if X.is_contiguous() else X.contiguous()
+
+
+def _np_dtype(t):
+    return np.float32 if t.dtype == torch.float32 else np.float64
+
+
+def _algo_code(algo):
+    if isinstance(algo, str):
+        if algo not in ALGO_NAMES:
+            raise ValueError(f"algo must be one of {sorted(ALGO_NAMES)}, got {algo!r}")
+        return ALGO_NAMES[algo]
+    return int(algo)
+
+
+def _weights_or_none(sample_weight, use_uniform_weights):
+    """NULL weights mean all ones inside the kernels; use that when the weights are
+    uniformly 1 (one scalar read)."""
+    if sample_weight is None:
+        return None
+    if use_uniform_weights and sample_weight.numel() > 0 and float(sample_weight[0]) == 1.0:
+        return None
+    return sample_weight
+
+
+def _read_status(status_dev, status_host):
+    status_host.copy_(status_dev, non_blocking=True)
+    torch.cuda.current_stream(status_dev.device).synchronize()
+    rec = status_host.numpy().view(STATUS_DTYPE)[0]
+    return int(rec["n_empty"]), int(rec["changed"]), float(rec["shift_total"])
+
+
+class LloydState:
+    """Buffers and one-iteration step of the Lloyd loop (kmeans/drivers.py:146-343 of the
+    reference allocates the same set once per call).  `step()` is what the benchmark times."""
+
+    def __init__(self, X, sample_weight, centers, algo=ALGO_AUTO):
+        self.X = X
+        self.w = sample_weight
+        n, d = X.shape
+        k = centers.shape[0]
+        self.n, self.d, self.k = n, d, k
+        dev, dt = X.device, X.dtype
+        self.dtype = dtype_code(dt)
+        self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, _algo_code(algo), n, d, k),
+                          "kmb_lloyd_resolve_algo")
+        self.acc_len = lib.kmb_lloyd_acc_len(d, k)
+        self.n_copies = check(lib.kmb_lloyd_acc_copies(self.dtype, self.algo, n, d, k))
+        self.C = centers.contiguous().clone()
+        self.C_new = torch.empty_like(self.C)
+        self.h = torch.empty(k, dtype=dt, device=dev)
+        self.h_new = torch.empty(k, dtype=dt, device=dev)
+        self.shifts = torch.empty(k, dtype=dt, device=dev)
+        self.labels = torch.empty(n, dtype=torch.int32, device=dev)
+        self.labels_new = torch.empty(n, dtype=torch.int32, device=dev)
+        self.acc = torch.empty((self.n_copies, self.acc_len), dtype=dt, device=dev)
+        self.packed = (self.acc[0] if self.n_copies == 1
+                       else torch.empty(self.acc_len, dtype=dt, device=dev))
+        self.empty_list = torch.empty(k, dtype=torch.int32, device=dev)
+        self.status_dev = torch.empty(32, dtype=torch.uint8, device=dev)
+        self.status_host = torch.empty(32, dtype=torch.uint8).pin_memory()
+        self.ws, self.ws_bytes = workspace_for(dev, n, d, k)
+        self.sq_dist = None
+        self.have_prev = False
+        self.kernel_launches = 0
+        check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
+              "kmb_half_l2_norm")
+        self.kernel_launches += 1
+
+    # -- pieces -----------------------------------------------------------------------
+    def _finalize(self):
+        check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.packed), ptr(self.C), ptr(self.C_new),
+                                     ptr(self.h_new), ptr(self.shifts), ptr(self.empty_list),
+                                     ptr(self.status_dev), self.k, self.d,
+                                     stream_ptr(self.X.device)), "kmb_lloyd_finalize")
+        self.kernel_launches += 2
+
+    def launch_step(self):
+        """E-step + accumulation + reduction + finalize, all enqueued (no host read)."""
+        dev = self.X.device
+        check(lib.kmb_lloyd_step(self.dtype, self.algo, ptr(self.X), ptr(self.w), ptr(self.C),
+                                 ptr(self.h), ptr(self.labels) if self.have_prev else None,
+                                 ptr(self.labels_new), ptr(self.acc), self.n_copies, self.n,
+                                 self.d, self.k, ptr(self.ws), self.ws_bytes, stream_ptr(dev)),
+              "kmb_lloyd_step")
+        self.kernel_launches += 1
+        if self.n_copies > 1:
+            check(lib.kmb_lloyd_merge_copies(self.dtype, ptr(self.acc), self.n_copies,
+                                             self.acc_len, ptr(self.packed), stream_ptr(dev)),
+                  "kmb_lloyd_merge_copies")
+            self.kernel_launches += 1
+        dist.all_reduce_sum_(self.packed)
+        self._finalize()
+
+    def _relocate(self, n_empty):
+        """kmeans/drivers.py:238-272 and 396-433 of the reference.  The distances that rank
+        the samples are taken against the un-normalised sums, exactly as there (the inertia
+        kernel runs before the division by the cluster sizes)."""
+        dev, dt = self.X.device, self.X.dtype
+        if self.sq_dist is None:
+            self.sq_dist = torch.empty(self.n, dtype=dt, device=dev)
+        check(lib.kmb_inertia(self.dtype, ptr(self.X), None, ptr(self.packed),
+                              ptr(self.labels_new), ptr(self.sq_dist), None, self.n, self.d,
+                              self.k, ptr(self.ws), self.ws_bytes, stream_ptr(dev)), "kmb_inertia")
+        m_local = min(n_empty, self.n)
+        far = topk_idx_1d(self.sq_dist, m_local) if m_local > 0 else \
+            torch.empty(0, dtype=torch.int64, device=dev)
+        if dist.active():
+            X_rows, w_rows, lab_rows, far = _gather_relocation_candidates(self, far, n_empty)
+        else:
+            X_rows, w_rows, lab_rows = self.X, self.w, self.labels_new
+        check(lib.kmb_relocate_empty_clusters(self.dtype, ptr(X_rows), ptr(w_rows), ptr(lab_rows),
+                                              ptr(far), ptr(self.empty_list),
+                                              min(n_empty, int(far.numel())), None,
+                                              ptr(self.packed), self.d, self.k, stream_ptr(dev)),
+              "kmb_relocate_empty_clusters")
+        self.kernel_launches += 2
+        self._finalize()
+
+    def step(self):
+        """One Lloyd iteration.  Returns (n_empty_before_relocation, changed, shift_total)."""
+        self.launch_step()
+        n_empty, changed, shift = _read_status(self.status_dev, self.status_host)
+        if n_empty > 0:
+            self._relocate(n_empty)
+            _, _, shift = _read_status(self.status_dev, self.status_host)
+        self.C, self.C_new = self.C_new, self.C
+        self.h, self.h_new = self.h_new, self.h
+        self.labels, self.labels_new = self.labels_new, self.labels
+        self.have_prev = True
+        return n_empty, changed, shift
+
+    def final_labels_inertia(self):
+        dev = self.X.device
+        check(lib.kmb_assign_labels(self.dtype, self.algo, ptr(self.X), ptr(self.C), ptr(self.h),
+                                    ptr(self.labels), self.n, self.d, self.k, ptr(self.ws),
+                                    self.ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+        total = torch.empty(1, dtype=self.X.dtype, device=dev)
+        check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.C), ptr(self.labels),
+                              None, ptr(total), self.n, self.d, self.k, ptr(self.ws),
+                              self.ws_bytes, stream_ptr(dev)), "kmb_inertia")
+        self.kernel_launches += 3
+        dist.all_reduce_sum_(total)
+        return self.labels, total
+
+
+def _gather_relocation_candidates(state, far_local, n_empty):
+    """Sharded relocation: every rank offers its local top candidates; all ranks pick the
+    same global winners and apply the relocation to their replicated sums."""
+    dev, dt = state.X.device, state.X.dtype
+    m = n_empty
+    counts = dist.all_gather_object(int(state.n))
+    offset = sum(counts[: dist.rank()])
+    vals = torch.full((m,), -math.inf, dtype=dt, device=dev)
+    gidx = torch.full((m,), -1, dtype=torch.int64, device=dev)
+    rows = torch.zeros((m, state.d), dtype=dt, device=dev)
+    wts = torch.zeros((m,), dtype=dt, device=dev)
+    labs = torch.zeros((m,), dtype=torch.int32, device=dev)
+    c = int(far_local.numel())
+    if c:
+        vals[:c] = state.sq_dist[far_local]
+        gidx[:c] = far_local + offset
+        rows[:c] = state.X[far_local]
+        wts[:c] = state.w[far_local] if state.w is not None else 1.0
+        labs[:c] = state.labels_new[far_local]
+    winners, _, _ = dist.merge_topk(vals, gidx, m)
+    rows_g = dist.all_gather_cat(rows)
+    wts_g = dist.all_gather_cat(wts)
+    labs_g = dist.all_gather_cat(labs)
+    valid = dist.all_gather_cat(gidx)[winners] >= 0
+    winners = winners[valid]
+    return rows_g.contiguous(), wts_g.contiguous(), labs_g.contiguous(), winners.contiguous()
+
+
+# -------------------------------------------------------------------------------- lloyd
+def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, verbose=False,
+          tol=1e-4, algo="auto"):
+    """Lloyd's algorithm.  Same contract as `lloyd` of the reference
+    (sklearn_numba_dpex/kmeans/drivers.py:43-393): returns
+    ``(labels (n,), inertia (host scalar of the compute dtype), centroids_t (d, k), n_iter)``.
+
+    Labels are int32 holding the reference's uint32 values.  The strict-convergence test
+    follows the reference: the flag is first armed after the second iteration, so the loop
+    can stop on unchanged labels at the end of the third iteration at the earliest.
+    """
+    X = _rows(X_t)
+    C0 = _rows(centroids_t, "centroids_t")
+    if X.dtype != C0.dtype:
+        raise ValueError("X_t and centroids_t must share one dtype")
+    if X.shape[1] != C0.shape[1]:
+        raise ValueError("X_t and centroids_t disagree on n_features")
+    T = _np_dtype(X)
+    w = _weights_or_none(sample_weight, use_uniform_weights)
+    state = LloydState(X, w, C0, algo)
+    if dist.active():
+        dist.check_same_across_ranks(d=state.d, k=state.k, dtype=str(X.dtype),
+                                     max_iter=int(max_iter), tol=float(tol))
+
+    n_iteration = 0
+    shift = np.inf
+    armed = False
+    strict = False
+    verbose = bool(verbose)
+    while n_iteration < max_iter and shift > tol:
+        _, changed, shift_total = state.step()
+        if verbose:
+            # the reference prints the inertia of the new assignments; here it is taken
+            # against the centroids the assignments were made with
+            total = torch.empty(1, dtype=X.dtype, device=X.device)
+            check(lib.kmb_inertia(state.dtype, ptr(X), ptr(w), ptr(state.C_new), ptr(state.labels),
+                                  None, ptr(total), state.n, state.d, state.k, ptr(state.ws),
+                                  state.ws_bytes, stream_ptr(X.device)))
+            dist.all_reduce_sum_(total)
+            print(f"Iteration {n_iteration}, inertia {float(total[0]):5.3e}")
+        n_iteration += 1
+        if n_iteration > 1:
+            if armed and changed == 0:
+                strict = True
+                break
+            armed = True
+        shift = T(shift_total)
+
+    if verbose:
+        converged_at = n_iteration - 1
+        if strict or shift == 0:
+            print(f"Converged at iteration {converged_at}: strict convergence.")
+        elif shift <= tol:
+            print(f"Converged at iteration {converged_at}: center shift {shift} within "
+                  f"tolerance {tol}.")
+
+    labels, total = state.final_labels_inertia()
+    inertia = total.cpu().numpy()[0]
+    return labels, inertia, state.C.T, n_iteration
+
+
+# ---------------------------------------------------------------------------- top-k
+def _topk_call(array_in, k, want_values, want_idx):
+    if not isinstance(array_in, torch.Tensor) or not array_in.is_cuda:
+        raise ValueError("array_in must be a CUDA tensor")
+    if array_in.dtype not in (torch.float32, torch.float64):
+        raise ValueError(
+            f"topk currently only supports dtypes in (float32, float64), but got dtype="
+            f"{array_in.dtype} .")
+    is_1d = array_in.dim() == 1
+    arr = array_in.reshape(1, -1) if is_1d else array_in
+    arr = arr.contiguous()
+    n_rows, n_cols = arr.shape
+    if n_cols < k:
+        raise ValueError(
+            "Expected k to be greater than or equal to the number of items in the search "
+            f"space, but got k={k} and {n_cols} items in the search space.")
+    dev = arr.device
+    nbytes = lib.kmb_topk_workspace_bytes(n_rows, n_cols, k)
+    ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+    vals = torch.empty((n_rows, k), dtype=arr.dtype, device=dev) if want_values else None
+    idx = torch.empty((n_rows, k), dtype=torch.int64, device=dev) if want_idx else None
+    check(lib.kmb_topk(dtype_code(arr.dtype), ptr(arr), n_rows, n_cols, k, ptr(vals), ptr(idx),
+                       ptr(ws), ws.numel(), stream_ptr(dev)), "kmb_topk")
+    if is_1d:
+        vals = vals.reshape(-1) if vals is not None else None
+        idx = idx.reshape(-1) if idx is not None else None
+    return vals, idx
+
+
+def topk_idx_1d(values, k):
+    return _topk_call(values, k, False, True)[1]
+
+
+# ----------------------------------------------------------------- data preparation
+def _device_sum(t, square):
+    dev = t.device
+    out = torch.empty(1, dtype=torch.float64, device=dev)
+    flat = t.reshape(-1)
+    ws, ws_bytes = workspace_for(dev, flat.numel(), 1, 1)
+    check(lib.kmb_sum(dtype_code(t.dtype), ptr(flat), flat.numel(), int(square), ptr(out), ptr(ws),
+                      ws_bytes, stream_ptr(dev)), "kmb_sum")
+    return out
+
+
+def _add_row_vector_(X, vec, sign):
+    check(lib.kmb_add_row_vector(dtype_code(X.dtype), ptr(X), X.shape[0], X.shape[1], ptr(vec),
+                                 float(sign), stream_ptr(X.device)), "kmb_add_row_vector")
+
+
+def prepare_data_for_lloyd(X_t, init, tol, sample_weight, copy_x):
+    """Centre the data, rescale the tolerance, test the weights for uniformity.  Same contract
+    as the reference's function (sklearn_numba_dpex/kmeans/drivers.py:436-545): returns
+    ``(X_t, X_mean | None, init, tol, sample_weight_is_uniform)``; `init` is a (d, k) tensor or
+    a non-array init spec passed through.  With ``copy_x=False`` X is centred in place (when
+    its rows are contiguous) and put back by `restore_data_after_lloyd`."""
+    X = _rows(X_t)
+    n, d = X.shape
+    T = _np_dtype(X)
+    dev = X.device
+    n_total = n
+    col = torch.empty(d, dtype=torch.float64, device=dev)
+    ws, ws_bytes = workspace_for(dev, n, d, 1)
+    check(lib.kmb_col_sums(dtype_code(X.dtype), ptr(X), n, d, ptr(col), ptr(ws), ws_bytes,
+                           stream_ptr(dev)), "kmb_col_sums")
+    if dist.active():
+        dist.all_reduce_sum_(col)
+        n_total = int(sum(dist.all_gather_object(int(n))))
+    X_mean = (col.to(X.dtype) / T(n_total)).contiguous()
+    mean_sq = float(_device_sum(X_mean, True)[0])
+    if mean_sq == 0.0:
+        X_mean = None
+    else:
+        X = X.clone() if copy_x else X
+        _add_row_vector_(X, X_mean, -1.0)
+        if isinstance(init, torch.Tensor):
+            init_rows = _rows(init, "init").clone()
+            _add_row_vector_(init_rows, X_mean, -1.0)
+            init = init_rows.T
+    variance = _device_sum(X, True)
+    dist.all_reduce_sum_(variance)
+    tol = T(T(float(variance[0])) / T(d * n_total)) * tol
+    wsum = _device_sum(sample_weight, False)
+    w0 = sample_weight[:1].to(torch.float64)
+    if dist.active():
+        dist.all_reduce_sum_(wsum)
+        dist.broadcast_(w0, 0)
+    uniform = bool(T(float(wsum[0])) == T(float(w0[0])) * n_total)
+    if dist.active():
+        w_all_equal = bool(float(sample_weight[0]) == float(w0[0])) if n else True
+        uniform = uniform and all(dist.all_gather_object(w_all_equal))
+    return X.T, X_mean, init, tol, uniform
+
+
+def restore_data_after_lloyd(X_t, best_centers_t, X_mean, copy_x):
+    """Adds the feature means back, in place (sklearn_numba_dpex/kmeans/drivers.py:548-589)."""
+    if X_mean is None:
+        return
+    C = best_centers_t.T
+    if C.is_contiguous():
+        _add_row_vector_(C, X_mean, 1.0)
+    else:
+        best_centers_t += X_mean.reshape(-1, 1)
+    if not copy_x:
+        X = X_t.T
+        if X.is_contiguous():
+            _add_row_vector_(X, X_mean, 1.0)
+        else:
+            X_t += X_mean.reshape(-1, 1)
+
+
+# ------------------------------------------------------------------- label utilities
+def _as_i32(labels):
+    if labels.dtype == torch.int32:
+        return labels.contiguous()
+    return labels.to(torch.int32).contiguous()
+
+
+def is_same_clustering(labels1, labels2, n_clusters):
+    """Equal up to a permutation of the label values
+    (sklearn_numba_dpex/kmeans/drivers.py:592-602)."""
+    l1, l2 = _as_i32(labels1), _as_i32(labels2)
+    dev = l1.device
+    mapping = torch.empty(n_clusters, dtype=torch.int32, device=dev)
+    result = torch.empty(1, dtype=torch.int32, device=dev)
+    check(lib.kmb_same_clustering(ptr(l1), ptr(l2), l1.numel(), n_clusters, ptr(mapping),
+                                  ptr(result), stream_ptr(dev)), "kmb_same_clustering")
+    if dist.active():
+        result = result.clone()
+        torch.distributed.all_reduce(result, op=torch.distributed.ReduceOp.MIN)
+    return bool(result.cpu()[0])
+
+
+def get_nb_distinct_clusters(labels, n_clusters):
+    """Number of distinct labels (sklearn_numba_dpex/kmeans/drivers.py:605-627)."""
+    lab = _as_i32(labels)
+    dev = lab.device
+    seen = torch.empty(n_clusters, dtype=torch.int32, device=dev)
+    out = torch.empty(1, dtype=torch.int32, device=dev)
+    check(lib.kmb_count_distinct(ptr(lab), lab.numel(), n_clusters, ptr(seen), ptr(out),
+                                 stream_ptr(dev)), "kmb_count_distinct")
+    if dist.active():
+        torch.distributed.all_reduce(seen, op=torch.distributed.ReduceOp.MAX)
+        return np.int32(int((seen > 0).sum().cpu()))
+    return out.cpu().numpy()[0]
+
+
+# ------------------------------------------------------------ predict / score / transform
+def get_labels_inertia(X_t, centroids_t, sample_weight, with_inertia, algo="auto"):
+    """Labels and (optionally) inertia against given centroids.  Same contract as the
+    reference (sklearn_numba_dpex/kmeans/drivers.py:630-699): inertia is a 1-element numpy
+    array, or None."""
+    X = _rows(X_t)
+    C = _rows(centroids_t, "centroids_t")
+    n, d = X.shape
+    k = C.shape[0]
+    dev = X.device
+    code = dtype_code(X.dtype)
+    h = torch.empty(k, dtype=X.dtype, device=dev)
+    labels = torch.empty(n, dtype=torch.int32, device=dev)
+    ws, ws_bytes = workspace_for(dev, n, d, k)
+    check(lib.kmb_half_l2_norm(code, ptr(C), ptr(h), k, d, stream_ptr(dev)), "kmb_half_l2_norm")
+    check(lib.kmb_assign_labels(code, _algo_code(algo), ptr(X), ptr(C), ptr(h), ptr(labels), n, d,
+                                k, ptr(ws), ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+    if not with_inertia:
+        return labels, None
+    total = torch.empty(1, dtype=X.dtype, device=dev)
+    check(lib.kmb_inertia(code, ptr(X), ptr(sample_weight), ptr(C), ptr(labels), None, ptr(total),
+                          n, d, k, ptr(ws), ws_bytes, stream_ptr(dev)), "kmb_inertia")
+    dist.all_reduce_sum_(total)
+    return labels, total.cpu().numpy()
+
+
+def get_euclidean_distances(X_t, Y_t):
+    """(n, k) euclidean distances, returned like the reference as the transposed view of a
+    (k, n) array (sklearn_numba_dpex/kmeans/drivers.py:702-732)."""
+    X = _rows(X_t)
+    Y = _rows(Y_t, "Y_t")
+    n, d = X.shape
+    k = Y.shape[0]
+    out_t = torch.empty((k, n), dtype=X.dtype, device=X.device)
+    check(lib.kmb_euclidean_distances(dtype_code(X.dtype), ptr(X), ptr(Y), ptr(out_t), n, d, k,
+                                      stream_ptr(X.device)), "kmb_euclidean_distances")
+    return out_t.T
+
+
+# ------------------------------------------------------------------------- k-means++
+def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
+    """Greedy k-means++ seeding with ``2 + int(log(k))`` trials per round.  Same contract as
+    the reference (sklearn_numba_dpex/kmeans/drivers.py:735-910): returns
+    ``(centers_t (d, k), center_indices int32 (k,))``.
+
+    The random stream is the reference's (xoroshiro128++, one state per trial, seeded from
+    `random_state`), drawn on the host ahead of the loop since each round consumes exactly
+    one value per trial.  Candidates are the first index whose inclusive prefix sum of the
+    current potentials reaches ``u * total``; the prefix is evaluated in float64 by a
+    two-level scan, where the reference runs a sequential sum in the compute dtype.
+    """
+    from ..common.random import create_xoroshiro128pp_states, get_random_raw, uniform_draws
+
+    if dist.active():
+        raise NotImplementedError("k-means++ over row shards is not implemented")
+    X = _rows(X_t)
+    n, d = X.shape
+    k = int(n_clusters)
+    dev, dt = X.device, X.dtype
+    code = dtype_code(dt)
+    T = _np_dtype(X)
+    t = 2 + int(math.log(k))
+    states = create_xoroshiro128pp_states(t, seed=random_state)
+    first = int(get_random_raw(states)[0] % np.uint64(n))
+    u_host = uniform_draws(states, k - 1, T)  # (k-1, t)
+    u = torch.from_numpy(u_host).to(dev) if k > 1 else torch.empty((0, t), dtype=dt, device=dev)
+
+    block = lib.kmb_kpp_block_rows()
+    nb = (n + block - 1) // block
+    M = [torch.empty((t, n), dtype=dt, device=dev) for _ in range(2)]
+    bsum = [torch.empty((t, nb), dtype=torch.float64, device=dev) for _ in range(2)]
+    best = torch.zeros(1, dtype=torch.int32, device=dev)
+    total = torch.empty(1, dtype=dt, device=dev)
+    cand = torch.empty(t, dtype=torch.int32, device=dev)
+    cand_rows = torch.empty((t, d), dtype=dt, device=dev)
+    pots = torch.empty(t, dtype=dt, device=dev)
+    centers = torch.empty((k, d), dtype=dt, device=dev)
+    indices = torch.full((k,), -1, dtype=torch.int32, device=dev)
+    w = sample_weight
+    s = stream_ptr(dev)
+
+    check(lib.kmb_kpp_init(code, ptr(X), ptr(w), first, ptr(M[0]), ptr(bsum[0]), ptr(centers),
+                           ptr(indices), n, d, s), "kmb_kpp_init")
+    check(lib.kmb_kpp_select(code, ptr(bsum[0]), 1, nb, None, ptr(best), ptr(total), None, None,
+                             None, None, 0, d, s), "kmb_kpp_select")
+    cur = 0
+    for c in range(1, k):
+        nxt = 1 - cur
+        check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
+                                 ptr(u[c - 1]), t, ptr(cand), n, s), "kmb_kpp_sample")
+        check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),
+              "kmb_gather_rows")
+        check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(cand_rows), ptr(M[cur]), ptr(best),
+                               ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
+        check(lib.kmb_kpp_select(code, ptr(bsum[nxt]), t, nb, ptr(pots), ptr(best), ptr(total),
+                                 ptr(cand_rows), ptr(cand), ptr(centers), ptr(indices), c, d, s),
+              "kmb_kpp_select")
+        cur = nxt
+    return centers.T, indices
