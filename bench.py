@@ -113,7 +113,7 @@ def initial_centres(cfg, X_shard, start, stop, torch, dist_mod):
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -128,11 +128,15 @@ class ClockSampler:
             self.path = fh.name
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)], stdout=fh, stderr=subprocess.DEVNULL)
+                 "-lms", "50", "-i", str(self.gpu_index)], stdout=fh, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Median SM clock and the throttle reasons seen between the two wall-clock times
+        (all samples when none fall inside, e.g. a sub-second timed region)."""
+        import datetime
+
         out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
         if self.proc is None:
             return out
@@ -141,26 +145,32 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         try:
             for line in open(self.path):
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 9:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[1]), float(parts[2]), parts[5:9]))
                 except ValueError:
                     continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                      "sw_power_cap"), parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), samples=len(sm))
+        inside = [r for r in rows if t_begin is not None and t_begin - 0.05 <= r[0] <= t_end + 0.05]
+        use = inside if inside else rows
+        reasons = set()
+        for _, _, _, flags in use:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), flags):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if use:
+            out.update(sm_mhz=float(np.median([r[1] for r in use])),
+                       sm_max_mhz=float(max(r[2] for r in use)), samples=len(use),
+                       samples_in_timed_region=len(inside))
         out["reasons"] = sorted(reasons)
         return out
 
@@ -248,12 +258,12 @@ def run_gpu_arm(args, cfg):
             tdist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        state.step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        state.step()
+    barrier()
     launches0 = state.kernel_launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -283,13 +293,15 @@ def run_gpu_arm(args, cfg):
         step_idx["i"] += 1
 
     state.launch_step = timed_launch_step
+    t_begin = time.time()
     ev0.record()
     for _ in range(args.steps):
         state.step()
     ev1.record()
     barrier()
+    t_end = time.time()
     state.launch_step = orig_launch
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     elapsed_ms = ev0.elapsed_time(ev1)
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
     launches = state.kernel_launches - launches0

@@ -89,6 +89,12 @@ int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void
                    void* acc, int n_copies, int64_t n, int d, int k, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* After a KMB_ALGO_TF32X3 step or assignment on `workspace`: copies the kernel's time-out
+ * flag to *host_flag (host memory), waits for the stream, and returns KMB_ERR_CUDA if a
+ * bounded wait inside that kernel ran out (its outputs are then invalid).  No counterpart in
+ * the reference, whose kernels have no device-side waits. */
+int kmb_lloyd_tc_error(const void* workspace, int d, int k, int* host_flag, void* stream);
+
 /* out[e] = sum over copies of acc[c][e], copies added in ascending order.
  * Replaces the private-copy summation of make_reduce_centroid_data_kernel,
  * sklearn_numba_dpex/kmeans/kernels/utils.py:130-157. */
@@ -129,10 +135,11 @@ int kmb_euclidean_distances(int dtype, const void* X, const void* Y, void* out_t
 
 /* Empty-cluster relocation on un-normalised sums: for i < n_reloc, j = empty_list[i],
  * q = far_idx[i]: sums[label_q] -= w_q x_q; sums[j] = w_q x_q; counts likewise;
- * per_sample[q] = 0 (per_sample may be NULL).  `acc` is one merged accumulator.
+ * per_sample[q] = 0 (per_sample may be NULL).  `acc` is one merged accumulator; X, w and
+ * labels hold n_rows rows, and pairs whose q or label falls outside are skipped.
  * Replaces make_relocate_empty_clusters_kernel, kmeans/kernels/utils.py:12-76. */
 int kmb_relocate_empty_clusters(int dtype, const void* X, const void* w,
-                                const uint32_t* labels, const int64_t* far_idx,
+                                const uint32_t* labels, int64_t n_rows, const int64_t* far_idx,
                                 const uint32_t* empty_list, int n_reloc, void* per_sample,
                                 void* acc, int d, int k, void* stream);
 

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "kmb_half_l2_norm": (c_int, [c_int, _P, _P, c_int, c_int, _P]),
     "kmb_lloyd_step": (c_int, [c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int64, c_int,
                                c_int, _P, c_size_t, _P]),
+    "kmb_lloyd_tc_error": (c_int, [_P, c_int, c_int, POINTER(c_int), _P]),
     "kmb_lloyd_merge_copies": (c_int, [c_int, _P, c_int, c_int64, _P, _P]),
     "kmb_lloyd_finalize": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P]),
     "kmb_assign_labels": (c_int, [c_int, c_int, _P, _P, _P, _P, c_int64, c_int, c_int, _P,
@@ -54,7 +55,7 @@ _SIGNATURES = {
     "kmb_inertia": (c_int, [c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t,
                             _P]),
     "kmb_euclidean_distances": (c_int, [c_int, _P, _P, _P, c_int64, c_int, c_int, _P]),
-    "kmb_relocate_empty_clusters": (c_int, [c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
+    "kmb_relocate_empty_clusters": (c_int, [c_int, _P, _P, _P, c_int64, _P, _P, c_int, _P, _P, c_int,
                                             c_int, _P]),
     "kmb_topk": (c_int, [c_int, _P, c_int, c_int64, c_int, _P, _P, _P, c_size_t, _P]),
     "kmb_topk_workspace_bytes": (c_size_t, [c_int, c_int64, c_int]),

@@ -30,7 +30,8 @@ size_t kmb_workspace_bytes(int64_t n, int d, int k) {
   // Fixed-order reductions use <= 4096 float64 partials per reduced quantity and at most
   // max(d, 64) quantities; the tensor-core step keeps hi/lo copies of the centroids.
   size_t partials = (size_t)4096 * sizeof(double) * (size_t)(d > 64 ? d : 64);
-  size_t centroid_split = (size_t)2 * (size_t)(k + 256) * (size_t)(d + 32) * sizeof(float) + 4096;
+  size_t centroid_split = (size_t)2 * (size_t)(k + 256) * (size_t)(d + 32) * sizeof(float) +
+                          (size_t)(k + 256) * sizeof(float) + 8192;
   size_t topk = kmb_topk_workspace_bytes(1, n, k);
   return partials + centroid_split + topk + 65536;
 }

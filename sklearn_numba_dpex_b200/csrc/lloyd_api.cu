@@ -17,6 +17,7 @@ int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
                  int64_t acc_len, int64_t n, int d, int k, bool update, void* workspace,
                  size_t workspace_bytes, cudaStream_t stream);
 int lloyd_tc_acc_copies(int d, int k);
+int lloyd_tc_error_flag_offset(void* workspace, int d, int k, size_t* offset);
 }  // namespace kmb
 
 using namespace kmb;
@@ -52,6 +53,20 @@ int kmb_lloyd_acc_copies(int dtype, int algo, int64_t n, int d, int k) {
   if (r < 0) return r;
   if (r == KMB_ALGO_TF32X3) return lloyd_tc_acc_copies(d, k);
   return lloyd_cc_privatises(dtype, d, k) ? 1 : 8;
+}
+
+int kmb_lloyd_tc_error(const void* workspace, int d, int k, int* host_flag, void* stream) {
+  KMB_REQUIRE(workspace && host_flag && d > 0 && k > 0, "kmb_lloyd_tc_error: bad arguments");
+  size_t off = 0;
+  lloyd_tc_error_flag_offset(const_cast<void*>(workspace), d, k, &off);
+  KMB_CHECK_CUDA(cudaMemcpyAsync(host_flag, (const unsigned char*)workspace + off, sizeof(int),
+                                 cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  KMB_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (*host_flag != 0) {
+    set_error("a bounded wait inside the tcgen05 Lloyd kernel ran out; its results are invalid");
+    return KMB_ERR_CUDA;
+  }
+  return KMB_OK;
 }
 
 int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void* C,

@@ -1,24 +1,616 @@
-// tcgen05 3xTF32 fused Lloyd step (placeholder until the kernel lands: reports
-// "not supported" so that KMB_ALGO_AUTO resolves to the CUDA-core kernel).
+// Fused Lloyd step on the 5th-generation tensor cores: tcgen05.mma kind::tf32 with the
+// 3xTF32 split (x = xh + xl, c = ch + cl, x.c ~ xh.ch + xh.cl + xl.ch, fp32 accumulation
+// in tensor memory), TMA-staged operand tiles, and an epilogue that reads the accumulators
+// back with tcgen05.ld, folds them into the running argmin and then adds w*x into the
+// centroid sums with 16-byte vector reductions.
+//
+// One persistent CTA per SM, 7 warps:
+//   warp 0      TMA producer of the sample tile (128 rows x d, fp32, 128B-swizzled)
+//   warp 1      TMA producer of the centroid stages (hi and lo parts, 128 centroids x 32 feats)
+//   warp 2      allocates tensor memory, issues the MMAs (one lane)
+//   warps 3..6  split the sample tile into hi/lo in shared memory, run the argmin epilogue
+//               (one sample row per thread = one TMEM lane), write labels, update sums.
+// Accumulators are double-buffered in tensor memory (2 x 128 columns), so the epilogue of
+// centroid tile j overlaps the MMAs of tile j+1.
+//
+// Every wait on an mbarrier is bounded: on time-out the CTA raises a flag in global memory,
+// all roles leave their loops, tensor memory is released and the kernel returns; the host
+// entry point then reports KMB_ERR_CUDA.
+//
+// Stands for fused_lloyd_single_step / assignment of the reference
+// (sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:149-414,
+//  kmeans/kernels/compute_labels.py:75-168) when the contraction is GEMM-sized.
+#include <cuda.h>
+
 #include "kmb_common.cuh"
 
 namespace kmb {
 
-bool lloyd_tc_supported(int, int64_t, int, int) { return false; }
-bool lloyd_tc_preferred(int, int64_t, int, int) { return false; }
-int lloyd_tc_acc_copies(int, int) { return 8; }
+constexpr int TC_BM = 128;          // samples per tile = TMEM lanes
+constexpr int TC_BN = 128;          // centroids per MMA / accumulator buffer
+constexpr int TC_KC = 32;           // features per 128-byte swizzle atom
+constexpr int TC_STAGES = 3;        // centroid stages in flight
+constexpr int TC_MAX_D = 128;       // d_pad <= 128 keeps the hi/lo sample tile in 128 KB
+constexpr int TC_THREADS = 7 * 32;
+constexpr int TC_EPI_WARP0 = 3;
+constexpr int TC_ATOM_BYTES = TC_BM * TC_KC * 4;  // 16 KB: 128 rows x 128 B
+constexpr int TC_TMEM_COLS = 2 * TC_BN;
+constexpr long long TC_TIMEOUT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
-int lloyd_tc_run(const float*, const float*, const float*, const float*, const uint32_t*,
-                 uint32_t*, float*, int, int64_t, int64_t, int, int, bool, void*, size_t,
-                 cudaStream_t) {
-  set_error("the tcgen05 step is not built into this library");
-  return KMB_ERR_UNSUPPORTED;
+struct TcSmem {
+  // all tiles 1024-byte aligned (128B swizzle atoms repeat every 1024 bytes)
+  unsigned char xhi[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
+  unsigned char xlo[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
+  unsigned char bhi[TC_STAGES][TC_ATOM_BYTES];
+  unsigned char blo[TC_STAGES][TC_ATOM_BYTES];
+  unsigned long long x_full, x_conv, x_free;
+  unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
+  unsigned long long acc_full[2], acc_empty[2];
+  unsigned int tmem_base;
+  volatile int abort_flag;
+};
+
+struct TcParams {
+  const float* X;
+  const float* w;
+  const float* h_pad;       // k_pad entries, +inf beyond k
+  const uint32_t* prev;
+  uint32_t* labels;
+  float* acc;               // n_copies x acc_len, or NULL (labels only)
+  float* dots;              // optional (n, ldd) raw dot products (test hook), or NULL
+  int* error_flag;
+  int64_t acc_len;
+  int64_t n;
+  int ldd;
+  int n_copies;
+  int d;
+  int d_pad;
+  int k;
+  int k_pad;
+};
+
+// ---------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(void* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the CTA is aborting or the time limit ran out.
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm, int* error_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm->abort_flag) return false;
+    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+      sm->abort_flag = 1;
+      atomicExch(error_flag, 1);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x),
+               "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(void* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-int lloyd_tc_matmul(const float*, const float*, float*, int64_t, int, int, void*, size_t,
-                    cudaStream_t) {
-  set_error("the tcgen05 step is not built into this library");
-  return KMB_ERR_UNSUPPORTED;
+// Shared-memory matrix descriptor of a K-major, 128B-swizzled tile whose rows are 128 bytes
+// apart and whose 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  desc |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle)
+  desc |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+  desc |= (uint64_t)1 << 46;                    // descriptor version of sm_100
+  desc |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return desc;
+}
+
+// kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = 128.
+constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+                              ((uint32_t)(TC_BM >> 4) << 24);
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// ------------------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(TC_THREADS, 1)
+lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
+                const __grid_constant__ CUtensorMap map_clo, TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  TcSmem* sm = reinterpret_cast<TcSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_kc = p.d_pad / TC_KC;
+  const int n_nt = p.k_pad / TC_BN;
+  const int64_t n_tiles = (p.n + TC_BM - 1) / TC_BM;
+  const bool update = p.acc != nullptr;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm->x_full, 1);
+    mbar_init(&sm->x_conv, 4);
+    mbar_init(&sm->x_free, 4);
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&sm->b_full[s], 1);
+      mbar_init(&sm->b_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm->acc_full[a], 1);
+      mbar_init(&sm->acc_empty[a], 4);
+    }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(&sm->tmem_base, TC_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- sample tiles
+    if (lane == 0) {
+      uint32_t t = 0;
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+        if (!mbar_wait(&sm->x_free, (t & 1) ^ 1, sm, p.error_flag)) break;
+        mbar_expect_tx(&sm->x_full, (uint32_t)n_kc * TC_ATOM_BYTES);
+        for (int kc = 0; kc < n_kc; ++kc)
+          tma_load_2d(sm->xhi[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
+        const int64_t next = tile + gridDim.x;
+        if (next < n_tiles)
+          for (int kc = 0; kc < n_kc; ++kc) tma_prefetch_2d(&map_x, kc * TC_KC, (int)(next * TC_BM));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- centroid stages
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        for (int nt = 0; nt < n_nt && ok; ++nt) {
+          for (int kc = 0; kc < n_kc; ++kc, ++it) {
+            const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
+            if (!mbar_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&sm->b_full[s], 2 * TC_ATOM_BYTES);
+            tma_load_2d(sm->bhi[s], &map_chi, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
+            tma_load_2d(sm->blo[s], &map_clo, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------------ MMA
+    if (lane == 0) {
+      uint32_t t = 0, it = 0, g = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+        if (!mbar_wait(&sm->x_conv, t & 1, sm, p.error_flag)) break;
+        tc_fence_after();
+        for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+          const uint32_t ab = g & 1, ug = g >> 1;
+          if (!mbar_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + ab * TC_BN;
+          for (int kc = 0; kc < n_kc; ++kc, ++it) {
+            const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
+            if (!mbar_wait(&sm->b_full[s], u & 1, sm, p.error_flag)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t a_hi = make_sdesc(smem_u32(sm->xhi[kc]));
+            const uint64_t a_lo = make_sdesc(smem_u32(sm->xlo[kc]));
+            const uint64_t b_hi = make_sdesc(smem_u32(sm->bhi[s]));
+            const uint64_t b_lo = make_sdesc(smem_u32(sm->blo[s]));
+#pragma unroll
+            for (int ks = 0; ks < TC_KC / 8; ++ks) {
+              const uint64_t adv = (uint64_t)(ks * 32 >> 4);  // 8 tf32 = 32 bytes per k-step
+              umma_tf32(d_tmem, a_lo + adv, b_hi + adv, TC_IDESC, (kc | ks) != 0);
+              umma_tf32(d_tmem, a_hi + adv, b_lo + adv, TC_IDESC, 1);
+              umma_tf32(d_tmem, a_hi + adv, b_hi + adv, TC_IDESC, 1);
+            }
+            umma_commit(&sm->b_empty[s]);
+          }
+          if (ok) umma_commit(&sm->acc_full[ab]);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------- split, argmin epilogue, update
+    const int ew = warp - TC_EPI_WARP0;            // 0..3
+    const int et = ew * 32 + lane;                 // 0..127
+    const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
+    const int row = lane_base + lane;              // sample row within the tile
+    float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
+    uint32_t t = 0, g = 0, changed = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+      const int64_t m0 = tile * TC_BM;
+      // ---- hi/lo split of the sample tile, in place (any element-wise map keeps the swizzle)
+      // wait results are made warp-uniform: the shuffles below need all 32 lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full, t & 1, sm, p.error_flag))) break;
+      {
+        float4* hi4 = reinterpret_cast<float4*>(sm->xhi[0]);
+        float4* lo4 = reinterpret_cast<float4*>(sm->xlo[0]);
+        const int n_vec = n_kc * (TC_ATOM_BYTES / 16);
+        for (int e = et; e < n_vec; e += 128) {
+          const float4 x = hi4[e];
+          float4 hh, ll;
+          hh.x = tf32_round(x.x); ll.x = x.x - hh.x;
+          hh.y = tf32_round(x.y); ll.y = x.y - hh.y;
+          hh.z = tf32_round(x.z); ll.z = x.z - hh.z;
+          hh.w = tf32_round(x.w); ll.w = x.w - hh.w;
+          hi4[e] = hh;
+          lo4[e] = ll;
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->x_conv);
+
+      float best = __int_as_float(0x7f800000);
+      uint32_t bi = 0;
+      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+        const uint32_t ab = g & 1, ug = g >> 1;
+        const int cn = nt * TC_BN;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + ab * TC_BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c0, v);
+          tmem_ld_wait();
+          if (p.dots != nullptr && m0 + row < p.n) {
+            float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(v[j]);
+          }
+          // same address in every lane: one broadcast load per four centroids
+          const float4* h4 = reinterpret_cast<const float4*>(p.h_pad + cn + c0);
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 hv = __ldg(h4 + j4);
+            const float q0 = hv.x - __uint_as_float(v[4 * j4 + 0]);
+            const float q1 = hv.y - __uint_as_float(v[4 * j4 + 1]);
+            const float q2 = hv.z - __uint_as_float(v[4 * j4 + 2]);
+            const float q3 = hv.w - __uint_as_float(v[4 * j4 + 3]);
+            const uint32_t jb = (uint32_t)(cn + c0 + 4 * j4);
+            if (q0 < best) { best = q0; bi = jb; }
+            if (q1 < best) { best = q1; bi = jb + 1; }
+            if (q2 < best) { best = q2; bi = jb + 2; }
+            if (q3 < best) { best = q3; bi = jb + 3; }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+      }
+      if (!ok) break;
+
+      // ---- labels, change count, centroid update (one warp adds one 512-byte row at a time)
+      const bool valid = m0 + row < p.n;
+      float wi = 0.f;
+      if (valid) {
+        p.labels[m0 + row] = bi;
+        if (update) {
+          changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
+          wi = p.w ? p.w[m0 + row] : 1.f;
+          atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
+        }
+      }
+      if (update) {
+        const int kc = lane >> 3, chunk = lane & 7;      // 16-byte chunk `chunk` of atom `kc`
+        const bool col_ok = (lane * 4) < p.d;
+        for (int r = 0; r < 32; ++r) {
+          const uint32_t lab = __shfl_sync(0xffffffffu, bi, r);
+          const float wr = __shfl_sync(0xffffffffu, wi, r);
+          const int rr = lane_base + r;
+          const bool row_ok = __shfl_sync(0xffffffffu, (int)valid, r) != 0;
+          if (row_ok && col_ok) {
+            const int off = rr * 128 + ((chunk ^ (rr & 7)) << 4);
+            const float4 xh = *reinterpret_cast<const float4*>(sm->xhi[kc] + off);
+            const float4 xl = *reinterpret_cast<const float4*>(sm->xlo[kc] + off);
+            float4 v;
+            v.x = (xh.x + xl.x) * wr;
+            v.y = (xh.y + xl.y) * wr;
+            v.z = (xh.z + xl.z) * wr;
+            v.w = (xh.w + xl.w) * wr;
+            atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + lane * 4), v);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->x_free);
+    }
+    if (update) {
+      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
+      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TC_TMEM_COLS);
+  }
+}
+
+// Centroids -> zero-padded hi / lo parts (both rounded to tf32) and +inf-padded half norms.
+__global__ void tc_split_centroids_kernel(const float* __restrict__ C, const float* __restrict__ h,
+                                          float* __restrict__ chi, float* __restrict__ clo,
+                                          float* __restrict__ h_pad, int k, int d, int k_pad,
+                                          int d_pad) {
+  const int64_t total = (int64_t)k_pad * d_pad;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(e / d_pad), f = (int)(e % d_pad);
+    float hi = 0.f, lo = 0.f;
+    if (j < k && f < d) {
+      const float c = C[(int64_t)j * d + f];
+      hi = tf32_round(c);
+      lo = tf32_round(c - hi);
+    }
+    chi[e] = hi;
+    clo[e] = lo;
+    if (f == 0) h_pad[j] = (j < k && h != nullptr) ? h[j] : (j < k ? 0.f : __int_as_float(0x7f800000));
+  }
+}
+
+// ------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// (rows, cols) fp32 row-major tensor with row stride ld (elements); box = 32 cols x 128 rows.
+static int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int64_t ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return KMB_ERR_CUDA;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)TC_BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%d ld=%lld)", (int)r,
+              (long long)rows, cols, (long long)ld);
+    return KMB_ERR_CUDA;
+  }
+  return KMB_OK;
+}
+
+static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+bool lloyd_tc_supported(int dtype, int64_t n, int d, int k) {
+  return dtype == KMB_F32 && n >= 1 && n < (1ll << 31) - TC_BM && d >= 4 && d % 4 == 0 &&
+         d <= TC_MAX_D && k >= 1 && k <= 65536;
+}
+
+bool lloyd_tc_preferred(int dtype, int64_t n, int d, int k) {
+  // GEMM-sized contractions only: small d or k leave most of every MMA tile as padding.
+  return lloyd_tc_supported(dtype, n, d, k) && d >= 32 && k >= 128 && n >= 4096;
+}
+
+int lloyd_tc_acc_copies(int, int) { return 16; }
+
+struct TcWorkspace {
+  float* chi;
+  float* clo;
+  float* h_pad;
+  int* error_flag;
+  size_t bytes;
+};
+
+static TcWorkspace carve(void* workspace, int k_pad, int d_pad) {
+  TcWorkspace w;
+  unsigned char* p = (unsigned char*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
+  const size_t mat = ((size_t)k_pad * d_pad * sizeof(float) + 255) / 256 * 256;
+  w.chi = (float*)p;
+  w.clo = (float*)(p + mat);
+  w.h_pad = (float*)(p + 2 * mat);
+  const size_t hb = ((size_t)k_pad * sizeof(float) + 255) / 256 * 256;
+  w.error_flag = (int*)(p + 2 * mat + hb);
+  w.bytes = (size_t)(p - (unsigned char*)workspace) + 2 * mat + hb + 256;
+  return w;
+}
+
+static int tc_launch(const float* X, const float* w, const float* C, const float* h,
+                     const uint32_t* prev, uint32_t* labels, float* acc, int n_copies,
+                     int64_t acc_len, float* dots, int ldd, int64_t n, int d, int k, void* workspace,
+                     size_t workspace_bytes, cudaStream_t stream) {
+  KMB_REQUIRE(lloyd_tc_supported(KMB_F32, n, d, k), "tcgen05 step: unsupported shape n=%lld d=%d k=%d",
+              (long long)n, d, k);
+  KMB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)C & 15) == 0,
+              "tcgen05 step: X and C must be 16-byte aligned");
+  KMB_REQUIRE(acc == nullptr || ((uintptr_t)acc & 15) == 0, "tcgen05 step: acc must be 16-byte aligned");
+  const int d_pad = round_up(d, TC_KC), k_pad = round_up(k, TC_BN);
+  KMB_REQUIRE(workspace != nullptr, "tcgen05 step: workspace is NULL");
+  TcWorkspace ws = carve(workspace, k_pad, d_pad);
+  if (ws.bytes > workspace_bytes) {
+    set_error("tcgen05 step: workspace of %zu bytes needed, %zu given", ws.bytes, workspace_bytes);
+    return KMB_ERR_WORKSPACE;
+  }
+  KMB_CHECK_CUDA(cudaMemsetAsync(ws.error_flag, 0, sizeof(int), stream));
+  {
+    const int64_t total = (int64_t)k_pad * d_pad;
+    int grid = (int)ceil_div(total, 256);
+    if (grid > 1184) grid = 1184;
+    tc_split_centroids_kernel<<<grid, 256, 0, stream>>>(C, h, ws.chi, ws.clo, ws.h_pad, k, d, k_pad,
+                                                        d_pad);
+    KMB_CHECK_LAUNCH();
+  }
+  CUtensorMap map_x, map_chi, map_clo;
+  int rc;
+  if ((rc = make_map(&map_x, X, n, d, d)) != KMB_OK) return rc;
+  if ((rc = make_map(&map_chi, ws.chi, k_pad, d_pad, d_pad)) != KMB_OK) return rc;
+  if ((rc = make_map(&map_clo, ws.clo, k_pad, d_pad, d_pad)) != KMB_OK) return rc;
+
+  TcParams p;
+  p.X = X; p.w = w; p.h_pad = ws.h_pad; p.prev = prev; p.labels = labels; p.acc = acc;
+  p.dots = dots; p.error_flag = ws.error_flag; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
+  p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
+
+  const size_t smem = sizeof(TcSmem) + 1024;
+  KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+  const int64_t n_tiles = ceil_div(n, TC_BM);
+  int64_t grid = sm_count();
+  if (grid > n_tiles) grid = n_tiles;
+  lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  KMB_CHECK_LAUNCH();
+  return KMB_OK;
+}
+
+int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
+                 const uint32_t* prev, uint32_t* labels, float* acc, int n_copies, int64_t acc_len,
+                 int64_t n, int d, int k, bool update, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream) {
+  return tc_launch(X, w, C, h, prev, labels, update ? acc : nullptr, n_copies, acc_len, nullptr, 0, n,
+                   d, k, workspace, workspace_bytes, stream);
+}
+
+// out[i, j] = X[i, :] . Y[j, :] with the 3xTF32 pipeline; labels go to scratch in the workspace.
+int lloyd_tc_matmul(const float* X, const float* Y, float* out, int64_t m, int n, int kdim,
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const int d_pad = round_up(kdim, TC_KC), k_pad = round_up(n, TC_BN);
+  TcWorkspace ws = carve(workspace, k_pad, d_pad);
+  const size_t lab_bytes = ((size_t)m * sizeof(uint32_t) + 255) / 256 * 256;
+  if (workspace == nullptr || ws.bytes + lab_bytes > workspace_bytes) {
+    set_error("kmb_matmul_nt: workspace of %zu bytes needed, %zu given", ws.bytes + lab_bytes,
+              workspace_bytes);
+    return KMB_ERR_WORKSPACE;
+  }
+  uint32_t* labels = (uint32_t*)((unsigned char*)workspace + ws.bytes);
+  return tc_launch(X, nullptr, Y, nullptr, nullptr, labels, nullptr, 1, 0, out, n, m, kdim, n,
+                   workspace, workspace_bytes, stream);
+}
+
+// Non-zero when a bounded wait inside the last tcgen05 step on this workspace ran out.
+int lloyd_tc_error_flag_offset(void* workspace, int d, int k, size_t* offset) {
+  const int d_pad = round_up(d, TC_KC), k_pad = round_up(k, TC_BN);
+  TcWorkspace ws = carve(workspace, k_pad, d_pad);
+  *offset = (size_t)((unsigned char*)ws.error_flag - (unsigned char*)workspace);
+  return KMB_OK;
 }
 
 }  // namespace kmb

@@ -157,11 +157,13 @@ __global__ void relocate_kernel(const T* __restrict__ X, const T* __restrict__ w
                                 const uint32_t* __restrict__ labels,
                                 const int64_t* __restrict__ far_idx,
                                 const uint32_t* __restrict__ empty_list, T* __restrict__ per_sample,
-                                T* __restrict__ acc, int d, int k) {
+                                T* __restrict__ acc, int d, int k, int64_t n_rows) {
   const int r = blockIdx.x;
   const uint32_t j = empty_list[r];
   const int64_t q = far_idx[r];
+  if (q < 0 || q >= n_rows || j >= (uint32_t)k) return;
   const uint32_t donor = labels[q];
+  if (donor >= (uint32_t)k) return;
   const T wq = w ? w[q] : T(1);
   for (int f = threadIdx.x; f < d; f += blockDim.x) {
     const T addend = X[q * (int64_t)d + f] * wq;
@@ -350,14 +352,14 @@ int kmb_add_row_vector(int dtype, void* X, int64_t n, int d, const void* vec, do
 }
 
 int kmb_relocate_empty_clusters(int dtype, const void* X, const void* w, const uint32_t* labels,
-                                const int64_t* far_idx, const uint32_t* empty_list, int n_reloc,
+                                int64_t n_rows, const int64_t* far_idx, const uint32_t* empty_list, int n_reloc,
                                 void* per_sample, void* acc, int d, int k, void* stream) {
   KMB_REQUIRE(X && labels && far_idx && empty_list && acc, "kmb_relocate_empty_clusters: NULL argument");
-  KMB_REQUIRE(n_reloc >= 0 && n_reloc <= k && d > 0, "kmb_relocate_empty_clusters: bad sizes");
+  KMB_REQUIRE(n_reloc >= 0 && n_reloc <= k && d > 0 && n_rows >= 0, "kmb_relocate_empty_clusters: bad sizes");
   if (n_reloc == 0) return KMB_OK;
   KMB_DISPATCH_DTYPE(dtype, {
     relocate_kernel<T><<<n_reloc, 128, 0, (cudaStream_t)stream>>>(
-        (const T*)X, (const T*)w, labels, far_idx, empty_list, (T*)per_sample, (T*)acc, d, k);
+        (const T*)X, (const T*)w, labels, far_idx, empty_list, (T*)per_sample, (T*)acc, d, k, n_rows);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;

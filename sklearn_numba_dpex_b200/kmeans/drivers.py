@@ -9,6 +9,7 @@ passes) costs nothing; a C-contiguous ``X_t`` is transposed into a new buffer on
 Every O(n) operation is a kmb200 kernel called through the C ABI; torch is used for
 memory, streams and the collectives.
 """
+import ctypes
 import math
 
 import numpy as np
@@ -139,7 +140,7 @@ class LloydState:
         else:
             X_rows, w_rows, lab_rows = self.X, self.w, self.labels_new
         check(lib.kmb_relocate_empty_clusters(self.dtype, ptr(X_rows), ptr(w_rows), ptr(lab_rows),
-                                              ptr(far), ptr(self.empty_list),
+                                              X_rows.shape[0], ptr(far), ptr(self.empty_list),
                                               min(n_empty, int(far.numel())), None,
                                               ptr(self.packed), self.d, self.k, stream_ptr(dev)),
               "kmb_relocate_empty_clusters")
@@ -170,7 +171,16 @@ class LloydState:
                               self.ws_bytes, stream_ptr(dev)), "kmb_inertia")
         self.kernel_launches += 3
         dist.all_reduce_sum_(total)
+        self.check_device_waits()
         return self.labels, total
+
+    def check_device_waits(self):
+        """Raises if a bounded wait inside the tensor-core kernel ran out on this workspace."""
+        if self.algo != ALGO_NAMES["tf32x3"]:
+            return
+        flag = ctypes.c_int(0)
+        check(lib.kmb_lloyd_tc_error(ptr(self.ws), self.d, self.k, ctypes.byref(flag),
+                                     stream_ptr(self.X.device)), "kmb_lloyd_tc_error")
 
 
 def _gather_relocation_candidates(state, far_local, n_empty):

