@@ -67,12 +67,19 @@ def all_reduce_sum_(t):
 
 
 def all_gather_cat(t):
-    """Concatenation over ranks along dim 0 of equally shaped tensors."""
+    """Concatenation over ranks along dim 0; the ranks' leading dimensions may differ
+    (shorter pieces are padded for the collective and trimmed afterwards)."""
     if not active():
         return t
-    out = [torch.empty_like(t) for _ in range(world_size())]
-    tdist.all_gather(out, t.contiguous(), group=_STATE["group"])
-    return torch.cat(out, dim=0)
+    lengths = all_gather_object(int(t.shape[0]))
+    longest = max(lengths)
+    padded = t.contiguous()
+    if t.shape[0] < longest:
+        pad = torch.zeros((longest - t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        padded = torch.cat([padded, pad], dim=0)
+    out = [torch.empty_like(padded) for _ in range(world_size())]
+    tdist.all_gather(out, padded, group=_STATE["group"])
+    return torch.cat([piece[:length] for piece, length in zip(out, lengths)], dim=0)
 
 
 def all_gather_object(obj):
