@@ -153,6 +153,23 @@ int kmb_topk(int dtype, const void* values, int n_rows, int64_t n_cols, int k,
              void* stream);
 size_t kmb_topk_workspace_bytes(int n_rows, int64_t n_cols, int k);
 
+/* kmb_topk for callers that can hand over no scratch memory: int64 indices of the k largest
+ * of ONE row of n_cols values, same order as kmb_topk.  Some hosts of this library cannot
+ * allocate device memory at the point where they need a top-k: a process that gave the whole
+ * GPU to its own arena at start-up has nothing left for cudaMalloc, and a latency-critical
+ * loop cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply.  For them the
+ * scratch (radix histograms, select state, gather list) is a 48 KB array built into the
+ * library image; it exists once on every GPU that loads the library and stays until the
+ * process ends.  Limits: one row, k <= 4096 (larger k is rejected with KMB_ERR_INVALID; use
+ * kmb_topk).  The call allocates and frees nothing.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress, with that device current) and should be
+ * made before any stream capture begins; later calls only launch kernels.  All calls on a
+ * device share the one array: each call clears the parts that must start at zero, but two
+ * calls whose kernels overlap on the GPU (different streams, or different host threads) race
+ * on it and must be serialised by the caller.  It has no counterpart in the reference. */
+int kmb_topk_idx_static(int dtype, const void* values, int64_t n_cols, int k, int64_t* out_idx,
+                        void* stream);
+
 /* ---- k-means++ (kmeans/drivers.py:735-910) ---------------------------------------- */
 /* Rows per partial-sum block used by the k-means++ kernels. */
 int kmb_kpp_block_rows(void);

@@ -59,6 +59,7 @@ _SIGNATURES = {
                                             c_int, _P]),
     "kmb_topk": (c_int, [c_int, _P, c_int, c_int64, c_int, _P, _P, _P, c_size_t, _P]),
     "kmb_topk_workspace_bytes": (c_size_t, [c_int, c_int64, c_int]),
+    "kmb_topk_idx_static": (c_int, [c_int, _P, c_int64, c_int, _P, _P]),
     "kmb_kpp_block_rows": (c_int, []),
     "kmb_kpp_init": (c_int, [c_int, _P, _P, c_int64, _P, _P, _P, _P, c_int64, c_int, _P]),
     "kmb_kpp_sample": (c_int, [c_int, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P]),

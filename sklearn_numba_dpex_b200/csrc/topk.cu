@@ -6,6 +6,8 @@
 // key order.  Stands for topk / topk_idx of sklearn_numba_dpex/common/topk.py:112-270
 // (histogram kernel :621-771, threshold search :1003-1093, gather :1143-1365), which leave
 // the order of the output and the choice among ties undefined.
+#include <mutex>
+
 #include "kmb_common.cuh"
 
 namespace kmb {
@@ -178,6 +180,31 @@ int topk_run(const T* values, int n_rows, int64_t n_cols, int k, T* out_values, 
   return KMB_OK;
 }
 
+// ---- scratch for kmb_topk_idx_static: lives in the library image, one instance per GPU that
+// loads the library, until the process exits.  48 KB covers one row and k <= 4096.
+constexpr int TK_STATIC_MAX_K = 4096;
+constexpr size_t TK_STATIC_BYTES = 48 * 1024;
+static __device__ __align__(256) unsigned char g_topk_static_scratch[TK_STATIC_BYTES];
+
+// In host code the symbol above is only a handle; the device address has to be asked for,
+// once per device, with that device current.
+static int topk_static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  KMB_CHECK_CUDA(cudaGetDevice(&dev));
+  KMB_REQUIRE(dev >= 0 && dev < 64, "kmb_topk_idx_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    KMB_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_topk_static_scratch));
+    KMB_REQUIRE(ptr != nullptr, "kmb_topk_idx_static: the scratch symbol has no device address");
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return KMB_OK;
+}
+
 }  // namespace kmb
 
 using namespace kmb;
@@ -214,6 +241,37 @@ int kmb_topk(int dtype, const void* values, int n_rows, int64_t n_cols, int k, v
   KMB_REQUIRE(((uintptr_t)workspace & 15) == 0, "kmb_topk: workspace must be 16-byte aligned");
   KMB_DISPATCH_DTYPE(dtype, {
     return topk_run<T>((const T*)values, n_rows, n_cols, k, (T*)out_values, out_idx, workspace,
+                       (cudaStream_t)stream);
+  });
+}
+
+int kmb_topk_idx_static(int dtype, const void* values, int64_t n_cols, int k, int64_t* out_idx,
+                        void* stream) {
+  KMB_REQUIRE(values && out_idx, "kmb_topk_idx_static: NULL argument");
+  KMB_REQUIRE(k >= 1, "kmb_topk_idx_static: k must be >= 1");
+  if (k > TK_STATIC_MAX_K) {
+    set_error("kmb_topk_idx_static: k=%d is beyond the built-in scratch, which holds k <= %d; use "
+              "kmb_topk with a workspace instead", k, TK_STATIC_MAX_K);
+    return KMB_ERR_INVALID;
+  }
+  if (n_cols < k) {
+    set_error("Expected k to be greater than or equal to the number of items in the search space, "
+              "but got k=%d and %lld items in the search space.", k, (long long)n_cols);
+    return KMB_ERR_INVALID;
+  }
+  KMB_REQUIRE(n_cols < (1ll << 32), "kmb_topk_idx_static: n_cols must be below 2^32");
+  if (kmb_topk_workspace_bytes(1, n_cols, k) > TK_STATIC_BYTES) {
+    set_error("kmb_topk_idx_static: built-in scratch of %zu bytes is too small for k=%d",
+              TK_STATIC_BYTES, k);
+    return KMB_ERR_INVALID;
+  }
+  void* scratch = nullptr;
+  const int rc = topk_static_scratch_ptr(&scratch);
+  if (rc != KMB_OK) return rc;
+  // topk_run begins by clearing the histograms, the prefix state and the gather cursor, so
+  // whatever the previous call left in the scratch does not matter.
+  KMB_DISPATCH_DTYPE(dtype, {
+    return topk_run<T>((const T*)values, 1, n_cols, k, (T*)nullptr, out_idx, scratch,
                        (cudaStream_t)stream);
   });
 }
