@@ -1,0 +1,98 @@
+"""Row-sharded Lloyd on 2 GPUs (NCCL) against the single-GPU run of the same data:
+identical labels and iteration count, centroids and inertia within fp32 tolerance, with an
+initialisation that forces an empty-cluster relocation across shards.  Skipped with fewer
+than two GPUs.  Ranks only leave between steps; NVLS is off so that a failing rank cannot
+leave multicast state behind."""
+import os
+import socket
+import traceback
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _make_data():
+    rng = np.random.default_rng(21)
+    n, d, k = 40_001, 32, 150
+    centers = rng.uniform(-10, 10, size=(k, d))
+    X = (centers[rng.integers(0, k, n)] + rng.standard_normal((n, d))).astype(np.float32)
+    init = X[rng.choice(n, k, replace=False)].copy()
+    init[7] = init[3]            # duplicate centre: cluster 7 starts empty -> relocation
+    init[100] = 1e3              # far away: empty as well
+    w = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    return X, init, w
+
+
+def _rank_main(rank, world, port, queue):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as tdist
+
+        from sklearn_numba_dpex_b200 import dist as kdist
+        from sklearn_numba_dpex_b200.kmeans.drivers import (get_labels_inertia, lloyd,
+                                                            prepare_data_for_lloyd)
+
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        X, init, w = _make_data()
+        single = None
+        if rank == 0:
+            Xd, wd, Cd = (torch.as_tensor(a).to(dev) for a in (X, w, init))
+            X_t, mean, init_t, tol, uni = prepare_data_for_lloyd(Xd.T, Cd.T, 1e-4, wd, True)
+            labels, inertia, C_t, n_iter = lloyd(X_t, wd, init_t, uni, 6, False, 0.0)
+            single = (labels.cpu().numpy(), float(inertia), C_t.T.cpu().numpy(), n_iter,
+                      mean.cpu().numpy(), float(tol))
+        tdist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        kdist.enable()
+        start, stop = kdist.shard_bounds(X.shape[0], rank, world)
+        Xs = torch.as_tensor(X[start:stop]).to(dev)
+        ws = torch.as_tensor(w[start:stop]).to(dev)
+        Cd = torch.as_tensor(init).to(dev)
+        X_t, mean, init_t, tol, uni = prepare_data_for_lloyd(Xs.T, Cd.T, 1e-4, ws, True)
+        labels, inertia, C_t, n_iter = lloyd(X_t, ws, init_t, uni, 6, False, 0.0)
+        all_labels = kdist.all_gather_cat(labels.to(torch.int64)).cpu().numpy()
+        _, score = get_labels_inertia(X_t, C_t, ws, True)
+        out = None
+        if rank == 0:
+            s_labels, s_inertia, s_C, s_iter, s_mean, s_tol = single
+            np.testing.assert_allclose(mean.cpu().numpy(), s_mean, rtol=1e-5, atol=1e-6)
+            np.testing.assert_allclose(float(tol), s_tol, rtol=1e-5)
+            assert n_iter == s_iter
+            mism = int((all_labels != s_labels).sum())
+            assert mism <= 2, f"{mism} labels differ between 1 and 2 GPUs"
+            np.testing.assert_allclose(C_t.T.cpu().numpy(), s_C, rtol=1e-4, atol=1e-4)
+            np.testing.assert_allclose(float(inertia), s_inertia, rtol=1e-5)
+            np.testing.assert_allclose(float(score[0]), s_inertia, rtol=1e-5)
+            out = (n_iter, mism)
+        tdist.barrier()
+        torch.cuda.synchronize()
+        queue.put((rank, "ok", out))
+        tdist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        queue.put((rank, "error", traceback.format_exc()))
+
+
+def test_two_gpu_lloyd_equals_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(queue.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    assert [r[1] for r in results] == ["ok", "ok"], results
