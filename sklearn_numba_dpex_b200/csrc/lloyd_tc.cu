@@ -21,6 +21,7 @@
 // (sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:149-414,
 //  kmeans/kernels/compute_labels.py:75-168) when the contraction is GEMM-sized.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "kmb_common.cuh"
 
@@ -67,6 +68,7 @@ struct TcParams {
   int d_pad;
   int k;
   int k_pad;
+  int debug;                // diagnostic bits (timing experiments only, results invalid)
 };
 
 // ---------------------------------------------------------------------------- PTX
@@ -177,6 +179,48 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+      "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+      "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// A operand read from tensor memory (lane = row, one 32-bit column per tf32 element).
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Round-to-nearest (ties away) to the 10-bit tf32 mantissa with integer ops only: the split
+// of a whole sample tile then runs on the ALU instead of the conversion unit.
+__device__ __forceinline__ float tf32_round_alu(float x) {
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
+
+// One lane of a converged warp (warp-uniform predicate).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // Shared-memory matrix descriptor of a K-major, 128B-swizzled tile whose rows are 128 bytes
@@ -437,6 +481,296 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   }
 }
 
+// ------------------------------------------------ variant with the sample tile in TMEM
+// Same roles as lloyd_tc_kernel, but the hi/lo parts of the sample tile live in tensor
+// memory (A operand read from TMEM): shared memory only stages the raw fp32 tile, which is
+// free again as soon as it has been split, so the next tile's TMA overlaps this tile's MMAs
+// and five centroid stages (160 KB) are in flight instead of three.
+constexpr int TS_STAGES = 5;
+constexpr int TS_A_HI_COL = 0, TS_A_LO_COL = 128, TS_ACC_COL = 256, TS_TMEM_COLS = 512;
+
+struct TsSmem {
+  unsigned char xstage[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
+  unsigned char bhi[TS_STAGES][TC_ATOM_BYTES];
+  unsigned char blo[TS_STAGES][TC_ATOM_BYTES];
+  unsigned long long x_full, x_conv, x_stage_free;
+  unsigned long long b_full[TS_STAGES], b_empty[TS_STAGES];
+  unsigned long long acc_full[2], acc_empty[2];
+  unsigned int tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, int* error_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm->abort_flag) return false;
+    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+      sm->abort_flag = 1;
+      atomicExch(error_flag, 1);
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
+                   const __grid_constant__ CUtensorMap map_clo, TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  TsSmem* sm = reinterpret_cast<TsSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_kc = p.d_pad / TC_KC;
+  const int n_nt = p.k_pad / TC_BN;
+  const int64_t n_tiles = (p.n + TC_BM - 1) / TC_BM;
+  const bool update = p.acc != nullptr;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm->x_full, 1);
+    mbar_init(&sm->x_conv, 4);
+    mbar_init(&sm->x_stage_free, 4);
+    for (int s = 0; s < TS_STAGES; ++s) {
+      mbar_init(&sm->b_full[s], 1);
+      mbar_init(&sm->b_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm->acc_full[a], 1);
+      mbar_init(&sm->acc_empty[a], 4);
+    }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(&sm->tmem_base, TS_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t t = 0;
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+        if (!ts_wait(&sm->x_stage_free, (t & 1) ^ 1, sm, p.error_flag)) break;
+        mbar_expect_tx(&sm->x_full, (uint32_t)n_kc * TC_ATOM_BYTES);
+        for (int kc = 0; kc < n_kc; ++kc)
+          tma_load_2d(sm->xstage[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        for (int nt = 0; nt < n_nt && ok; ++nt) {
+          for (int kc = 0; kc < n_kc; ++kc, ++it) {
+            const uint32_t s = it % TS_STAGES, u = it / TS_STAGES;
+            if (!ts_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&sm->b_full[s], 2 * TC_ATOM_BYTES);
+            tma_load_2d(sm->bhi[s], &map_chi, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
+            tma_load_2d(sm->blo[s], &map_clo, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // The whole warp walks the loop so that every address and descriptor below is
+    // warp-uniform (uniform datapath); one elected lane issues the tensor-core work.
+    uint32_t t = 0, it = 0, g = 0;
+    bool ok = true;
+    const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
+    const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_conv, t & 1, sm, p.error_flag))) break;
+      tc_fence_after();
+      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+        const uint32_t ab = g & 1, ug = g >> 1;
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + TS_ACC_COL + ab * TC_BN;
+        for (int kc = 0; kc < n_kc; ++kc, ++it) {
+          const uint32_t s = it % TS_STAGES, u = it / TS_STAGES;
+          if (!__all_sync(0xffffffffu, ts_wait(&sm->b_full[s], u & 1, sm, p.error_flag))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          const uint32_t a_hi = tmem_base + TS_A_HI_COL + kc * TC_KC;
+          const uint32_t a_lo = tmem_base + TS_A_LO_COL + kc * TC_KC;
+          if (elect_one()) {
+#pragma unroll
+            for (int ks = 0; ks < TC_KC / 8; ++ks) {
+              const uint64_t adv = (uint64_t)(ks * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units
+              umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, (kc | ks) != 0);
+              umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
+              umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
+            }
+            umma_commit(&sm->b_empty[s]);
+            if (kc == n_kc - 1) umma_commit(&sm->acc_full[ab]);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    const int lane_base = (warp & 3) * 32;
+    const int row = lane_base + lane;
+    float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
+    uint32_t t = 0, g = 0, changed = 0;
+    bool ok = true;
+
+    // Splits the staged tile (row `row`, 128B-swizzled atoms) into TMEM: hi -> columns
+    // [0, d_pad), lo -> [128, 128 + d_pad) of this thread's lane.  Returns false on time-out.
+    auto convert_tile = [&](uint32_t tt) -> bool {
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_full, tt & 1, sm, p.error_flag))) return false;
+      for (int kc = 0; kc < n_kc; ++kc) {
+        uint32_t hi[32], lo[32];
+        const unsigned char* rowp = sm->xstage[kc] + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+          const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
+          const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
+          hi[4 * c + 0] = __float_as_uint(h0); lo[4 * c + 0] = __float_as_uint(x.x - h0);
+          hi[4 * c + 1] = __float_as_uint(h1); lo[4 * c + 1] = __float_as_uint(x.y - h1);
+          hi[4 * c + 2] = __float_as_uint(h2); lo[4 * c + 2] = __float_as_uint(x.z - h2);
+          hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(x.w - h3);
+        }
+        const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + kc * TC_KC;
+        tmem_st32(lane_addr + TS_A_HI_COL, hi);
+        tmem_st32(lane_addr + TS_A_LO_COL, lo);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sm->x_conv);
+        mbar_arrive(&sm->x_stage_free);
+      }
+      return true;
+    };
+
+    if ((int64_t)blockIdx.x < n_tiles) ok = convert_tile(0);
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+      const int64_t m0 = tile * TC_BM;
+      const bool has_next = tile + gridDim.x < n_tiles;
+      float best = __int_as_float(0x7f800000);
+      uint32_t bi = 0;
+      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+        const uint32_t ab = g & 1, ug = g >> 1;
+        const int cn = nt * TC_BN;
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // The last accumulator of a tile completing means every MMA of the tile has read its
+        // A operand: split the next tile into TMEM first, so the MMA warp can go on while
+        // this tile's last epilogue and update run.
+        if (nt == n_nt - 1 && has_next) {
+          if (!convert_tile(t + 1)) {
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TS_ACC_COL + ab * TC_BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+          if (p.debug & 1) break;
+          uint32_t v[32];
+          tmem_ld32(taddr + c0, v);
+          tmem_ld_wait();
+          if (p.dots != nullptr && m0 + row < p.n) {
+            float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(v[j]);
+          }
+          const float4* h4 = reinterpret_cast<const float4*>(p.h_pad + cn + c0);
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 hv = __ldg(h4 + j4);
+            const float q0 = hv.x - __uint_as_float(v[4 * j4 + 0]);
+            const float q1 = hv.y - __uint_as_float(v[4 * j4 + 1]);
+            const float q2 = hv.z - __uint_as_float(v[4 * j4 + 2]);
+            const float q3 = hv.w - __uint_as_float(v[4 * j4 + 3]);
+            const uint32_t jb = (uint32_t)(cn + c0 + 4 * j4);
+            if (q0 < best) { best = q0; bi = jb; }
+            if (q1 < best) { best = q1; bi = jb + 1; }
+            if (q2 < best) { best = q2; bi = jb + 2; }
+            if (q3 < best) { best = q3; bi = jb + 3; }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+      }
+      if (!ok) break;
+
+      const bool valid = m0 + row < p.n;
+      float wi = 0.f;
+      if (valid) {
+        p.labels[m0 + row] = bi;
+        if (update) {
+          changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
+          wi = p.w ? p.w[m0 + row] : 1.f;
+          atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
+        }
+      }
+      if (update && !(p.debug & 2)) {
+        // the tile's rows come back from L2 (they were streamed through it moments ago):
+        // one warp adds one row (d floats, 16 bytes per lane) per instruction
+        const bool col_ok = (lane * 4) < p.d;
+        const float* xbase = p.X + (m0 + lane_base) * (int64_t)p.d + lane * 4;
+#pragma unroll 1
+        for (int r0 = 0; r0 < 32; r0 += 8) {
+          // eight rows in flight: the loads come back from L2 together, then eight reductions
+          float4 xs[8];
+          bool oks[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            oks[j] = (__shfl_sync(0xffffffffu, (int)valid, r0 + j) != 0) && col_ok;
+            xs[j] = oks[j] ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(r0 + j) * p.d))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t lab = __shfl_sync(0xffffffffu, bi, r0 + j);
+            const float wr = __shfl_sync(0xffffffffu, wi, r0 + j);
+            if (oks[j]) {
+              float4 v;
+              v.x = xs[j].x * wr; v.y = xs[j].y * wr; v.z = xs[j].z * wr; v.w = xs[j].w * wr;
+              atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + lane * 4), v);
+            }
+          }
+        }
+      }
+    }
+    if (update) {
+      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
+      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TS_TMEM_COLS);
+  }
+}
+
 // Centroids -> zero-padded hi / lo parts (both rounded to tf32) and +inf-padded half norms.
 __global__ void tc_split_centroids_kernel(const float* __restrict__ C, const float* __restrict__ h,
                                           float* __restrict__ chi, float* __restrict__ clo,
@@ -497,6 +831,17 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols,
     return KMB_ERR_CUDA;
   }
   return KMB_OK;
+}
+
+// KMB_TC_VARIANT=ss selects the kernel with both operands in shared memory; the default is the
+// kernel that keeps the sample tile in tensor memory.
+static bool tc_variant_is_ts() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* v = getenv("KMB_TC_VARIANT");
+    cached = (v != nullptr && v[0] == 's' && v[1] == 's') ? 0 : 1;
+  }
+  return cached == 1;
 }
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -569,14 +914,25 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.X = X; p.w = w; p.h_pad = ws.h_pad; p.prev = prev; p.labels = labels; p.acc = acc;
   p.dots = dots; p.error_flag = ws.error_flag; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
+  {
+    const char* dbg = getenv("KMB_TC_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
 
-  const size_t smem = sizeof(TcSmem) + 1024;
-  KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem));
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
-  lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  if (tc_variant_is_ts()) {
+    const size_t smem = sizeof(TsSmem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_ts_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    lloyd_tc_ts_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  } else {
+    const size_t smem = sizeof(TcSmem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  }
   KMB_CHECK_LAUNCH();
   return KMB_OK;
 }
