@@ -1,21 +1,32 @@
 // Fused Lloyd step on the 5th-generation tensor cores: tcgen05.mma kind::tf32 with the
-// 3xTF32 split (x = xh + xl, c = ch + cl, x.c ~ xh.ch + xh.cl + xl.ch, fp32 accumulation
-// in tensor memory), TMA-staged operand tiles, and an epilogue that reads the accumulators
-// back with tcgen05.ld, folds them into the running argmin and then adds w*x into the
-// centroid sums with 16-byte vector reductions.
+// 3xTF32 split (x = xh + xl, c = ch + cl, x.c ~ xl.ch + xh.cl + xh.ch, fp32 accumulation in
+// tensor memory), TMA-staged operand tiles, an argmin epilogue fed by tcgen05.ld, and a
+// centroid update with 16-byte vector reductions.
 //
-// One persistent CTA per SM, 7 warps:
-//   warp 0      TMA producer of the sample tile (128 rows x d, fp32, 128B-swizzled)
-//   warp 1      TMA producer of the centroid stages (hi and lo parts, 128 centroids x 32 feats)
-//   warp 2      allocates tensor memory, issues the MMAs (one lane)
-//   warps 3..6  split the sample tile into hi/lo in shared memory, run the argmin epilogue
-//               (one sample row per thread = one TMEM lane), write labels, update sums.
-// Accumulators are double-buffered in tensor memory (2 x 128 columns), so the epilogue of
-// centroid tile j overlaps the MMAs of tile j+1.
+// One persistent CTA per SM, 11 warps:
+//   warp 0       TMA producer of the raw fp32 sample tile (128 rows x d, 128B-swizzled)
+//   warp 1       TMA producer of the centroid stages (hi and lo parts, 128 centroids x 32
+//                features each, five stages = 160 KB in flight)
+//   warp 2       allocates tensor memory and issues the MMAs; the whole warp walks the loop so
+//                that descriptors stay in the uniform datapath, one elected lane issues
+//   warps 3..6   split the staged sample tile into hi / lo parts held in TENSOR MEMORY (the A
+//                operand is read from TMEM), then run the argmin epilogue: one sample row per
+//                thread = one TMEM lane, a min-tree per 32 accumulator columns
+//   warps 7..10  centroid update of the previous tile: one warp adds one 512-byte sample row
+//                per instruction (red.global.add.v4.f32) into an L2-resident accumulator copy
+// Tensor memory (512 columns): A_hi [0,128) | A_lo [128,256) | accumulator 0 [256,384) |
+// accumulator 1 [384,512).  Accumulators are double-buffered, so the epilogue of centroid
+// tile j overlaps the MMAs of tile j+1, and the next sample tile is split into TMEM as soon
+// as the last accumulator of the current tile has completed.
+//
+// CTAs walk the centroid tiles (and the feature chunks inside a tile) in rotated orders
+// that depend on blockIdx, so that the 148 SMs do not all pull the same L2 lines at the same
+// moment; the argmin stays "lowest index wins ties" by merging per-tile minima
+// lexicographically.
 //
 // Every wait on an mbarrier is bounded: on time-out the CTA raises a flag in global memory,
 // all roles leave their loops, tensor memory is released and the kernel returns; the host
-// entry point then reports KMB_ERR_CUDA.
+// reads the flag with kmb_lloyd_tc_error.
 //
 // Stands for fused_lloyd_single_step / assignment of the reference
 // (sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:149-414,
@@ -30,23 +41,26 @@ namespace kmb {
 constexpr int TC_BM = 128;          // samples per tile = TMEM lanes
 constexpr int TC_BN = 128;          // centroids per MMA / accumulator buffer
 constexpr int TC_KC = 32;           // features per 128-byte swizzle atom
-constexpr int TC_STAGES = 3;        // centroid stages in flight
-constexpr int TC_MAX_D = 128;       // d_pad <= 128 keeps the hi/lo sample tile in 128 KB
-constexpr int TC_THREADS = 7 * 32;
+constexpr int TC_STAGES = 5;        // centroid stages in flight
+constexpr int TC_MAX_D = 128;       // d_pad <= 128: hi and lo parts take 2 x 128 TMEM columns
+constexpr int TC_WARPS = 11;
+constexpr int TC_THREADS = TC_WARPS * 32;
 constexpr int TC_EPI_WARP0 = 3;
+constexpr int TC_UPD_WARP0 = 7;
 constexpr int TC_ATOM_BYTES = TC_BM * TC_KC * 4;  // 16 KB: 128 rows x 128 B
-constexpr int TC_TMEM_COLS = 2 * TC_BN;
+constexpr int TC_A_HI_COL = 0, TC_A_LO_COL = 128, TC_ACC_COL = 256, TC_TMEM_COLS = 512;
 constexpr long long TC_TIMEOUT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
 struct TcSmem {
   // all tiles 1024-byte aligned (128B swizzle atoms repeat every 1024 bytes)
-  unsigned char xhi[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
-  unsigned char xlo[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
+  unsigned char xstage[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
   unsigned char bhi[TC_STAGES][TC_ATOM_BYTES];
   unsigned char blo[TC_STAGES][TC_ATOM_BYTES];
-  unsigned long long x_full, x_conv, x_free;
+  uint32_t lab_s[2][TC_BM];       // labels of a finished tile, handed to the update warps
+  unsigned long long x_full, x_conv, x_stage_free;
   unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
   unsigned long long acc_full[2], acc_empty[2];
+  unsigned long long upd_full[2], upd_empty[2];
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -68,7 +82,6 @@ struct TcParams {
   int d_pad;
   int k;
   int k_pad;
-  int debug;                // diagnostic bits (timing experiments only, results invalid)
 };
 
 // ---------------------------------------------------------------------------- PTX
@@ -246,6 +259,46 @@ __device__ __forceinline__ float tf32_round(float x) {
 }
 
 // ------------------------------------------------------------------------- the kernel
+// (value, index) minimum of two candidates where `a` has the lower index: b wins only when it
+// is strictly smaller; a NaN never wins against a number (fminf drops it).
+#define KMB_MIN2(va, ia, vb, ib, vo, io)          \
+  {                                               \
+    const float _m = fminf(va, vb);               \
+    io = (_m == (va)) ? (ia) : (ib);              \
+    vo = _m;                                      \
+  }
+
+// Minimum of q[j] = h[j] - acc[j] over 32 consecutive centroids, lowest index on ties.
+__device__ __forceinline__ void min_tree32(const uint32_t (&v)[32], const float4* __restrict__ h4,
+                                           uint32_t base, float& out_v, uint32_t& out_i) {
+  float q[32];
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const float4 hv = __ldg(h4 + j4);  // same address in every lane: one broadcast load
+    q[4 * j4 + 0] = hv.x - __uint_as_float(v[4 * j4 + 0]);
+    q[4 * j4 + 1] = hv.y - __uint_as_float(v[4 * j4 + 1]);
+    q[4 * j4 + 2] = hv.z - __uint_as_float(v[4 * j4 + 2]);
+    q[4 * j4 + 3] = hv.w - __uint_as_float(v[4 * j4 + 3]);
+  }
+  float v16[16];
+  uint32_t i16[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) KMB_MIN2(q[2 * j], base + 2 * j, q[2 * j + 1], base + 2 * j + 1, v16[j], i16[j]);
+  float v8[8];
+  uint32_t i8[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) KMB_MIN2(v16[2 * j], i16[2 * j], v16[2 * j + 1], i16[2 * j + 1], v8[j], i8[j]);
+  float v4[4];
+  uint32_t i4[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) KMB_MIN2(v8[2 * j], i8[2 * j], v8[2 * j + 1], i8[2 * j + 1], v4[j], i4[j]);
+  float va, vb;
+  uint32_t ia, ib;
+  KMB_MIN2(v4[0], i4[0], v4[1], i4[1], va, ia);
+  KMB_MIN2(v4[2], i4[2], v4[3], i4[3], vb, ib);
+  KMB_MIN2(va, ia, vb, ib, out_v, out_i);
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1)
 lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                 const __grid_constant__ CUtensorMap map_clo, TcParams p) {
@@ -256,11 +309,14 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int n_nt = p.k_pad / TC_BN;
   const int64_t n_tiles = (p.n + TC_BM - 1) / TC_BM;
   const bool update = p.acc != nullptr;
+  // rotated walk orders of this CTA
+  const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
+  const int kc0 = (int)((blockIdx.x / (unsigned)n_nt) % (unsigned)n_kc);
 
   if (threadIdx.x == 0) {
     mbar_init(&sm->x_full, 1);
     mbar_init(&sm->x_conv, 4);
-    mbar_init(&sm->x_free, 4);
+    mbar_init(&sm->x_stage_free, 4);
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
       mbar_init(&sm->b_empty[s], 1);
@@ -268,6 +324,8 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm->acc_full[a], 1);
       mbar_init(&sm->acc_empty[a], 4);
+      mbar_init(&sm->upd_full[a], 4);
+      mbar_init(&sm->upd_empty[a], 4);
     }
     sm->abort_flag = 0;
     fence_barrier_init();
@@ -286,13 +344,10 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (lane == 0) {
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-        if (!mbar_wait(&sm->x_free, (t & 1) ^ 1, sm, p.error_flag)) break;
+        if (!mbar_wait(&sm->x_stage_free, (t & 1) ^ 1, sm, p.error_flag)) break;
         mbar_expect_tx(&sm->x_full, (uint32_t)n_kc * TC_ATOM_BYTES);
         for (int kc = 0; kc < n_kc; ++kc)
-          tma_load_2d(sm->xhi[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
-        const int64_t next = tile + gridDim.x;
-        if (next < n_tiles)
-          for (int kc = 0; kc < n_kc; ++kc) tma_prefetch_2d(&map_x, kc * TC_KC, (int)(next * TC_BM));
+          tma_load_2d(sm->xstage[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
       }
     }
   } else if (warp == 1) {
@@ -301,8 +356,10 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        for (int nt = 0; nt < n_nt && ok; ++nt) {
-          for (int kc = 0; kc < n_kc; ++kc, ++it) {
+        for (int i = 0; i < n_nt && ok; ++i) {
+          const int nt = (nt0 + i) % n_nt;
+          for (int j = 0; j < n_kc; ++j, ++it) {
+            const int kc = (kc0 + j) % n_kc;
             const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
             if (!mbar_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
               ok = false;
@@ -317,313 +374,50 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------------ MMA
-    if (lane == 0) {
-      uint32_t t = 0, it = 0, g = 0;
-      bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-        if (!mbar_wait(&sm->x_conv, t & 1, sm, p.error_flag)) break;
-        tc_fence_after();
-        for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
-          const uint32_t ab = g & 1, ug = g >> 1;
-          if (!mbar_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + ab * TC_BN;
-          for (int kc = 0; kc < n_kc; ++kc, ++it) {
-            const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
-            if (!mbar_wait(&sm->b_full[s], u & 1, sm, p.error_flag)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint64_t a_hi = make_sdesc(smem_u32(sm->xhi[kc]));
-            const uint64_t a_lo = make_sdesc(smem_u32(sm->xlo[kc]));
-            const uint64_t b_hi = make_sdesc(smem_u32(sm->bhi[s]));
-            const uint64_t b_lo = make_sdesc(smem_u32(sm->blo[s]));
-#pragma unroll
-            for (int ks = 0; ks < TC_KC / 8; ++ks) {
-              const uint64_t adv = (uint64_t)(ks * 32 >> 4);  // 8 tf32 = 32 bytes per k-step
-              umma_tf32(d_tmem, a_lo + adv, b_hi + adv, TC_IDESC, (kc | ks) != 0);
-              umma_tf32(d_tmem, a_hi + adv, b_lo + adv, TC_IDESC, 1);
-              umma_tf32(d_tmem, a_hi + adv, b_hi + adv, TC_IDESC, 1);
-            }
-            umma_commit(&sm->b_empty[s]);
-          }
-          if (ok) umma_commit(&sm->acc_full[ab]);
-        }
-      }
-    }
-  } else {
-    // ---------------------------------------------- split, argmin epilogue, update
-    const int ew = warp - TC_EPI_WARP0;            // 0..3
-    const int et = ew * 32 + lane;                 // 0..127
-    const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
-    const int row = lane_base + lane;              // sample row within the tile
-    float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
-    uint32_t t = 0, g = 0, changed = 0;
-    bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-      const int64_t m0 = tile * TC_BM;
-      // ---- hi/lo split of the sample tile, in place (any element-wise map keeps the swizzle)
-      // wait results are made warp-uniform: the shuffles below need all 32 lanes
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full, t & 1, sm, p.error_flag))) break;
-      {
-        float4* hi4 = reinterpret_cast<float4*>(sm->xhi[0]);
-        float4* lo4 = reinterpret_cast<float4*>(sm->xlo[0]);
-        const int n_vec = n_kc * (TC_ATOM_BYTES / 16);
-        for (int e = et; e < n_vec; e += 128) {
-          const float4 x = hi4[e];
-          float4 hh, ll;
-          hh.x = tf32_round(x.x); ll.x = x.x - hh.x;
-          hh.y = tf32_round(x.y); ll.y = x.y - hh.y;
-          hh.z = tf32_round(x.z); ll.z = x.z - hh.z;
-          hh.w = tf32_round(x.w); ll.w = x.w - hh.w;
-          hi4[e] = hh;
-          lo4[e] = ll;
-        }
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->x_conv);
-
-      float best = __int_as_float(0x7f800000);
-      uint32_t bi = 0;
-      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
-        const uint32_t ab = g & 1, ug = g >> 1;
-        const int cn = nt * TC_BN;
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + ab * TC_BN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c0, v);
-          tmem_ld_wait();
-          if (p.dots != nullptr && m0 + row < p.n) {
-            float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(v[j]);
-          }
-          // same address in every lane: one broadcast load per four centroids
-          const float4* h4 = reinterpret_cast<const float4*>(p.h_pad + cn + c0);
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 hv = __ldg(h4 + j4);
-            const float q0 = hv.x - __uint_as_float(v[4 * j4 + 0]);
-            const float q1 = hv.y - __uint_as_float(v[4 * j4 + 1]);
-            const float q2 = hv.z - __uint_as_float(v[4 * j4 + 2]);
-            const float q3 = hv.w - __uint_as_float(v[4 * j4 + 3]);
-            const uint32_t jb = (uint32_t)(cn + c0 + 4 * j4);
-            if (q0 < best) { best = q0; bi = jb; }
-            if (q1 < best) { best = q1; bi = jb + 1; }
-            if (q2 < best) { best = q2; bi = jb + 2; }
-            if (q3 < best) { best = q3; bi = jb + 3; }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
-      }
-      if (!ok) break;
-
-      // ---- labels, change count, centroid update (one warp adds one 512-byte row at a time)
-      const bool valid = m0 + row < p.n;
-      float wi = 0.f;
-      if (valid) {
-        p.labels[m0 + row] = bi;
-        if (update) {
-          changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
-          wi = p.w ? p.w[m0 + row] : 1.f;
-          atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
-        }
-      }
-      if (update) {
-        const int kc = lane >> 3, chunk = lane & 7;      // 16-byte chunk `chunk` of atom `kc`
-        const bool col_ok = (lane * 4) < p.d;
-        for (int r = 0; r < 32; ++r) {
-          const uint32_t lab = __shfl_sync(0xffffffffu, bi, r);
-          const float wr = __shfl_sync(0xffffffffu, wi, r);
-          const int rr = lane_base + r;
-          const bool row_ok = __shfl_sync(0xffffffffu, (int)valid, r) != 0;
-          if (row_ok && col_ok) {
-            const int off = rr * 128 + ((chunk ^ (rr & 7)) << 4);
-            const float4 xh = *reinterpret_cast<const float4*>(sm->xhi[kc] + off);
-            const float4 xl = *reinterpret_cast<const float4*>(sm->xlo[kc] + off);
-            float4 v;
-            v.x = (xh.x + xl.x) * wr;
-            v.y = (xh.y + xl.y) * wr;
-            v.z = (xh.z + xl.z) * wr;
-            v.w = (xh.w + xl.w) * wr;
-            atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + lane * 4), v);
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->x_free);
-    }
-    if (update) {
-      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
-      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TC_TMEM_COLS);
-  }
-}
-
-// ------------------------------------------------ variant with the sample tile in TMEM
-// Same roles as lloyd_tc_kernel, but the hi/lo parts of the sample tile live in tensor
-// memory (A operand read from TMEM): shared memory only stages the raw fp32 tile, which is
-// free again as soon as it has been split, so the next tile's TMA overlaps this tile's MMAs
-// and five centroid stages (160 KB) are in flight instead of three.
-constexpr int TS_STAGES = 5;
-constexpr int TS_A_HI_COL = 0, TS_A_LO_COL = 128, TS_ACC_COL = 256, TS_TMEM_COLS = 512;
-
-struct TsSmem {
-  unsigned char xstage[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
-  unsigned char bhi[TS_STAGES][TC_ATOM_BYTES];
-  unsigned char blo[TS_STAGES][TC_ATOM_BYTES];
-  unsigned long long x_full, x_conv, x_stage_free;
-  unsigned long long b_full[TS_STAGES], b_empty[TS_STAGES];
-  unsigned long long acc_full[2], acc_empty[2];
-  unsigned int tmem_base;
-  volatile int abort_flag;
-};
-
-__device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, int* error_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (sm->abort_flag) return false;
-    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
-      sm->abort_flag = 1;
-      atomicExch(error_flag, 1);
-      return false;
-    }
-  }
-}
-
-__global__ void __launch_bounds__(TC_THREADS, 1)
-lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
-                   const __grid_constant__ CUtensorMap map_clo, TcParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  TsSmem* sm = reinterpret_cast<TsSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_kc = p.d_pad / TC_KC;
-  const int n_nt = p.k_pad / TC_BN;
-  const int64_t n_tiles = (p.n + TC_BM - 1) / TC_BM;
-  const bool update = p.acc != nullptr;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&sm->x_full, 1);
-    mbar_init(&sm->x_conv, 4);
-    mbar_init(&sm->x_stage_free, 4);
-    for (int s = 0; s < TS_STAGES; ++s) {
-      mbar_init(&sm->b_full[s], 1);
-      mbar_init(&sm->b_empty[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&sm->acc_full[a], 1);
-      mbar_init(&sm->acc_empty[a], 4);
-    }
-    sm->abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 2) {
-    tmem_alloc(&sm->tmem_base, TS_TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = sm->tmem_base;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      uint32_t t = 0;
-      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-        if (!ts_wait(&sm->x_stage_free, (t & 1) ^ 1, sm, p.error_flag)) break;
-        mbar_expect_tx(&sm->x_full, (uint32_t)n_kc * TC_ATOM_BYTES);
-        for (int kc = 0; kc < n_kc; ++kc)
-          tma_load_2d(sm->xstage[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        for (int nt = 0; nt < n_nt && ok; ++nt) {
-          for (int kc = 0; kc < n_kc; ++kc, ++it) {
-            const uint32_t s = it % TS_STAGES, u = it / TS_STAGES;
-            if (!ts_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
-              ok = false;
-              break;
-            }
-            mbar_expect_tx(&sm->b_full[s], 2 * TC_ATOM_BYTES);
-            tma_load_2d(sm->bhi[s], &map_chi, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
-            tma_load_2d(sm->blo[s], &map_clo, kc * TC_KC, nt * TC_BN, &sm->b_full[s]);
-          }
-        }
-      }
-    }
-  } else if (warp == 2) {
-    // The whole warp walks the loop so that every address and descriptor below is
-    // warp-uniform (uniform datapath); one elected lane issues the tensor-core work.
     uint32_t t = 0, it = 0, g = 0;
     bool ok = true;
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_conv, t & 1, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_conv, t & 1, sm, p.error_flag))) break;
       tc_fence_after();
-      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+      for (int i = 0; i < n_nt && ok; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
-        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag))) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + TS_ACC_COL + ab * TC_BN;
-        for (int kc = 0; kc < n_kc; ++kc, ++it) {
-          const uint32_t s = it % TS_STAGES, u = it / TS_STAGES;
-          if (!__all_sync(0xffffffffu, ts_wait(&sm->b_full[s], u & 1, sm, p.error_flag))) {
+        const uint32_t d_tmem = tmem_base + TC_ACC_COL + ab * TC_BN;
+        for (int j = 0; j < n_kc; ++j, ++it) {
+          const int kc = (kc0 + j) % n_kc;
+          const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
+          if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full[s], u & 1, sm, p.error_flag))) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
           const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
-          const uint32_t a_hi = tmem_base + TS_A_HI_COL + kc * TC_KC;
-          const uint32_t a_lo = tmem_base + TS_A_LO_COL + kc * TC_KC;
+          const uint32_t a_hi = tmem_base + TC_A_HI_COL + kc * TC_KC;
+          const uint32_t a_lo = tmem_base + TC_A_LO_COL + kc * TC_KC;
           if (elect_one()) {
 #pragma unroll
             for (int ks = 0; ks < TC_KC / 8; ++ks) {
               const uint64_t adv = (uint64_t)(ks * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units
-              umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, (kc | ks) != 0);
+              umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, (j | ks) != 0);
               umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
               umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
             }
             umma_commit(&sm->b_empty[s]);
-            if (kc == n_kc - 1) umma_commit(&sm->acc_full[ab]);
+            if (j == n_kc - 1) umma_commit(&sm->acc_full[ab]);
           }
           __syncwarp();
         }
       }
     }
-  } else {
+  } else if (warp < TC_UPD_WARP0) {
+    // ------------------------------------------------ split into TMEM, argmin epilogue
     const int lane_base = (warp & 3) * 32;
     const int row = lane_base + lane;
     float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
@@ -631,9 +425,9 @@ lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     bool ok = true;
 
     // Splits the staged tile (row `row`, 128B-swizzled atoms) into TMEM: hi -> columns
-    // [0, d_pad), lo -> [128, 128 + d_pad) of this thread's lane.  Returns false on time-out.
+    // [0, d_pad), lo -> [128, 128 + d_pad) of this thread's lane.  False on time-out.
     auto convert_tile = [&](uint32_t tt) -> bool {
-      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_full, tt & 1, sm, p.error_flag))) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full, tt & 1, sm, p.error_flag))) return false;
       for (int kc = 0; kc < n_kc; ++kc) {
         uint32_t hi[32], lo[32];
         const unsigned char* rowp = sm->xstage[kc] + row * 128;
@@ -648,8 +442,8 @@ lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(x.w - h3);
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + kc * TC_KC;
-        tmem_st32(lane_addr + TS_A_HI_COL, hi);
-        tmem_st32(lane_addr + TS_A_LO_COL, lo);
+        tmem_st32(lane_addr + TC_A_HI_COL, hi);
+        tmem_st32(lane_addr + TC_A_LO_COL, lo);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -661,105 +455,127 @@ lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       return true;
     };
 
-    if ((int64_t)blockIdx.x < n_tiles) ok = convert_tile(0);
+    ok = convert_tile(0);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
       const int64_t m0 = tile * TC_BM;
       const bool has_next = tile + gridDim.x < n_tiles;
       float best = __int_as_float(0x7f800000);
       uint32_t bi = 0;
-      for (int nt = 0; nt < n_nt && ok; ++nt, ++g) {
+      for (int i = 0; i < n_nt && ok; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
-        const int cn = nt * TC_BN;
-        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+        const int cn = ((nt0 + i) % n_nt) * TC_BN;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
           ok = false;
           break;
         }
         tc_fence_after();
         // The last accumulator of a tile completing means every MMA of the tile has read its
-        // A operand: split the next tile into TMEM first, so the MMA warp can go on while
-        // this tile's last epilogue and update run.
-        if (nt == n_nt - 1 && has_next) {
+        // A operand: split the next tile into TMEM first, so that the MMA warp can go on
+        // while this tile's last epilogue runs.
+        if (i == n_nt - 1 && has_next) {
           if (!convert_tile(t + 1)) {
             ok = false;
             break;
           }
         }
-        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TS_ACC_COL + ab * TC_BN;
+        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN;
+        float tbest = __int_as_float(0x7f800000);   // minimum over this centroid tile
+        uint32_t tbi = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
-          if (p.debug & 1) break;
-          uint32_t v[32];
-          tmem_ld32(taddr + c0, v);
+        for (int c0 = 0; c0 < TC_BN; c0 += 64) {
+          uint32_t va[32], vb[32];
+          tmem_ld32(taddr + c0, va);
+          tmem_ld32(taddr + c0 + 32, vb);
           tmem_ld_wait();
           if (p.dots != nullptr && m0 + row < p.n) {
             float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) {
+              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(va[j]);
+              if (cn + c0 + 32 + j < p.k) drow[cn + c0 + 32 + j] = __uint_as_float(vb[j]);
+            }
           }
-          const float4* h4 = reinterpret_cast<const float4*>(p.h_pad + cn + c0);
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 hv = __ldg(h4 + j4);
-            const float q0 = hv.x - __uint_as_float(v[4 * j4 + 0]);
-            const float q1 = hv.y - __uint_as_float(v[4 * j4 + 1]);
-            const float q2 = hv.z - __uint_as_float(v[4 * j4 + 2]);
-            const float q3 = hv.w - __uint_as_float(v[4 * j4 + 3]);
-            const uint32_t jb = (uint32_t)(cn + c0 + 4 * j4);
-            if (q0 < best) { best = q0; bi = jb; }
-            if (q1 < best) { best = q1; bi = jb + 1; }
-            if (q2 < best) { best = q2; bi = jb + 2; }
-            if (q3 < best) { best = q3; bi = jb + 3; }
-          }
+          float qa, qb;
+          uint32_t ia, ib;
+          min_tree32(va, reinterpret_cast<const float4*>(p.h_pad + cn + c0), (uint32_t)(cn + c0), qa, ia);
+          min_tree32(vb, reinterpret_cast<const float4*>(p.h_pad + cn + c0 + 32),
+                     (uint32_t)(cn + c0 + 32), qb, ib);
+          if (qa < tbest) { tbest = qa; tbi = ia; }   // ascending inside the tile: strict '<'
+          if (qb < tbest) { tbest = qb; tbi = ib; }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+        // tiles arrive in rotated order: smaller value wins, equal values -> smaller index
+        if (tbest < best || (tbest == best && tbi < bi)) {
+          best = tbest;
+          bi = tbi;
+        }
       }
       if (!ok) break;
 
       const bool valid = m0 + row < p.n;
-      float wi = 0.f;
       if (valid) {
         p.labels[m0 + row] = bi;
-        if (update) {
-          changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
-          wi = p.w ? p.w[m0 + row] : 1.f;
-          atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
-        }
+        if (update) changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
       }
-      if (update && !(p.debug & 2)) {
-        // the tile's rows come back from L2 (they were streamed through it moments ago):
-        // one warp adds one row (d floats, 16 bytes per lane) per instruction
-        const bool col_ok = (lane * 4) < p.d;
-        const float* xbase = p.X + (m0 + lane_base) * (int64_t)p.d + lane * 4;
-#pragma unroll 1
-        for (int r0 = 0; r0 < 32; r0 += 8) {
-          // eight rows in flight: the loads come back from L2 together, then eight reductions
-          float4 xs[8];
-          bool oks[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            oks[j] = (__shfl_sync(0xffffffffu, (int)valid, r0 + j) != 0) && col_ok;
-            xs[j] = oks[j] ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(r0 + j) * p.d))
-                           : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t lab = __shfl_sync(0xffffffffu, bi, r0 + j);
-            const float wr = __shfl_sync(0xffffffffu, wi, r0 + j);
-            if (oks[j]) {
-              float4 v;
-              v.x = xs[j].x * wr; v.y = xs[j].y * wr; v.z = xs[j].z * wr; v.w = xs[j].w * wr;
-              atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + lane * 4), v);
-            }
-          }
-        }
+      if (update) {
+        // hand the tile's labels to the update warps
+        const uint32_t buf = t & 1, ub = t >> 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->upd_empty[buf], (ub & 1) ^ 1, sm, p.error_flag))) break;
+        sm->lab_s[buf][row] = bi;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->upd_full[buf]);
       }
     }
     if (update) {
       for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
       if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
+    }
+  } else if (update) {
+    // ------------------------------------------------------ centroid update warps
+    const int uw = warp - TC_UPD_WARP0;
+    const int row = uw * 32 + lane;
+    float* acc_copy = p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len;
+    const bool col_ok = (lane * 4) < p.d;
+    uint32_t t = 0;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+      const int64_t m0 = tile * TC_BM;
+      const uint32_t buf = t & 1, ub = t >> 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->upd_full[buf], ub & 1, sm, p.error_flag))) break;
+      const uint32_t bi = sm->lab_s[buf][row];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->upd_empty[buf]);
+      const bool valid = m0 + row < p.n;
+      float wi = 0.f;
+      if (valid) {
+        wi = p.w ? p.w[m0 + row] : 1.f;
+        atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
+      }
+      // the tile's rows come back from L2 (they were streamed through it moments ago): one
+      // warp adds one row (d floats, 16 bytes per lane) per instruction, eight rows in flight
+      const float* xbase = p.X + (m0 + uw * 32) * (int64_t)p.d + lane * 4;
+#pragma unroll 1
+      for (int r0 = 0; r0 < 32; r0 += 8) {
+        float4 xs[8];
+        bool oks[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          oks[j] = (__shfl_sync(0xffffffffu, (int)valid, r0 + j) != 0) && col_ok;
+          xs[j] = oks[j] ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(r0 + j) * p.d))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t lab = __shfl_sync(0xffffffffu, bi, r0 + j);
+          const float wr = __shfl_sync(0xffffffffu, wi, r0 + j);
+          if (oks[j]) {
+            float4 v;
+            v.x = xs[j].x * wr; v.y = xs[j].y * wr; v.z = xs[j].z * wr; v.w = xs[j].w * wr;
+            atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + lane * 4), v);
+          }
+        }
+      }
     }
   }
 
@@ -767,7 +583,7 @@ lloyd_tc_ts_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TS_TMEM_COLS);
+    tmem_dealloc(tmem_base, TC_TMEM_COLS);
   }
 }
 
@@ -831,17 +647,6 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols,
     return KMB_ERR_CUDA;
   }
   return KMB_OK;
-}
-
-// KMB_TC_VARIANT=ss selects the kernel with both operands in shared memory; the default is the
-// kernel that keeps the sample tile in tensor memory.
-static bool tc_variant_is_ts() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* v = getenv("KMB_TC_VARIANT");
-    cached = (v != nullptr && v[0] == 's' && v[1] == 's') ? 0 : 1;
-  }
-  return cached == 1;
 }
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -914,25 +719,14 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.X = X; p.w = w; p.h_pad = ws.h_pad; p.prev = prev; p.labels = labels; p.acc = acc;
   p.dots = dots; p.error_flag = ws.error_flag; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
-  {
-    const char* dbg = getenv("KMB_TC_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-  }
 
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
-  if (tc_variant_is_ts()) {
-    const size_t smem = sizeof(TsSmem) + 1024;
-    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_ts_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    lloyd_tc_ts_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
-  } else {
-    const size_t smem = sizeof(TcSmem) + 1024;
-    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-    lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
-  }
+  const size_t smem = sizeof(TcSmem) + 1024;
+  KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+  lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
   KMB_CHECK_LAUNCH();
   return KMB_OK;
 }
