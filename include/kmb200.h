@@ -175,21 +175,23 @@ int kmb_topk_idx_static(int dtype, const void* values, int64_t n_cols, int k, in
 int kmb_kpp_block_rows(void);
 
 /* closest[i] = w_i * ||X[i] - X[first]||^2, bsum[b] = float64 sum of block b,
- * centers row 0 = X[first], indices[0] = first.
+ * centers row 0 = X[first], indices[0] = first.  When first_row (d elements) is given it is
+ * used instead of X[first] (row shards: the first centre may live on another rank).
  * Replaces make_kmeansplusplus_init_kernel, kmeans/kernels/kmeans_plusplus.py:16-58, and
  * the potential sum of drivers.py:844. */
-int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, void* closest,
-                 double* bsum, void* centers, int32_t* indices, int64_t n, int d,
+int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, const void* first_row,
+                 void* closest, double* bsum, void* centers, int32_t* indices, int64_t n, int d,
                  void* stream);
 
 /* For each trial tau < t: r = u[tau] * total, cand[tau] = first i whose inclusive prefix
  * sum of closest reaches r (0 if r <= 0, n-1 if never).  closest is row *best of
  * M (.., n) and its block sums row *best of bsum (.., nb); the prefix is taken in
- * float64.  Replaces make_sample_center_candidates_kernel,
+ * float64.  offset (one element, may be NULL) is subtracted from r: the potential held by
+ * the row shards before this one.  Replaces make_sample_center_candidates_kernel,
  * kmeans/kernels/kmeans_plusplus.py:61-103 (a sequential running sum there). */
 int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
-                   const void* total, const void* u, int t, int32_t* cand, int64_t n,
-                   void* stream);
+                   const void* total, const void* u, const void* offset, int t, int32_t* cand,
+                   int64_t n, void* stream);
 
 /* out[tau, :] = X[ids[tau], :]  (ids on device). */
 int kmb_gather_rows(int dtype, const void* X, const int32_t* ids, int t, int d, void* out,
@@ -203,13 +205,18 @@ int kmb_kpp_step(int dtype, const void* X, const void* w, const void* cand_rows,
                  const void* M_prev, const int32_t* best_prev, void* M_out,
                  double* bsum_out, int64_t n, int d, int t, void* stream);
 
-/* pots[tau] = sum_b bsum[tau, b] (fixed order, rounded to dtype); *best = argmin (lowest
+/* pots[tau] = sum_b bsum[tau, b] in float64, fixed order (the row sums of drivers.py:895,
+ * kept in float64 so that shards can be all-reduced before the argmin). */
+int kmb_kpp_potentials(const double* bsum, int t, int64_t nb, double* pots, void* stream);
+
+/* pots[tau] = pots_in[tau] if given, else sum_b bsum[tau, b] (rounded to dtype); *best = argmin (lowest
  * tau on ties); *total = pots[*best]; centers row c = cand_rows[*best];
  * indices[c] = cand[*best].  Replaces make_argmin_reduction_1d_kernel
  * (common/reductions.py:18-209) and the host steps of drivers.py:897-908. */
-int kmb_kpp_select(int dtype, const double* bsum, int t, int64_t nb, void* pots,
-                   int32_t* best, void* total, const void* cand_rows, const int32_t* cand,
-                   void* centers, int32_t* indices, int c, int d, void* stream);
+int kmb_kpp_select(int dtype, const double* bsum, const double* pots_in, int t, int64_t nb,
+                   void* pots, int32_t* best, void* total, const void* cand_rows,
+                   const int32_t* cand, void* centers, int32_t* indices, int c, int d,
+                   void* stream);
 
 /* ---- data preparation (kmeans/drivers.py:436-589) --------------------------------- */
 /* out[f] = sum_i X[i,f] in float64 (d doubles). Replaces make_sum_reduction_2d_kernel

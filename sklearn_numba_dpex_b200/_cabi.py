@@ -61,11 +61,12 @@ _SIGNATURES = {
     "kmb_topk_workspace_bytes": (c_size_t, [c_int, c_int64, c_int]),
     "kmb_topk_idx_static": (c_int, [c_int, _P, c_int64, c_int, _P, _P]),
     "kmb_kpp_block_rows": (c_int, []),
-    "kmb_kpp_init": (c_int, [c_int, _P, _P, c_int64, _P, _P, _P, _P, c_int64, c_int, _P]),
-    "kmb_kpp_sample": (c_int, [c_int, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P]),
+    "kmb_kpp_init": (c_int, [c_int, _P, _P, c_int64, _P, _P, _P, _P, _P, c_int64, c_int, _P]),
+    "kmb_kpp_sample": (c_int, [c_int, _P, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P]),
     "kmb_gather_rows": (c_int, [c_int, _P, _P, c_int, c_int, _P, _P]),
     "kmb_kpp_step": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P]),
-    "kmb_kpp_select": (c_int, [c_int, _P, c_int, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int,
+    "kmb_kpp_potentials": (c_int, [_P, c_int, c_int64, _P, _P]),
+    "kmb_kpp_select": (c_int, [c_int, _P, _P, c_int, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int,
                                c_int, _P]),
     "kmb_col_sums": (c_int, [c_int, _P, c_int64, c_int, _P, _P, c_size_t, _P]),
     "kmb_sum": (c_int, [c_int, _P, c_int64, c_int, _P, _P, c_size_t, _P]),

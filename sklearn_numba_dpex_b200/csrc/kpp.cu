@@ -22,12 +22,13 @@ __device__ __forceinline__ double group_sum_kpp(double v, int G) {
 template <typename T>
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_init_kernel(const T* __restrict__ X, const T* __restrict__ w, int64_t first,
-                T* __restrict__ closest, double* __restrict__ bsum, T* __restrict__ centers,
+                const T* __restrict__ first_row, T* __restrict__ closest, double* __restrict__ bsum, T* __restrict__ centers,
                 int32_t* __restrict__ indices, int64_t n, int d, int G) {
   __shared__ double red[32];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   T* c = reinterpret_cast<T*>(dyn_smem);
-  for (int f = threadIdx.x; f < d; f += KPP_THREADS) c[f] = X[first * (int64_t)d + f];
+  for (int f = threadIdx.x; f < d; f += KPP_THREADS)
+    c[f] = first_row ? first_row[f] : X[first * (int64_t)d + f];
   __syncthreads();
   if (blockIdx.x == 0) {
     for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers[f] = c[f];
@@ -64,7 +65,8 @@ template <typename T>
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
                   const int32_t* __restrict__ best, const T* __restrict__ total,
-                  const T* __restrict__ u, int32_t* __restrict__ cand, int64_t n, int64_t nb) {
+                  const T* __restrict__ u, const T* __restrict__ offset,
+                  int32_t* __restrict__ cand, int64_t n, int64_t nb) {
   __shared__ double scan_s[KPP_THREADS];
   __shared__ double carry_s;
   __shared__ unsigned long long found_s;  // smallest matching index, ~0 = none
@@ -73,7 +75,8 @@ kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
   const T* closest = M + (int64_t)b * n;
   const double* bs = bsum + (int64_t)b * nb;
   const T r_t = u[blockIdx.x] * total[0];
-  const double r = (double)r_t;
+  // on a row shard the threshold is taken relative to the potential held by earlier shards
+  const double r = (double)r_t - (offset ? (double)offset[0] : 0.0);
   if (!(r > 0.0)) {
     if (tid == 0) cand[blockIdx.x] = 0;
     return;
@@ -218,7 +221,8 @@ kpp_step_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
 // Single CTA: potentials in fixed order, argmin (lowest trial on ties), commit the centre.
 template <typename T>
 __global__ void __launch_bounds__(KPP_THREADS)
-kpp_select_kernel(const double* __restrict__ bsum, int t, int64_t nb, T* __restrict__ pots,
+kpp_select_kernel(const double* __restrict__ bsum, const double* __restrict__ pots_in, int t,
+                  int64_t nb, T* __restrict__ pots,
                   int32_t* __restrict__ best, T* __restrict__ total,
                   const T* __restrict__ cand_rows, const int32_t* __restrict__ cand,
                   T* __restrict__ centers, int32_t* __restrict__ indices, int c, int d) {
@@ -226,9 +230,14 @@ kpp_select_kernel(const double* __restrict__ bsum, int t, int64_t nb, T* __restr
   __shared__ T pots_s[KPP_MAX_T];
   __shared__ int best_s;
   for (int tau = 0; tau < t; ++tau) {
-    double s = 0.0;
-    for (int64_t b = threadIdx.x; b < nb; b += KPP_THREADS) s += bsum[(int64_t)tau * nb + b];
-    const double tot = block_sum(s, red);
+    double tot;
+    if (pots_in != nullptr) {
+      tot = pots_in[tau];
+    } else {
+      double s = 0.0;
+      for (int64_t b = threadIdx.x; b < nb; b += KPP_THREADS) s += bsum[(int64_t)tau * nb + b];
+      tot = block_sum(s, red);
+    }
     if (threadIdx.x == 0) pots_s[tau] = (T)tot;
     __syncthreads();
   }
@@ -253,6 +262,16 @@ kpp_select_kernel(const double* __restrict__ bsum, int t, int64_t nb, T* __restr
       centers[(int64_t)c * d + f] = cand_rows[(int64_t)best_s * d + f];
 }
 
+// pots[tau] = sum_b bsum[tau, b] in float64, fixed order; one block per trial.
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_potentials_kernel(const double* __restrict__ bsum, int64_t nb, double* __restrict__ pots) {
+  __shared__ double red[32];
+  double s = 0.0;
+  for (int64_t b = threadIdx.x; b < nb; b += KPP_THREADS) s += bsum[(int64_t)blockIdx.x * nb + b];
+  const double tot = block_sum(s, red);
+  if (threadIdx.x == 0) pots[blockIdx.x] = tot;
+}
+
 }  // namespace kmb
 
 using namespace kmb;
@@ -261,10 +280,12 @@ extern "C" {
 
 int kmb_kpp_block_rows(void) { return KPP_BLOCK; }
 
-int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, void* closest,
-                 double* bsum, void* centers, int32_t* indices, int64_t n, int d, void* stream) {
+int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, const void* first_row,
+                 void* closest, double* bsum, void* centers, int32_t* indices, int64_t n, int d,
+                 void* stream) {
   KMB_REQUIRE(X && closest && bsum && centers && indices, "kmb_kpp_init: NULL argument");
-  KMB_REQUIRE(n > 0 && d > 0 && first >= 0 && first < n, "kmb_kpp_init: bad sizes");
+  KMB_REQUIRE(n > 0 && d > 0 && first >= 0 && (first_row != nullptr || first < n),
+              "kmb_kpp_init: bad sizes");
   KMB_REQUIRE(n < (1ll << 31), "kmb_kpp_init: n must be below 2^31 (int32 candidate ids)");
   const int G = lanes_per_row(d);
   const int64_t nb = ceil_div(n, KPP_BLOCK);
@@ -272,21 +293,22 @@ int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, void* c
     const size_t dyn = (size_t)d * sizeof(T);
     KMB_REQUIRE(dyn <= 48 * 1024, "kmb_kpp_init: d too large (%d)", d);
     kpp_init_kernel<T><<<(unsigned)nb, KPP_THREADS, dyn, (cudaStream_t)stream>>>(
-        (const T*)X, (const T*)w, first, (T*)closest, bsum, (T*)centers, indices, n, d, G);
+        (const T*)X, (const T*)w, first, (const T*)first_row, (T*)closest, bsum, (T*)centers, indices,
+        n, d, G);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;
 }
 
 int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
-                   const void* total, const void* u, int t, int32_t* cand, int64_t n,
-                   void* stream) {
+                   const void* total, const void* u, const void* offset, int t, int32_t* cand,
+                   int64_t n, void* stream) {
   KMB_REQUIRE(M && bsum && total && u && cand, "kmb_kpp_sample: NULL argument");
   KMB_REQUIRE(n > 0 && t > 0 && t <= KPP_MAX_T, "kmb_kpp_sample: bad sizes");
   const int64_t nb = ceil_div(n, KPP_BLOCK);
   KMB_DISPATCH_DTYPE(dtype, {
     kpp_sample_kernel<T><<<t, KPP_THREADS, 0, (cudaStream_t)stream>>>(
-        (const T*)M, bsum, best, (const T*)total, (const T*)u, cand, n, nb);
+        (const T*)M, bsum, best, (const T*)total, (const T*)u, (const T*)offset, cand, n, nb);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;
@@ -324,15 +346,23 @@ int kmb_kpp_step(int dtype, const void* X, const void* w, const void* cand_rows,
   return KMB_OK;
 }
 
-int kmb_kpp_select(int dtype, const double* bsum, int t, int64_t nb, void* pots, int32_t* best,
-                   void* total, const void* cand_rows, const int32_t* cand, void* centers,
-                   int32_t* indices, int c, int d, void* stream) {
-  KMB_REQUIRE(bsum && best && total, "kmb_kpp_select: NULL argument");
+int kmb_kpp_potentials(const double* bsum, int t, int64_t nb, double* pots, void* stream) {
+  KMB_REQUIRE(bsum && pots && t > 0 && nb > 0, "kmb_kpp_potentials: bad arguments");
+  kpp_potentials_kernel<<<t, KPP_THREADS, 0, (cudaStream_t)stream>>>(bsum, nb, pots);
+  KMB_CHECK_LAUNCH();
+  return KMB_OK;
+}
+
+int kmb_kpp_select(int dtype, const double* bsum, const double* pots_in, int t, int64_t nb,
+                   void* pots, int32_t* best, void* total, const void* cand_rows,
+                   const int32_t* cand, void* centers, int32_t* indices, int c, int d,
+                   void* stream) {
+  KMB_REQUIRE((bsum || pots_in) && best && total, "kmb_kpp_select: NULL argument");
   KMB_REQUIRE(t > 0 && t <= KPP_MAX_T && nb > 0 && c >= 0 && d > 0, "kmb_kpp_select: bad sizes");
   KMB_DISPATCH_DTYPE(dtype, {
     kpp_select_kernel<T><<<1, KPP_THREADS, 0, (cudaStream_t)stream>>>(
-        bsum, t, nb, (T*)pots, best, (T*)total, (const T*)cand_rows, cand, (T*)centers, indices, c,
-        d);
+        bsum, pots_in, t, nb, (T*)pots, best, (T*)total, (const T*)cand_rows, cand, (T*)centers,
+        indices, c, d);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;

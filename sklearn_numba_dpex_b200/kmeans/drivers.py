@@ -471,8 +471,6 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     """
     from ..common.random import create_xoroshiro128pp_states, get_random_raw, uniform_draws
 
-    if dist.active():
-        raise NotImplementedError("k-means++ over row shards is not implemented")
     X = _rows(X_t)
     n, d = X.shape
     k = int(n_clusters)
@@ -480,9 +478,15 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     code = dtype_code(dt)
     T = _np_dtype(X)
     t = 2 + int(math.log(k))
+    sharded = dist.active()
+    counts = dist.all_gather_object(int(n)) if sharded else [n]
+    n_total = int(sum(counts))
+    row0 = int(sum(counts[: dist.rank()])) if sharded else 0
     states = create_xoroshiro128pp_states(t, seed=random_state)
-    first = int(get_random_raw(states)[0] % np.uint64(n))
+    first = int(get_random_raw(states)[0] % np.uint64(n_total))
     u_host = uniform_draws(states, k - 1, T)  # (k-1, t)
+    if sharded:
+        dist.check_same_across_ranks(first=first, k=k, d=d, u_sum=float(u_host.sum()))
     u = torch.from_numpy(u_host).to(dev) if k > 1 else torch.empty((0, t), dtype=dt, device=dev)
 
     block = lib.kmb_kpp_block_rows()
@@ -499,21 +503,67 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     w = sample_weight
     s = stream_ptr(dev)
 
-    check(lib.kmb_kpp_init(code, ptr(X), ptr(w), first, ptr(M[0]), ptr(bsum[0]), ptr(centers),
-                           ptr(indices), n, d, s), "kmb_kpp_init")
-    check(lib.kmb_kpp_select(code, ptr(bsum[0]), 1, nb, None, ptr(best), ptr(total), None, None,
-                             None, None, 0, d, s), "kmb_kpp_select")
+    if not sharded:
+        check(lib.kmb_kpp_init(code, ptr(X), ptr(w), first, None, ptr(M[0]), ptr(bsum[0]),
+                               ptr(centers), ptr(indices), n, d, s), "kmb_kpp_init")
+        check(lib.kmb_kpp_select(code, ptr(bsum[0]), None, 1, nb, None, ptr(best), ptr(total), None,
+                                 None, None, None, 0, d, s), "kmb_kpp_select")
+        cur = 0
+        for c in range(1, k):
+            nxt = 1 - cur
+            check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
+                                     ptr(u[c - 1]), None, t, ptr(cand), n, s), "kmb_kpp_sample")
+            check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),
+                  "kmb_gather_rows")
+            check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(cand_rows), ptr(M[cur]), ptr(best),
+                                   ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
+            check(lib.kmb_kpp_select(code, ptr(bsum[nxt]), None, t, nb, ptr(pots), ptr(best),
+                                     ptr(total), ptr(cand_rows), ptr(cand), ptr(centers),
+                                     ptr(indices), c, d, s), "kmb_kpp_select")
+            cur = nxt
+        return centers.T, indices
+
+    # ---- row shards: every rank scans its own rows; per round one all-gather of the local
+    # potentials and candidates and one all-reduce of the t candidate potentials, no host sync
+    world, me = dist.world_size(), dist.rank()
+    first_row = torch.zeros(d, dtype=dt, device=dev)
+    if row0 <= first < row0 + n:
+        first_row.copy_(X[first - row0])
+    dist.all_reduce_sum_(first_row)
+    check(lib.kmb_kpp_init(code, ptr(X), ptr(w), first, ptr(first_row), ptr(M[0]), ptr(bsum[0]),
+                           ptr(centers), ptr(indices), n, d, s), "kmb_kpp_init")
+    pots64 = torch.empty(t, dtype=torch.float64, device=dev)
+    check(lib.kmb_kpp_potentials(ptr(bsum[0]), 1, nb, ptr(pots64), s), "kmb_kpp_potentials")
+    local_tot = pots64[:1].clone()                       # this shard's share of the potential
+    glob = dist.all_reduce_sum_(pots64[:1].clone())
+    total.copy_(glob.to(dt))
+    rows_off = torch.tensor([sum(counts[:r]) for r in range(world)], dtype=torch.int64, device=dev)
     cur = 0
     for c in range(1, k):
         nxt = 1 - cur
+        shares = dist.all_gather_cat(local_tot)                      # (world,) float64
+        ends = torch.cumsum(shares, 0)
+        offset = (ends[me] - shares[me]).reshape(1).to(dt)
         check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
-                                 ptr(u[c - 1]), t, ptr(cand), n, s), "kmb_kpp_sample")
+                                 ptr(u[c - 1]), ptr(offset), t, ptr(cand), n, s), "kmb_kpp_sample")
         check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),
               "kmb_gather_rows")
-        check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(cand_rows), ptr(M[cur]), ptr(best),
+        # owner of trial tau: first shard whose inclusive prefix reaches r = u * total
+        r = (u[c - 1] * total[0]).to(torch.float64)
+        owner = torch.clamp((ends.reshape(1, -1) < r.reshape(-1, 1)).sum(dim=1), max=world - 1)
+        all_cand = dist.all_gather_cat(cand.reshape(1, t)).to(torch.int64)          # (world, t)
+        all_rows = dist.all_gather_cat(cand_rows.reshape(1, t, d))                   # (world, t, d)
+        sel = owner.reshape(1, t)
+        cand_glob = (torch.gather(all_cand, 0, sel)[0] + rows_off[owner]).to(torch.int32).contiguous()
+        rows_glob = torch.gather(all_rows, 0, owner.reshape(1, t, 1).expand(1, t, d))[0].contiguous()
+        check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(rows_glob), ptr(M[cur]), ptr(best),
                                ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
-        check(lib.kmb_kpp_select(code, ptr(bsum[nxt]), t, nb, ptr(pots), ptr(best), ptr(total),
-                                 ptr(cand_rows), ptr(cand), ptr(centers), ptr(indices), c, d, s),
-              "kmb_kpp_select")
+        check(lib.kmb_kpp_potentials(ptr(bsum[nxt]), t, nb, ptr(pots64), s), "kmb_kpp_potentials")
+        local_pots = pots64.clone()
+        dist.all_reduce_sum_(pots64)
+        check(lib.kmb_kpp_select(code, None, ptr(pots64), t, nb, ptr(pots), ptr(best), ptr(total),
+                                 ptr(rows_glob), ptr(cand_glob), ptr(centers), ptr(indices), c, d,
+                                 s), "kmb_kpp_select")
+        local_tot = local_pots.gather(0, best.to(torch.int64))
         cur = nxt
     return centers.T, indices

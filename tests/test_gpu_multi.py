@@ -38,8 +38,8 @@ def _rank_main(rank, world, port, queue):
         import torch.distributed as tdist
 
         from sklearn_numba_dpex_b200 import dist as kdist
-        from sklearn_numba_dpex_b200.kmeans.drivers import (get_labels_inertia, lloyd,
-                                                            prepare_data_for_lloyd)
+        from sklearn_numba_dpex_b200.kmeans.drivers import (get_labels_inertia, kmeans_plusplus,
+                                                            lloyd, prepare_data_for_lloyd)
 
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
@@ -49,8 +49,9 @@ def _rank_main(rank, world, port, queue):
             Xd, wd, Cd = (torch.as_tensor(a).to(dev) for a in (X, w, init))
             X_t, mean, init_t, tol, uni = prepare_data_for_lloyd(Xd.T, Cd.T, 1e-4, wd, True)
             labels, inertia, C_t, n_iter = lloyd(X_t, wd, init_t, uni, 6, False, 0.0)
+            kpp_C, kpp_idx = kmeans_plusplus(Xd.T, wd, 40, np.random.RandomState(5))
             single = (labels.cpu().numpy(), float(inertia), C_t.T.cpu().numpy(), n_iter,
-                      mean.cpu().numpy(), float(tol))
+                      mean.cpu().numpy(), float(tol), kpp_idx.cpu().numpy(), kpp_C.T.cpu().numpy())
         tdist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
         kdist.enable()
         start, stop = kdist.shard_bounds(X.shape[0], rank, world)
@@ -61,9 +62,14 @@ def _rank_main(rank, world, port, queue):
         labels, inertia, C_t, n_iter = lloyd(X_t, ws, init_t, uni, 6, False, 0.0)
         all_labels = kdist.all_gather_cat(labels.to(torch.int64)).cpu().numpy()
         _, score = get_labels_inertia(X_t, C_t, ws, True)
+        Xraw = torch.as_tensor(X[start:stop]).to(dev)
+        kpp_C, kpp_idx = kmeans_plusplus(Xraw.T, ws, 40, np.random.RandomState(5))
         out = None
         if rank == 0:
-            s_labels, s_inertia, s_C, s_iter, s_mean, s_tol = single
+            s_labels, s_inertia, s_C, s_iter, s_mean, s_tol, s_kpp_idx, s_kpp_C = single
+            # sharded k-means++: same random stream, same candidates, same centres
+            np.testing.assert_array_equal(kpp_idx.cpu().numpy(), s_kpp_idx)
+            np.testing.assert_allclose(kpp_C.T.cpu().numpy(), s_kpp_C)
             np.testing.assert_allclose(mean.cpu().numpy(), s_mean, rtol=1e-5, atol=1e-6)
             np.testing.assert_allclose(float(tol), s_tol, rtol=1e-5)
             assert n_iter == s_iter
