@@ -65,14 +65,27 @@ class LloydState:
     reference allocates the same set once per call).  `step()` is what the benchmark times."""
 
     def __init__(self, X, sample_weight, centers, algo=ALGO_AUTO):
-        self.X = X
-        self.w = sample_weight
         n, d = X.shape
         k = centers.shape[0]
-        self.n, self.d, self.k = n, d, k
         dev, dt = X.device, X.dtype
         self.dtype = dtype_code(dt)
-        self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, _algo_code(algo), n, d, k),
+        self.d_orig = d
+        want = _algo_code(algo)
+        # The tensor-core step moves sample tiles with TMA, whose row pitch must be a multiple
+        # of 16 bytes: when it is wanted and d is not a multiple of 4, work on a copy of the
+        # samples and centres padded with zero features (distances and sums are unchanged).
+        d4 = (d + 3) // 4 * 4
+        if (dt == torch.float32 and d4 != d and want != ALGO_NAMES["cuda_core"]
+                and lib.kmb_lloyd_resolve_algo(self.dtype, want, n, d4, k) == ALGO_NAMES["tf32x3"]):
+            Xp = torch.zeros((n, d4), dtype=dt, device=dev)
+            Xp[:, :d] = X
+            Cp = torch.zeros((k, d4), dtype=dt, device=dev)
+            Cp[:, :d] = centers
+            X, centers, d = Xp, Cp, d4
+        self.X = X
+        self.w = sample_weight
+        self.n, self.d, self.k = n, d, k
+        self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, want, n, d, k),
                           "kmb_lloyd_resolve_algo")
         self.acc_len = lib.kmb_lloyd_acc_len(d, k)
         self.n_copies = check(lib.kmb_lloyd_acc_copies(self.dtype, self.algo, n, d, k))
@@ -174,6 +187,12 @@ class LloydState:
         self.check_device_waits()
         return self.labels, total
 
+    def centers(self):
+        """Current centroids (k, d) without the padding features, contiguous."""
+        if self.d == self.d_orig:
+            return self.C
+        return self.C[:, : self.d_orig].contiguous()
+
     def check_device_waits(self):
         """Raises if a bounded wait inside the tensor-core kernel ran out on this workspace."""
         if self.algo != ALGO_NAMES["tf32x3"]:
@@ -269,7 +288,7 @@ def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, ve
 
     labels, total = state.final_labels_inertia()
     inertia = total.cpu().numpy()[0]
-    return labels, inertia, state.C.T, n_iteration
+    return labels, inertia, state.centers().T, n_iteration
 
 
 # ---------------------------------------------------------------------------- top-k
