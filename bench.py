@@ -38,6 +38,10 @@ CONFIGS = {
                desc="KMeans fp64 n=2M d=32 k=64, U[0,1] data, random-row init seed 3, tol=0"),
     "c1": dict(n=50_000, d=14, k=127, dtype="f32", noise=1.0, spread=None, seed=0,
                desc="KMeans fp32 n=50k d=14 k=127 blobs"),
+    "c5": dict(n=20_000_000, d=64, k=4096, dtype="f32", noise=0.1, spread=None, seed=4,
+               blobs=512, outliers=0.1, box=50.0,
+               desc="KMeans fp32 n=20M d=64 k=4096: 90% from 512 tight blobs (std 0.1), 10% uniform "
+                    "outliers in [-50,50]^64, k-means++ from seed 4"),
 }
 CHUNK = 1 << 20
 
@@ -88,7 +92,9 @@ def measure_tf32_cublas(torch, device, size=8192, reps=10):
 # ----------------------------------------------------------------------------- data
 def cluster_offsets(cfg, torch, device):
     g = torch.Generator(device="cpu").manual_seed(cfg["seed"] * 7919 + 1)
-    d, k = cfg["d"], cfg["k"]
+    d, k = cfg["d"], cfg.get("blobs", cfg["k"])
+    if "box" in cfg:
+        return ((torch.rand((k, d), generator=g) * 2.0 - 1.0) * cfg["box"]).to(device)
     if cfg["spread"] is not None:
         off = torch.randn((k, d), generator=g) * cfg["spread"]
     else:
@@ -111,9 +117,14 @@ def generate_rows(cfg, start, stop, torch, device, dtype):
         if cfg["noise"] is None:
             block = torch.rand((hi - lo, d), generator=g, device=device, dtype=dtype)
         else:
-            ids = torch.randint(0, k, (hi - lo,), generator=g, device=device)
+            ids = torch.randint(0, offsets.shape[0], (hi - lo,), generator=g, device=device)
             block = torch.randn((hi - lo, d), generator=g, device=device, dtype=dtype) * cfg["noise"]
             block += offsets[ids]
+            if "outliers" in cfg:
+                out_rows = torch.rand((hi - lo,), generator=g, device=device) < cfg["outliers"]
+                uni = (torch.rand((hi - lo, d), generator=g, device=device, dtype=dtype) * 2 - 1) * cfg["box"]
+                block = torch.where(out_rows[:, None], uni, block)
+                del uni
         a, b = max(start, lo) - lo, min(stop, hi) - lo
         out[pos:pos + (b - a)] = block[a:b]
         pos += b - a
@@ -384,7 +395,7 @@ def run_gpu_arm(args, cfg):
             peak = peaks["bf16_tflops"] / 6.0
             peak_sust = peaks["bf16_tflops_sustained"] / 6.0
             # DRAM bytes per sample row of the d=128 kernel from the ncu capture of n=1M
-            # (profiles/lloyd_tc_kernel_c3_n1m_ncu_full.md), which grow in proportion to n
+            # (summary kept with the other ncu summaries of this repository), growing in proportion to n
             traffic = 539.6 * n_local if d == 128 else None
             roofline = {"bound": "tensor", "achieved": tf_achieved, "peak": peak, "unit": "TFLOP/s",
                         "frac": tf_achieved / peak, "traffic": traffic,
@@ -420,6 +431,57 @@ def run_gpu_arm(args, cfg):
         tdist.destroy_process_group()
 
 
+def run_fit_arm(args, cfg):
+    """Whole-fit timing through the drivers: k-means++ seeding then `steps` Lloyd iterations
+    (tol=0), rows sharded over the ranks.  Used for the seeding / relocation stress
+    configuration; prints its own JSON line (not the headline metric)."""
+    import torch
+    import torch.distributed as tdist
+
+    from sklearn_numba_dpex_b200 import dist as kdist
+    from sklearn_numba_dpex_b200.kmeans.drivers import kmeans_plusplus, lloyd
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        tdist.init_process_group("nccl", device_id=device)
+        kdist.enable()
+    dtype = torch.float32 if cfg["dtype"] == "f32" else torch.float64
+    n, d, k = cfg["n"], cfg["d"], cfg["k"]
+    start, stop = kdist.shard_bounds(n, rank, world)
+    X = generate_rows(cfg, start, stop, torch, device, dtype)
+    w = torch.ones(X.shape[0], dtype=dtype, device=device)
+
+    def sync():
+        if world > 1:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    sync()
+    t0 = time.perf_counter()
+    centers_t, indices = kmeans_plusplus(X.T, w, k, np.random.RandomState(cfg["seed"]))
+    sync()
+    t1 = time.perf_counter()
+    labels, inertia, C_t, n_iter = lloyd(X.T, w, centers_t, True, args.steps, False, 0.0, algo=args.algo)
+    sync()
+    t2 = time.perf_counter()
+    distinct = int(torch.unique(indices).numel())
+    if rank == 0:
+        print(json.dumps({
+            "mode": "fit", "n_gpus": world, "config": {"workload": cfg["desc"], "n": n, "d": d, "k": k},
+            "kmeanspp_seconds": t1 - t0, "kmeanspp_rounds_per_s": (k - 1) / (t1 - t0),
+            "kmeanspp_distinct_centres": distinct,
+            "lloyd_seconds_incl_final_pass": t2 - t1, "lloyd_iterations": int(n_iter),
+            "lloyd_iterations_per_s": n_iter / (t2 - t1), "inertia": float(inertia),
+            "data": "synthetic"}), flush=True)
+    if world > 1:
+        tdist.barrier()
+        tdist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,6 +492,8 @@ def main():
     ap.add_argument("--n", type=int, default=None, help="override the number of samples")
     ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
     ap.add_argument("--cpu-sample-rows", type=int, default=200_000)
+    ap.add_argument("--mode", default="step", choices=["step", "fit"],
+                    help="step: the headline per-iteration benchmark; fit: k-means++ + Lloyd")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
@@ -439,6 +503,8 @@ def main():
         cfg["desc"] += f" [n overridden to {args.n}]"
     if args.impl == "reference":
         run_reference_arm(args, cfg)
+    elif args.mode == "fit":
+        run_fit_arm(args, cfg)
     else:
         run_gpu_arm(args, cfg)
 

@@ -271,7 +271,7 @@ def test_kmeans_plusplus_matches_oracle(dtype, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_full_fit_matches_oracle_c1_shape(dtype):
-    """BASELINE config 1 (n=50 000, d=14, k=127 blobs, k-means++ from seed 0, tol=0) at a
+    """The n=50 000, d=14, k=127 blob configuration (k-means++ from seed 0, tol=0) at a
     bounded iteration count: the CUDA path and the oracle are started from the same initial
     centres and compared after every iteration is forced to the same labels (teacher
     forcing is implicit: the data are well separated, so labels agree exactly)."""
