@@ -490,6 +490,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--n", type=int, default=None, help="override the number of samples")
+    ap.add_argument("--k", type=int, default=None, help="override the number of clusters")
     ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
     ap.add_argument("--cpu-sample-rows", type=int, default=200_000)
     ap.add_argument("--mode", default="step", choices=["step", "fit"],
@@ -501,6 +502,9 @@ def main():
     if args.n:
         cfg["n"] = args.n
         cfg["desc"] += f" [n overridden to {args.n}]"
+    if args.k:
+        cfg["k"] = args.k
+        cfg["desc"] += f" [k overridden to {args.k}]"
     if args.impl == "reference":
         run_reference_arm(args, cfg)
     elif args.mode == "fit":

@@ -1,6 +1,7 @@
 // Shared helpers for the kmb200 kernels (sm_100a only).
 #pragma once
 #include <cuda_runtime.h>
+#include <cuda_pipeline.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
@@ -68,6 +69,67 @@ inline int lanes_per_row(int d) {
   int g = 1;
   while (g < d && g < 32) g <<= 1;
   return g;
+}
+
+// 16-byte vectors of consecutive features: 4 floats or 2 doubles per lane.
+template <typename T>
+struct RowVec;
+template <>
+struct RowVec<float> {
+  static constexpr int VEC = 4;
+};
+template <>
+struct RowVec<double> {
+  static constexpr int VEC = 2;
+};
+
+// Lanes per sample row when every lane takes one 16-byte vector: the smallest power of two
+// >= ceil(d / VEC), capped at 32 (longer rows take several trips).
+inline int vec_lanes_per_row(int d, int vec) {
+  const int need = (d + vec - 1) / vec;
+  int g = 1;
+  while (g < need && g < 32) g <<= 1;
+  return g;
+}
+
+// v[j] = p[f0 + j] for f0 + j < d, else 0.  `aligned` = the row pitch and the base pointer
+// allow one 16-byte load (d a multiple of VEC, base 16-byte aligned).
+template <typename T>
+__device__ __forceinline__ void load_row_vec(const T* __restrict__ p, int f0, int d, bool aligned,
+                                             T (&v)[RowVec<T>::VEC]) {
+  constexpr int VEC = RowVec<T>::VEC;
+  if (aligned && f0 + VEC <= d) {
+    if constexpr (sizeof(T) == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(p + f0);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+      const double2 q = *reinterpret_cast<const double2*>(p + f0);
+      v[0] = q.x; v[1] = q.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) v[j] = (f0 + j < d) ? p[f0 + j] : T(0);
+  }
+}
+
+// Copies rows [r0, r0 + rows) of X (rows x d, contiguous) to shared memory.  The tile starts
+// on a 16-byte boundary when X does and r0 is a multiple of 4; a ragged tail goes by plain
+// loads.  Every thread commits exactly one group per call (possibly empty).
+template <typename T, int THREADS>
+__device__ __forceinline__ void issue_row_tile(T* __restrict__ dst, const T* __restrict__ X,
+                                               int64_t r0, int rows, int d, bool base_aligned) {
+  if (rows > 0) {
+    const size_t bytes = (size_t)rows * d * sizeof(T);
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(X + r0 * (int64_t)d);
+    unsigned char* out = reinterpret_cast<unsigned char*>(dst);
+    const size_t vec_bytes = base_aligned ? (bytes & ~(size_t)15) : 0;
+    for (size_t off = (size_t)threadIdx.x * 16; off < vec_bytes; off += (size_t)THREADS * 16)
+      __pipeline_memcpy_async(out + off, src + off, 16);
+    for (size_t off = vec_bytes + threadIdx.x * sizeof(T); off < bytes;
+         off += (size_t)THREADS * sizeof(T))
+      *reinterpret_cast<T*>(out + off) = *reinterpret_cast<const T*>(src + off);
+  }
+  __pipeline_commit();
 }
 
 template <typename T>

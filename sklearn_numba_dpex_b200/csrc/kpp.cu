@@ -9,54 +9,131 @@
 
 namespace kmb {
 
-constexpr int KPP_BLOCK = 2048;   // rows per partial-sum block
-constexpr int KPP_THREADS = 256;
+constexpr int KPP_BLOCK = 512;    // rows per partial-sum block (one CTA each)
+constexpr int KPP_THREADS = 128;
 constexpr int KPP_MAX_T = 16;     // 2 + ln(k) stays below 16 for k < 1.2e6
 
-__device__ __forceinline__ double group_sum_kpp(double v, int G) {
-  for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
+// One pass over the samples for up to TT candidates at once:
+//   M_out[tau, i] = min(w_i * ||cand_tau - x_i||^2, closest_i)     (no min when closest == NULL)
+//   bsum_out[tau, block] = float64 sum of the block's values.
+// A CTA owns KPP_BLOCK consecutive rows and streams them through shared memory in tiles of
+// KPP_THREADS / G rows with 16-byte asynchronous copies (KPP_STAGES tiles in flight), so the
+// bytes outstanding per SM do not depend on the register budget of the arithmetic.  One row
+// belongs to G adjacent threads (G = 1 unless rows are long); a thread walks its 16-byte
+// chunks in an order rotated by the row number, which keeps both the tile reads and the
+// candidate reads free of bank conflicts, and keeps one running sum per candidate in
+// registers: no reduction across lanes for G = 1, one or two shuffles otherwise.
+constexpr int KPP_STAGES = 2;
+
+// Threads per row: rows longer than 256 bytes are split over 2 or 4 threads so that a tile
+// of KPP_THREADS / G rows stays around 32 KB.
+inline int kpp_threads_per_row(int d, size_t esize) {
+  const size_t row_bytes = (size_t)d * esize;
+  return row_bytes <= 256 ? 1 : (row_bytes <= 512 ? 2 : 4);
 }
 
-// closest[i] = w_i * ||x_i - x_first||^2 ; bsum[block] = float64 sum.
-template <typename T>
+template <typename T, int TT>
 __global__ void __launch_bounds__(KPP_THREADS)
-kpp_init_kernel(const T* __restrict__ X, const T* __restrict__ w, int64_t first,
-                const T* __restrict__ first_row, T* __restrict__ closest, double* __restrict__ bsum, T* __restrict__ centers,
-                int32_t* __restrict__ indices, int64_t n, int d, int G) {
+kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ cand_rows,
+                const T* __restrict__ M_prev, const int32_t* __restrict__ best_prev,
+                T* __restrict__ M_out, double* __restrict__ bsum_out, T* __restrict__ centers0,
+                int64_t n, int d, int t, int64_t nb, int G, int aligned, int c_elems) {
+  constexpr int VEC = RowVec<T>::VEC;
   __shared__ double red[32];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
-  T* c = reinterpret_cast<T*>(dyn_smem);
-  for (int f = threadIdx.x; f < d; f += KPP_THREADS)
-    c[f] = first_row ? first_row[f] : X[first * (int64_t)d + f];
-  __syncthreads();
-  if (blockIdx.x == 0) {
-    for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers[f] = c[f];
-    if (threadIdx.x == 0) indices[0] = (int32_t)first;
-  }
-  const int rows_per_pass = KPP_THREADS / G;
-  const int g = threadIdx.x / G, l = threadIdx.x % G;
+  T* c = reinterpret_cast<T*>(dyn_smem);              // t x d candidates (c_elems, 16B multiple)
+  T* tiles = c + c_elems;                             // KPP_STAGES x (R x d)
+  const int R = KPP_THREADS / G;                      // rows per tile
+  const size_t tile_elems = (size_t)R * d;
   const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
-  double acc = 0.0;
-  for (int r = 0; r < KPP_BLOCK; r += rows_per_pass) {
-    const int64_t i = b0 + r + g;
-    T s = T(0);
-    if (i < n) {
-      const T* x = X + i * (int64_t)d;
-      for (int f = l; f < d; f += G) {
-        const T diff = x[f] - c[f];
-        s = fma(diff, diff, s);
+  const int n_tiles = KPP_BLOCK / R;
+  const bool base_aligned = (((uintptr_t)X) & 15) == 0;
+
+#pragma unroll
+  for (int sidx = 0; sidx < KPP_STAGES; ++sidx) {
+    const int64_t r0 = b0 + (int64_t)sidx * R;
+    const int rows = (sidx < n_tiles && r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
+    issue_row_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, base_aligned);
+  }
+  for (int e = threadIdx.x; e < t * d; e += KPP_THREADS) c[e] = cand_rows[e];
+  if (centers0 != nullptr && blockIdx.x == 0)
+    for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers0[f] = cand_rows[f];
+  const T* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
+  const int r = threadIdx.x / G, li = threadIdx.x % G;   // row in the tile, part of the row
+  const int nq = (d + VEC - 1) / VEC;                     // 16-byte chunks per row
+  const bool vec_ok = aligned != 0;                       // d % VEC == 0: rows in smem stay aligned
+  double acc[TT];
+#pragma unroll
+  for (int tau = 0; tau < TT; ++tau) acc[tau] = 0.0;
+
+  for (int tix = 0; tix < n_tiles; ++tix) {
+    __pipeline_wait_prior(KPP_STAGES - 1);
+    __syncthreads();
+    const T* row = tiles + (tix % KPP_STAGES) * tile_elems + (size_t)r * d;
+    const int64_t i = b0 + (int64_t)tix * R + r;
+    const bool valid = i < n;
+    // fetched first, so that their latency hides behind the distance arithmetic
+    const T wi = (valid && w) ? w[i] : T(1);
+    const T cl = (valid && closest) ? closest[i] : inf_value<T>();
+    T s[TT];
+#pragma unroll
+    for (int tau = 0; tau < TT; ++tau) s[tau] = T(0);
+    int qq = (li + r) % nq;                               // rotated start: conflict-free reads
+    for (int q = li; q < nq; q += G) {
+      const int f0 = qq * VEC;
+      T xv[VEC];
+      load_row_vec<T>(row, f0, d, vec_ok, xv);
+#pragma unroll
+      for (int tau = 0; tau < TT; ++tau) {
+        if (tau < t) {
+          T cv[VEC];
+          load_row_vec<T>(c + tau * d, f0, d, vec_ok, cv);
+#pragma unroll
+          for (int jj = 0; jj < VEC; ++jj) {
+            const T diff = cv[jj] - xv[jj];
+            s[tau] = fma(diff, diff, s[tau]);
+          }
+        }
+      }
+      qq += G;
+      if (qq >= nq) qq -= nq;
+    }
+    if (G > 1) {
+#pragma unroll
+      for (int tau = 0; tau < TT; ++tau) {
+        if (tau < t) {
+          s[tau] += __shfl_xor_sync(0xffffffffu, s[tau], 1);
+          if (G > 2) s[tau] += __shfl_xor_sync(0xffffffffu, s[tau], 2);
+        }
       }
     }
-    const double sd = group_sum_kpp((double)s, G);
-    if (i < n && l == 0) {
-      const T v = (T)sd * (w ? w[i] : T(1));
-      closest[i] = v;
-      acc += (double)v;
+    if (valid && li == 0) {
+      T* out = M_out + i;
+#pragma unroll
+      for (int tau = 0; tau < TT; ++tau) {
+        if (tau < t) {
+          T v = s[tau] * wi;
+          v = (v < cl) ? v : cl;
+          *out = v;
+          out += n;
+          acc[tau] += (double)v;
+        }
+      }
+    }
+    __syncthreads();
+    const int nxt = tix + KPP_STAGES;
+    const int64_t rn = b0 + (int64_t)nxt * R;
+    const int rows = (nxt < n_tiles && rn < n) ? (int)((n - rn < R) ? (n - rn) : R) : 0;
+    issue_row_tile<T, KPP_THREADS>(tiles + (nxt % KPP_STAGES) * tile_elems, X, rn, rows, d, base_aligned);
+  }
+  __pipeline_wait_prior(0);
+#pragma unroll
+  for (int tau = 0; tau < TT; ++tau) {
+    if (tau < t) {
+      const double tot = block_sum(acc[tau], red);
+      if (threadIdx.x == 0) bsum_out[(int64_t)tau * nb + blockIdx.x] = tot;
     }
   }
-  const double tot = block_sum(acc, red);
-  if (threadIdx.x == 0) bsum[blockIdx.x] = tot;
 }
 
 // One CTA per trial.  r = u * total; walk the block sums, then the elements of the block
@@ -156,68 +233,6 @@ __global__ void gather_rows_kernel(const T* __restrict__ X, const int32_t* __res
     out[(int64_t)blockIdx.x * d + f] = X[row * (int64_t)d + f];
 }
 
-// M_out[tau, i] = min(w_i * ||cand_tau - x_i||^2, closest_i); bsum_out[tau, block].
-template <typename T>
-__global__ void __launch_bounds__(KPP_THREADS)
-kpp_step_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ cand_rows,
-                const T* __restrict__ M_prev, const int32_t* __restrict__ best_prev,
-                T* __restrict__ M_out, double* __restrict__ bsum_out, int64_t n, int d, int t,
-                int64_t nb, int G) {
-  __shared__ double red[32];
-  extern __shared__ __align__(16) unsigned char dyn_smem[];
-  T* c = reinterpret_cast<T*>(dyn_smem);  // t x d
-  for (int e = threadIdx.x; e < t * d; e += KPP_THREADS) c[e] = cand_rows[e];
-  __syncthreads();
-  const T* closest = M_prev + (int64_t)(best_prev ? *best_prev : 0) * n;
-  const int rows_per_pass = KPP_THREADS / G;
-  const int g = threadIdx.x / G, l = threadIdx.x % G;
-  const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
-  double acc[KPP_MAX_T];
-#pragma unroll
-  for (int tau = 0; tau < KPP_MAX_T; ++tau) acc[tau] = 0.0;
-
-  for (int r = 0; r < KPP_BLOCK; r += rows_per_pass) {
-    const int64_t i = b0 + r + g;
-    T s[KPP_MAX_T];
-#pragma unroll
-    for (int tau = 0; tau < KPP_MAX_T; ++tau) s[tau] = T(0);
-    if (i < n) {
-      const T* x = X + i * (int64_t)d;
-      for (int f = l; f < d; f += G) {
-        const T xv = x[f];
-#pragma unroll
-        for (int tau = 0; tau < KPP_MAX_T; ++tau) {
-          if (tau < t) {
-            const T diff = c[tau * d + f] - xv;
-            s[tau] = fma(diff, diff, s[tau]);
-          }
-        }
-      }
-    }
-    const T wi = (i < n) ? (w ? w[i] : T(1)) : T(0);
-    const T cl = (i < n) ? closest[i] : T(0);
-#pragma unroll
-    for (int tau = 0; tau < KPP_MAX_T; ++tau) {
-      if (tau < t) {
-        const double sd = group_sum_kpp((double)s[tau], G);
-        if (i < n && l == 0) {
-          T v = (T)sd * wi;
-          v = (v < cl) ? v : cl;
-          M_out[(int64_t)tau * n + i] = v;
-          acc[tau] += (double)v;
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int tau = 0; tau < KPP_MAX_T; ++tau) {
-    if (tau < t) {
-      const double tot = block_sum(acc[tau], red);
-      if (threadIdx.x == 0) bsum_out[(int64_t)tau * nb + blockIdx.x] = tot;
-    }
-  }
-}
-
 // Single CTA: potentials in fixed order, argmin (lowest trial on ties), commit the centre.
 template <typename T>
 __global__ void __launch_bounds__(KPP_THREADS)
@@ -272,6 +287,34 @@ kpp_potentials_kernel(const double* __restrict__ bsum, int64_t nb, double* __res
   if (threadIdx.x == 0) pots[blockIdx.x] = tot;
 }
 
+// Launches kpp_scan_kernel with the instantiation that fits t and the dtype.
+template <typename T>
+static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* M_prev,
+                           const int32_t* best_prev, T* M_out, double* bsum_out, T* centers0,
+                           int64_t n, int d, int t, cudaStream_t stream) {
+  constexpr int VEC = RowVec<T>::VEC;
+  const int G = kpp_threads_per_row(d, sizeof(T));
+  const int R = KPP_THREADS / G;
+  const int64_t nb = ceil_div(n, KPP_BLOCK);
+  const int c_elems = (int)(((size_t)t * d * sizeof(T) + 15) / 16 * 16 / sizeof(T));
+  const size_t dyn = ((size_t)c_elems + (size_t)KPP_STAGES * R * d) * sizeof(T);
+  KMB_REQUIRE(dyn <= 200 * 1024, "k-means++ pass: rows too long for the staged tiles (d=%d, t=%d)", d, t);
+  const int aligned = (d % VEC == 0) ? 1 : 0;
+  auto run = [&](auto kern) -> int {
+    if (dyn > 48 * 1024)
+      KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    kern<<<(unsigned)nb, KPP_THREADS, dyn, stream>>>(X, w, cand_rows, M_prev, best_prev, M_out,
+                                                     bsum_out, centers0, n, d, t, nb, G, aligned,
+                                                     c_elems);
+    KMB_CHECK_LAUNCH();
+    return KMB_OK;
+  };
+  if (t <= 1) return run(kpp_scan_kernel<T, 1>);
+  if (t <= 8) return run(kpp_scan_kernel<T, 8>);
+  if (t <= 12) return run(kpp_scan_kernel<T, 12>);
+  return run(kpp_scan_kernel<T, KPP_MAX_T>);
+}
+
 }  // namespace kmb
 
 using namespace kmb;
@@ -287,17 +330,14 @@ int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, const v
   KMB_REQUIRE(n > 0 && d > 0 && first >= 0 && (first_row != nullptr || first < n),
               "kmb_kpp_init: bad sizes");
   KMB_REQUIRE(n < (1ll << 31), "kmb_kpp_init: n must be below 2^31 (int32 candidate ids)");
-  const int G = lanes_per_row(d);
-  const int64_t nb = ceil_div(n, KPP_BLOCK);
+  const int32_t first32 = (int32_t)first;
+  KMB_CHECK_CUDA(cudaMemcpyAsync(indices, &first32, sizeof(int32_t), cudaMemcpyHostToDevice,
+                                 (cudaStream_t)stream));
   KMB_DISPATCH_DTYPE(dtype, {
-    const size_t dyn = (size_t)d * sizeof(T);
-    KMB_REQUIRE(dyn <= 48 * 1024, "kmb_kpp_init: d too large (%d)", d);
-    kpp_init_kernel<T><<<(unsigned)nb, KPP_THREADS, dyn, (cudaStream_t)stream>>>(
-        (const T*)X, (const T*)w, first, (const T*)first_row, (T*)closest, bsum, (T*)centers, indices,
-        n, d, G);
-    KMB_CHECK_LAUNCH();
+    const T* row = first_row ? (const T*)first_row : (const T*)X + first * (int64_t)d;
+    return launch_kpp_scan<T>((const T*)X, (const T*)w, row, nullptr, nullptr, (T*)closest, bsum,
+                              (T*)centers, n, d, 1, (cudaStream_t)stream);
   });
-  return KMB_OK;
 }
 
 int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
@@ -330,20 +370,11 @@ int kmb_kpp_step(int dtype, const void* X, const void* w, const void* cand_rows,
   KMB_REQUIRE(X && cand_rows && M_prev && M_out && bsum_out, "kmb_kpp_step: NULL argument");
   KMB_REQUIRE(n > 0 && d > 0 && t > 0 && t <= KPP_MAX_T, "kmb_kpp_step: bad sizes (t <= %d)",
               KPP_MAX_T);
-  const int G = lanes_per_row(d);
-  const int64_t nb = ceil_div(n, KPP_BLOCK);
   KMB_DISPATCH_DTYPE(dtype, {
-    const size_t dyn = (size_t)t * d * sizeof(T);
-    KMB_REQUIRE(dyn <= 96 * 1024, "kmb_kpp_step: t*d too large (%d x %d)", t, d);
-    auto kern = kpp_step_kernel<T>;
-    if (dyn > 48 * 1024)
-      KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    kern<<<(unsigned)nb, KPP_THREADS, dyn, (cudaStream_t)stream>>>(
-        (const T*)X, (const T*)w, (const T*)cand_rows, (const T*)M_prev, best_prev, (T*)M_out,
-        bsum_out, n, d, t, nb, G);
-    KMB_CHECK_LAUNCH();
+    return launch_kpp_scan<T>((const T*)X, (const T*)w, (const T*)cand_rows, (const T*)M_prev,
+                              best_prev, (T*)M_out, bsum_out, (T*)nullptr, n, d, t,
+                              (cudaStream_t)stream);
   });
-  return KMB_OK;
 }
 
 int kmb_kpp_potentials(const double* bsum, int t, int64_t nb, double* pots, void* stream) {

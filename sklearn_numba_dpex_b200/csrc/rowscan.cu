@@ -17,34 +17,88 @@ __device__ __forceinline__ double group_sum(double v, int G) {
 }
 
 // per_sample[i] = w_i * sum_f (x - c[label])^2 ; partial[b] = float64 block sum.
+// Rows stream through shared memory in tiles (two in flight, 16-byte asynchronous copies);
+// one row belongs to G adjacent threads, each walking its 16-byte chunks in an order rotated
+// by the row number (conflict-free tile reads); the row's centroid is gathered from L2.
+constexpr int IN_THREADS = 128;
+constexpr int IN_STAGES = 2;
+
+inline int inertia_threads_per_row(int d, size_t esize) {
+  const size_t row_bytes = (size_t)d * esize;
+  return row_bytes <= 256 ? 1 : (row_bytes <= 512 ? 2 : 4);
+}
+
 template <typename T>
-__global__ void __launch_bounds__(RS_THREADS)
+__global__ void __launch_bounds__(IN_THREADS)
 inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ C,
                const uint32_t* __restrict__ labels, T* __restrict__ per_sample,
-               double* __restrict__ partial, int64_t n, int d, int G) {
+               double* __restrict__ partial, int64_t n, int d, int k, int G, int aligned,
+               int64_t n_tiles_total) {
+  constexpr int VEC = RowVec<T>::VEC;
   __shared__ double red[32];
-  const int rows_per_block = RS_THREADS / G;
-  const int g = threadIdx.x / G, l = threadIdx.x % G;
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  T* tiles = reinterpret_cast<T*>(dyn_smem);          // IN_STAGES x (R x d)
+  const int R = IN_THREADS / G;
+  const size_t tile_elems = (size_t)R * d;
+  const bool base_aligned = (((uintptr_t)X) & 15) == 0;
+  const int r = threadIdx.x / G, li = threadIdx.x % G;
+  const int nq = (d + VEC - 1) / VEC;
+  const bool vec_ok = aligned != 0;
   double block_acc = 0.0;
-  for (int64_t row0 = (int64_t)blockIdx.x * rows_per_block; row0 < n;
-       row0 += (int64_t)gridDim.x * rows_per_block) {
-    const int64_t i = row0 + g;
+
+  // this CTA's tiles: blockIdx, blockIdx + gridDim, ...
+  auto tile_rows = [&](int64_t tile) -> int {
+    const int64_t r0 = tile * R;
+    return (tile < n_tiles_total && r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
+  };
+#pragma unroll
+  for (int sidx = 0; sidx < IN_STAGES; ++sidx) {
+    const int64_t tile = (int64_t)blockIdx.x + (int64_t)sidx * gridDim.x;
+    issue_row_tile<T, IN_THREADS>(tiles + sidx * tile_elems, X, tile * R, tile_rows(tile), d,
+                                  base_aligned);
+  }
+  int slot = 0;
+  for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
+    __pipeline_wait_prior(IN_STAGES - 1);
+    __syncthreads();
+    const T* row = tiles + slot * tile_elems + (size_t)r * d;
+    const int64_t i = tile * R + r;
+    const bool valid = i < n;
+    const uint32_t lab = valid ? labels[i] : 0u;
+    const T wi = (valid && w) ? w[i] : T(1);
+    const T* crow = C + (int64_t)(lab < (uint32_t)k ? lab : 0u) * d;
+    const bool c_vec = vec_ok && ((((uintptr_t)C) & 15) == 0);
     T s = T(0);
-    if (i < n) {
-      const T* x = X + i * (int64_t)d;
-      const T* c = C + (int64_t)labels[i] * d;
-      for (int f = l; f < d; f += G) {
-        const T diff = x[f] - c[f];
+    int qq = (li + r) % nq;
+    for (int q = li; q < nq; q += G) {
+      const int f0 = qq * VEC;
+      T xv[VEC], cv[VEC];
+      load_row_vec<T>(row, f0, d, vec_ok, xv);
+      load_row_vec<T>(crow, f0, d, c_vec, cv);
+#pragma unroll
+      for (int jj = 0; jj < VEC; ++jj) {
+        const T diff = xv[jj] - cv[jj];
         s = fma(diff, diff, s);
       }
+      qq += G;
+      if (qq >= nq) qq -= nq;
     }
-    double sd = group_sum((double)s, G);
-    if (i < n && l == 0) {
-      const T v = (T)sd * (w ? w[i] : T(1));
+    if (G > 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if (G > 2) s += __shfl_xor_sync(0xffffffffu, s, 2);
+    }
+    if (valid && li == 0) {
+      const T v = s * wi;
       if (per_sample) per_sample[i] = v;
       block_acc += (double)v;
     }
+    __syncthreads();
+    const int64_t nxt = tile + (int64_t)IN_STAGES * gridDim.x;
+    issue_row_tile<T, IN_THREADS>(tiles + slot * tile_elems, X, nxt * R, tile_rows(nxt), d,
+                                  base_aligned);
+    slot = (slot + 1) % IN_STAGES;
   }
+  __pipeline_wait_prior(0);
   const double tot = block_sum(block_acc, red);
   if (threadIdx.x == 0 && partial) partial[blockIdx.x] = tot;
 }
@@ -243,8 +297,15 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
   KMB_REQUIRE(X && C && labels, "kmb_inertia: NULL argument");
   KMB_REQUIRE(n >= 0 && d > 0 && k > 0, "kmb_inertia: bad sizes");
   cudaStream_t s = (cudaStream_t)stream;
-  const int G = lanes_per_row(d);
-  const int grid = scan_grid(RS_THREADS / G, n > 0 ? n : 1);
+  const size_t esize = dtype == KMB_F32 ? 4 : 8;
+  const int G = inertia_threads_per_row(d, esize);
+  const int R = IN_THREADS / G;
+  const int64_t n_tiles = ceil_div(n > 0 ? n : 1, R);
+  const size_t dyn = (size_t)IN_STAGES * R * d * esize;
+  KMB_REQUIRE(dyn <= 200 * 1024, "kmb_inertia: rows too long for the staged tiles (d=%d)", d);
+  int64_t grid = (int64_t)sm_count() * (dyn > 64 * 1024 ? 1 : (dyn > 32 * 1024 ? 3 : 6));
+  if (grid > n_tiles) grid = n_tiles;
+  if (grid > RS_MAX_BLOCKS) grid = RS_MAX_BLOCKS;
   if (total) {
     if (workspace == nullptr || workspace_bytes < (size_t)grid * sizeof(double)) {
       set_error("kmb_inertia: workspace of %zu bytes needed, %zu given",
@@ -253,13 +314,17 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
     }
   }
   KMB_DISPATCH_DTYPE(dtype, {
-    inertia_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (const T*)w, (const T*)C, labels,
-                                                  (T*)per_sample, total ? (double*)workspace : nullptr,
-                                                  n, d, G);
+    const int aligned = (d % RowVec<T>::VEC == 0) ? 1 : 0;
+    auto kern = inertia_kernel<T>;
+    if (dyn > 48 * 1024)
+      KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    kern<<<(unsigned)grid, IN_THREADS, dyn, s>>>((const T*)X, (const T*)w, (const T*)C, labels,
+                                                 (T*)per_sample, total ? (double*)workspace : nullptr,
+                                                 n, d, k, G, aligned, n_tiles);
     KMB_CHECK_LAUNCH();
     if (total) {
-      sum_partials_kernel<T><<<1, 256, 0, s>>>((const double*)workspace, grid, grid, (T*)total,
-                                               nullptr);
+      sum_partials_kernel<T><<<1, 256, 0, s>>>((const double*)workspace, (int)grid, (int)grid,
+                                               (T*)total, nullptr);
       KMB_CHECK_LAUNCH();
     }
   });
