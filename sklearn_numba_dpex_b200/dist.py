@@ -82,6 +82,22 @@ def all_gather_cat(t):
     return torch.cat([piece[:length] for piece, length in zip(out, lengths)], dim=0)
 
 
+def all_gather_same(t):
+    """Concatenation over ranks along dim 0 of tensors that have the SAME shape on every rank:
+    one collective, no host round trip (use all_gather_cat when lengths may differ)."""
+    if not active():
+        return t
+    t = t.contiguous()
+    if t.is_cuda:
+        out = torch.empty((world_size() * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype,
+                          device=t.device)
+        tdist.all_gather_into_tensor(out, t, group=_STATE["group"])
+        return out
+    pieces = [torch.empty_like(t) for _ in range(world_size())]
+    tdist.all_gather(pieces, t, group=_STATE["group"])
+    return torch.cat(pieces, dim=0)
+
+
 def all_gather_object(obj):
     if not active():
         return [obj]
@@ -112,11 +128,11 @@ def check_same_across_ranks(**named_values):
 
 def merge_topk(values, global_idx, m):
     """Global top-m out of per-rank candidates.  `values` (c,) and `global_idx` (c,) are this
-    rank's candidates (c may differ per rank only through padding with -inf).  Returns the
+    rank's candidates; c is the same on every rank (pad with -inf / -1).  Returns the
     positions, in the gathered candidate list, of the m winners ordered by descending value
     then ascending global index, together with the gathered arrays."""
-    vals = all_gather_cat(values)
-    idx = all_gather_cat(global_idx)
+    vals = all_gather_same(values)
+    idx = all_gather_same(global_idx)
     # descending value, ascending index: stable sort on index first, then on value
     order = torch.argsort(idx, stable=True)
     order = order[torch.argsort(vals[order], descending=True, stable=True)]

@@ -222,10 +222,10 @@ def _gather_relocation_candidates(state, far_local, n_empty):
         wts[:c] = state.w[far_local] if state.w is not None else 1.0
         labs[:c] = state.labels_new[far_local]
     winners, _, _ = dist.merge_topk(vals, gidx, m)
-    rows_g = dist.all_gather_cat(rows)
-    wts_g = dist.all_gather_cat(wts)
-    labs_g = dist.all_gather_cat(labs)
-    valid = dist.all_gather_cat(gidx)[winners] >= 0
+    rows_g = dist.all_gather_same(rows)
+    wts_g = dist.all_gather_same(wts)
+    labs_g = dist.all_gather_same(labs)
+    valid = dist.all_gather_same(gidx)[winners] >= 0
     winners = winners[valid]
     return rows_g.contiguous(), wts_g.contiguous(), labs_g.contiguous(), winners.contiguous()
 
@@ -560,7 +560,7 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     cur = 0
     for c in range(1, k):
         nxt = 1 - cur
-        shares = dist.all_gather_cat(local_tot)                      # (world,) float64
+        shares = dist.all_gather_same(local_tot)                     # (world,) float64
         ends = torch.cumsum(shares, 0)
         offset = (ends[me] - shares[me]).reshape(1).to(dt)
         check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
@@ -570,8 +570,8 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
         # owner of trial tau: first shard whose inclusive prefix reaches r = u * total
         r = (u[c - 1] * total[0]).to(torch.float64)
         owner = torch.clamp((ends.reshape(1, -1) < r.reshape(-1, 1)).sum(dim=1), max=world - 1)
-        all_cand = dist.all_gather_cat(cand.reshape(1, t)).to(torch.int64)          # (world, t)
-        all_rows = dist.all_gather_cat(cand_rows.reshape(1, t, d))                   # (world, t, d)
+        all_cand = dist.all_gather_same(cand.reshape(1, t)).to(torch.int64)         # (world, t)
+        all_rows = dist.all_gather_same(cand_rows.reshape(1, t, d))                  # (world, t, d)
         sel = owner.reshape(1, t)
         cand_glob = (torch.gather(all_cand, 0, sel)[0] + rows_off[owner]).to(torch.int32).contiguous()
         rows_glob = torch.gather(all_rows, 0, owner.reshape(1, t, 1).expand(1, t, d))[0].contiguous()
