@@ -489,7 +489,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
-    ap.add_argument("--n", type=int, default=None, help="override the number of samples")
+    ap.add_argument("--n", "--rows", dest="n", type=int, default=None,
+                    help="override the number of samples (use --rows under torchrun, whose own "
+                         "parser claims the --n prefix)")
     ap.add_argument("--k", type=int, default=None, help="override the number of clusters")
     ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
     ap.add_argument("--cpu-sample-rows", type=int, default=200_000)

@@ -112,22 +112,41 @@ __device__ __forceinline__ void load_row_vec(const T* __restrict__ p, int f0, in
   }
 }
 
-// Copies rows [r0, r0 + rows) of X (rows x d, contiguous) to shared memory.  The tile starts
-// on a 16-byte boundary when X does and r0 is a multiple of 4; a ragged tail goes by plain
-// loads.  Every thread commits exactly one group per call (possibly empty).
+// Row pitch (in elements) of a staged tile: the row length rounded up so that the pitch is an
+// odd number of 16-byte chunks (or of words when rows cannot be copied in 16-byte chunks), which
+// makes "every thread reads chunk q of its own row" free of bank conflicts while all threads
+// walk the features in the same ascending order.
+template <typename T>
+__host__ __device__ inline int tile_row_pitch(int d, bool vec) {
+  constexpr int VEC = RowVec<T>::VEC;
+  if (vec) return (((d + VEC - 1) / VEC) | 1) * VEC;
+  return d | 1;
+}
+
+// Copies rows [r0, r0 + rows) of X (rows x d, contiguous in global memory) to a shared-memory
+// tile with row pitch `ld`.  With `vec` (d a multiple of VEC and X 16-byte aligned) the copy is
+// made of 16-byte asynchronous copies; otherwise of plain loads.  Every thread commits exactly
+// one group per call (possibly empty).
 template <typename T, int THREADS>
 __device__ __forceinline__ void issue_row_tile(T* __restrict__ dst, const T* __restrict__ X,
-                                               int64_t r0, int rows, int d, bool base_aligned) {
+                                               int64_t r0, int rows, int d, int ld, bool vec) {
+  constexpr int VEC = RowVec<T>::VEC;
   if (rows > 0) {
-    const size_t bytes = (size_t)rows * d * sizeof(T);
-    const unsigned char* src = reinterpret_cast<const unsigned char*>(X + r0 * (int64_t)d);
-    unsigned char* out = reinterpret_cast<unsigned char*>(dst);
-    const size_t vec_bytes = base_aligned ? (bytes & ~(size_t)15) : 0;
-    for (size_t off = (size_t)threadIdx.x * 16; off < vec_bytes; off += (size_t)THREADS * 16)
-      __pipeline_memcpy_async(out + off, src + off, 16);
-    for (size_t off = vec_bytes + threadIdx.x * sizeof(T); off < bytes;
-         off += (size_t)THREADS * sizeof(T))
-      *reinterpret_cast<T*>(out + off) = *reinterpret_cast<const T*>(src + off);
+    const T* src = X + r0 * (int64_t)d;
+    if (vec) {
+      const int nq = d / VEC;
+      const int total = rows * nq;
+      for (int ch = threadIdx.x; ch < total; ch += THREADS) {
+        const int row = ch / nq, q = ch - row * nq;
+        __pipeline_memcpy_async(dst + (size_t)row * ld + q * VEC, src + (size_t)ch * VEC, 16);
+      }
+    } else {
+      const int total = rows * d;
+      for (int e = threadIdx.x; e < total; e += THREADS) {
+        const int row = e / d, f = e - row * d;
+        dst[(size_t)row * ld + f] = src[e];
+      }
+    }
   }
   __pipeline_commit();
 }

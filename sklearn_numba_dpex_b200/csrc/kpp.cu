@@ -19,9 +19,9 @@ constexpr int KPP_MAX_T = 16;     // 2 + ln(k) stays below 16 for k < 1.2e6
 // A CTA owns KPP_BLOCK consecutive rows and streams them through shared memory in tiles of
 // KPP_THREADS / G rows with 16-byte asynchronous copies (KPP_STAGES tiles in flight), so the
 // bytes outstanding per SM do not depend on the register budget of the arithmetic.  One row
-// belongs to G adjacent threads (G = 1 unless rows are long); a thread walks its 16-byte
-// chunks in an order rotated by the row number, which keeps both the tile reads and the
-// candidate reads free of bank conflicts, and keeps one running sum per candidate in
+// belongs to G adjacent threads (G = 1 unless rows are long); every thread walks its 16-byte
+// chunks in ascending feature order (the tile's odd row pitch keeps these reads free of bank
+// conflicts, the candidate reads are broadcasts) and keeps one running sum per candidate in
 // registers: no reduction across lanes for G = 1, one or two shuffles otherwise.
 constexpr int KPP_STAGES = 2;
 
@@ -44,16 +44,17 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   T* c = reinterpret_cast<T*>(dyn_smem);              // t x d candidates (c_elems, 16B multiple)
   T* tiles = c + c_elems;                             // KPP_STAGES x (R x d)
   const int R = KPP_THREADS / G;                      // rows per tile
-  const size_t tile_elems = (size_t)R * d;
+  const bool vec_ok = aligned != 0;                   // 16-byte chunks usable for X rows
+  const int ld = tile_row_pitch<T>(d, vec_ok);
+  const size_t tile_elems = (size_t)R * ld;
   const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
   const int n_tiles = KPP_BLOCK / R;
-  const bool base_aligned = (((uintptr_t)X) & 15) == 0;
 
 #pragma unroll
   for (int sidx = 0; sidx < KPP_STAGES; ++sidx) {
     const int64_t r0 = b0 + (int64_t)sidx * R;
     const int rows = (sidx < n_tiles && r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
-    issue_row_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, base_aligned);
+    issue_row_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, ld, vec_ok);
   }
   for (int e = threadIdx.x; e < t * d; e += KPP_THREADS) c[e] = cand_rows[e];
   if (centers0 != nullptr && blockIdx.x == 0)
@@ -61,7 +62,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   const T* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
   const int r = threadIdx.x / G, li = threadIdx.x % G;   // row in the tile, part of the row
   const int nq = (d + VEC - 1) / VEC;                     // 16-byte chunks per row
-  const bool vec_ok = aligned != 0;                       // d % VEC == 0: rows in smem stay aligned
+  const bool c_vec = (d % VEC) == 0;                      // candidate rows in smem are 16B aligned
   double acc[TT];
 #pragma unroll
   for (int tau = 0; tau < TT; ++tau) acc[tau] = 0.0;
@@ -69,7 +70,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   for (int tix = 0; tix < n_tiles; ++tix) {
     __pipeline_wait_prior(KPP_STAGES - 1);
     __syncthreads();
-    const T* row = tiles + (tix % KPP_STAGES) * tile_elems + (size_t)r * d;
+    const T* row = tiles + (tix % KPP_STAGES) * tile_elems + (size_t)r * ld;
     const int64_t i = b0 + (int64_t)tix * R + r;
     const bool valid = i < n;
     // fetched first, so that their latency hides behind the distance arithmetic
@@ -78,16 +79,15 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     T s[TT];
 #pragma unroll
     for (int tau = 0; tau < TT; ++tau) s[tau] = T(0);
-    int qq = (li + r) % nq;                               // rotated start: conflict-free reads
     for (int q = li; q < nq; q += G) {
-      const int f0 = qq * VEC;
+      const int f0 = q * VEC;
       T xv[VEC];
       load_row_vec<T>(row, f0, d, vec_ok, xv);
 #pragma unroll
       for (int tau = 0; tau < TT; ++tau) {
         if (tau < t) {
           T cv[VEC];
-          load_row_vec<T>(c + tau * d, f0, d, vec_ok, cv);
+          load_row_vec<T>(c + tau * d, f0, d, c_vec, cv);
 #pragma unroll
           for (int jj = 0; jj < VEC; ++jj) {
             const T diff = cv[jj] - xv[jj];
@@ -95,8 +95,6 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
           }
         }
       }
-      qq += G;
-      if (qq >= nq) qq -= nq;
     }
     if (G > 1) {
 #pragma unroll
@@ -124,7 +122,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     const int nxt = tix + KPP_STAGES;
     const int64_t rn = b0 + (int64_t)nxt * R;
     const int rows = (nxt < n_tiles && rn < n) ? (int)((n - rn < R) ? (n - rn) : R) : 0;
-    issue_row_tile<T, KPP_THREADS>(tiles + (nxt % KPP_STAGES) * tile_elems, X, rn, rows, d, base_aligned);
+    issue_row_tile<T, KPP_THREADS>(tiles + (nxt % KPP_STAGES) * tile_elems, X, rn, rows, d, ld, vec_ok);
   }
   __pipeline_wait_prior(0);
 #pragma unroll
@@ -297,9 +295,10 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
   const int R = KPP_THREADS / G;
   const int64_t nb = ceil_div(n, KPP_BLOCK);
   const int c_elems = (int)(((size_t)t * d * sizeof(T) + 15) / 16 * 16 / sizeof(T));
-  const size_t dyn = ((size_t)c_elems + (size_t)KPP_STAGES * R * d) * sizeof(T);
+  const int aligned = ((d % VEC == 0) && (((uintptr_t)X & 15) == 0)) ? 1 : 0;
+  const int ld = tile_row_pitch<T>(d, aligned != 0);
+  const size_t dyn = ((size_t)c_elems + (size_t)KPP_STAGES * R * ld) * sizeof(T);
   KMB_REQUIRE(dyn <= 200 * 1024, "k-means++ pass: rows too long for the staged tiles (d=%d, t=%d)", d, t);
-  const int aligned = (d % VEC == 0) ? 1 : 0;
   auto run = [&](auto kern) -> int {
     if (dyn > 48 * 1024)
       KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));

@@ -18,8 +18,9 @@ __device__ __forceinline__ double group_sum(double v, int G) {
 
 // per_sample[i] = w_i * sum_f (x - c[label])^2 ; partial[b] = float64 block sum.
 // Rows stream through shared memory in tiles (two in flight, 16-byte asynchronous copies);
-// one row belongs to G adjacent threads, each walking its 16-byte chunks in an order rotated
-// by the row number (conflict-free tile reads); the row's centroid is gathered from L2.
+// one row belongs to G adjacent threads, each walking its 16-byte chunks in ascending feature
+// order (the tile's odd row pitch keeps the reads conflict-free); the row's centroid is
+// gathered from L2.
 constexpr int IN_THREADS = 128;
 constexpr int IN_STAGES = 2;
 
@@ -39,11 +40,11 @@ inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __rest
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   T* tiles = reinterpret_cast<T*>(dyn_smem);          // IN_STAGES x (R x d)
   const int R = IN_THREADS / G;
-  const size_t tile_elems = (size_t)R * d;
-  const bool base_aligned = (((uintptr_t)X) & 15) == 0;
+  const bool vec_ok = aligned != 0;                   // 16-byte chunks usable for X rows
+  const int ld = tile_row_pitch<T>(d, vec_ok);
+  const size_t tile_elems = (size_t)R * ld;
   const int r = threadIdx.x / G, li = threadIdx.x % G;
   const int nq = (d + VEC - 1) / VEC;
-  const bool vec_ok = aligned != 0;
   double block_acc = 0.0;
 
   // this CTA's tiles: blockIdx, blockIdx + gridDim, ...
@@ -54,24 +55,23 @@ inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __rest
 #pragma unroll
   for (int sidx = 0; sidx < IN_STAGES; ++sidx) {
     const int64_t tile = (int64_t)blockIdx.x + (int64_t)sidx * gridDim.x;
-    issue_row_tile<T, IN_THREADS>(tiles + sidx * tile_elems, X, tile * R, tile_rows(tile), d,
-                                  base_aligned);
+    issue_row_tile<T, IN_THREADS>(tiles + sidx * tile_elems, X, tile * R, tile_rows(tile), d, ld,
+                                  vec_ok);
   }
   int slot = 0;
   for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
     __pipeline_wait_prior(IN_STAGES - 1);
     __syncthreads();
-    const T* row = tiles + slot * tile_elems + (size_t)r * d;
+    const T* row = tiles + slot * tile_elems + (size_t)r * ld;
     const int64_t i = tile * R + r;
     const bool valid = i < n;
     const uint32_t lab = valid ? labels[i] : 0u;
     const T wi = (valid && w) ? w[i] : T(1);
     const T* crow = C + (int64_t)(lab < (uint32_t)k ? lab : 0u) * d;
-    const bool c_vec = vec_ok && ((((uintptr_t)C) & 15) == 0);
+    const bool c_vec = ((d % VEC) == 0) && ((((uintptr_t)C) & 15) == 0);
     T s = T(0);
-    int qq = (li + r) % nq;
     for (int q = li; q < nq; q += G) {
-      const int f0 = qq * VEC;
+      const int f0 = q * VEC;
       T xv[VEC], cv[VEC];
       load_row_vec<T>(row, f0, d, vec_ok, xv);
       load_row_vec<T>(crow, f0, d, c_vec, cv);
@@ -80,8 +80,6 @@ inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __rest
         const T diff = xv[jj] - cv[jj];
         s = fma(diff, diff, s);
       }
-      qq += G;
-      if (qq >= nq) qq -= nq;
     }
     if (G > 1) {
       s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -94,8 +92,8 @@ inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __rest
     }
     __syncthreads();
     const int64_t nxt = tile + (int64_t)IN_STAGES * gridDim.x;
-    issue_row_tile<T, IN_THREADS>(tiles + slot * tile_elems, X, nxt * R, tile_rows(nxt), d,
-                                  base_aligned);
+    issue_row_tile<T, IN_THREADS>(tiles + slot * tile_elems, X, nxt * R, tile_rows(nxt), d, ld,
+                                  vec_ok);
     slot = (slot + 1) % IN_STAGES;
   }
   __pipeline_wait_prior(0);
@@ -301,9 +299,15 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
   const int G = inertia_threads_per_row(d, esize);
   const int R = IN_THREADS / G;
   const int64_t n_tiles = ceil_div(n > 0 ? n : 1, R);
-  const size_t dyn = (size_t)IN_STAGES * R * d * esize;
+  const bool vec = (d % (int)(16 / esize) == 0) && (((uintptr_t)X & 15) == 0);
+  const int vecn = (int)(16 / esize);
+  const int ld = vec ? ((((d + vecn - 1) / vecn) | 1) * vecn) : (d | 1);
+  const size_t dyn = (size_t)IN_STAGES * R * ld * esize;
   KMB_REQUIRE(dyn <= 200 * 1024, "kmb_inertia: rows too long for the staged tiles (d=%d)", d);
-  int64_t grid = (int64_t)sm_count() * (dyn > 64 * 1024 ? 1 : (dyn > 32 * 1024 ? 3 : 6));
+  int per_sm = (int)((220 * 1024) / (dyn + 1024));   // CTAs that fit one SM's shared memory
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > n_tiles) grid = n_tiles;
   if (grid > RS_MAX_BLOCKS) grid = RS_MAX_BLOCKS;
   if (total) {
@@ -314,7 +318,7 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
     }
   }
   KMB_DISPATCH_DTYPE(dtype, {
-    const int aligned = (d % RowVec<T>::VEC == 0) ? 1 : 0;
+    const int aligned = vec ? 1 : 0;
     auto kern = inertia_kernel<T>;
     if (dyn > 48 * 1024)
       KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));

@@ -52,7 +52,11 @@ def _rank_main(rank, world, port, queue):
             kpp_C, kpp_idx = kmeans_plusplus(Xd.T, wd, 40, np.random.RandomState(5))
             single = (labels.cpu().numpy(), float(inertia), C_t.T.cpu().numpy(), n_iter,
                       mean.cpu().numpy(), float(tol), kpp_idx.cpu().numpy(), kpp_C.T.cpu().numpy())
-        tdist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        # a short collective timeout: if the other rank fails, this one errors out instead of
+        # waiting for it
+        import datetime
+        tdist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                 timeout=datetime.timedelta(seconds=90))
         kdist.enable()
         start, stop = kdist.shard_bounds(X.shape[0], rank, world)
         Xs = torch.as_tensor(X[start:stop]).to(dev)
@@ -98,7 +102,16 @@ def test_two_gpu_lloyd_equals_single_gpu():
     procs = [ctx.Process(target=_rank_main, args=(r, 2, port, queue)) for r in range(2)]
     for p in procs:
         p.start()
-    results = sorted(queue.get(timeout=600) for _ in procs)
-    for p in procs:
-        p.join(timeout=120)
-    assert [r[1] for r in results] == ["ok", "ok"], results
+    results = []
+    try:
+        for _ in procs:
+            results.append(queue.get(timeout=240))
+            if results[-1][1] != "ok":
+                break  # the other rank may be stuck in a collective: do not wait for it
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.kill()
+    results.sort()
+    assert [r[1] for r in results] == ["ok", "ok"], results[-1][2] if results else "no result"
