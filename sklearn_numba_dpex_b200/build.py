@@ -51,7 +51,8 @@ def _compile_one(nvcc, src, force, verbose):
     newest = max(os.path.getmtime(src_path), _headers_mtime())
     if not force and os.path.exists(obj) and os.path.getmtime(obj) >= newest:
         return obj, ""
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", INCLUDE, "-c", src_path, "-o", obj]
+    extra = os.environ.get("KMB_NVCC_EXTRA", "").split()
+    cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", INCLUDE, "-c", src_path, "-o", obj]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src}:\n{proc.stdout}\n{proc.stderr}")

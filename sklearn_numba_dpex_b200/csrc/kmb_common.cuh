@@ -63,14 +63,6 @@ inline int sm_count() {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// Lanes that cooperate on one sample row in the row-scan kernels: the smallest power of
-// two >= d, capped at 32.
-inline int lanes_per_row(int d) {
-  int g = 1;
-  while (g < d && g < 32) g <<= 1;
-  return g;
-}
-
 // 16-byte vectors of consecutive features: 4 floats or 2 doubles per lane.
 template <typename T>
 struct RowVec;
@@ -82,15 +74,6 @@ template <>
 struct RowVec<double> {
   static constexpr int VEC = 2;
 };
-
-// Lanes per sample row when every lane takes one 16-byte vector: the smallest power of two
-// >= ceil(d / VEC), capped at 32 (longer rows take several trips).
-inline int vec_lanes_per_row(int d, int vec) {
-  const int need = (d + vec - 1) / vec;
-  int g = 1;
-  while (g < need && g < 32) g <<= 1;
-  return g;
-}
 
 // v[j] = p[f0 + j] for f0 + j < d, else 0.  `aligned` = the row pitch and the base pointer
 // allow one 16-byte load (d a multiple of VEC, base 16-byte aligned).

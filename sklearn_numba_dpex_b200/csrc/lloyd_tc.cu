@@ -3,21 +3,26 @@
 // tensor memory), TMA-staged operand tiles, an argmin epilogue fed by tcgen05.ld, and a
 // centroid update with 16-byte vector reductions.
 //
-// One persistent CTA per SM, 11 warps:
+// One persistent CTA per SM, 12 warps:
 //   warp 0       TMA producer of the raw fp32 sample tile (128 rows x d, 128B-swizzled)
 //   warp 1       TMA producer of the centroid stages (hi and lo parts, 128 centroids x 32
 //                features each, five stages = 160 KB in flight)
-//   warp 2       allocates tensor memory and issues the MMAs; the whole warp walks the loop so
-//                that descriptors stay in the uniform datapath, one elected lane issues
-//   warps 3..6   split the staged sample tile into hi / lo parts held in TENSOR MEMORY (the A
-//                operand is read from TMEM), then run the argmin epilogue: one sample row per
-//                thread = one TMEM lane, a min-tree per 32 accumulator columns
-//   warps 7..10  centroid update of the previous tile: one warp adds one 512-byte sample row
-//                per instruction (red.global.add.v4.f32) into an L2-resident accumulator copy
+//   warps 2, 3   issue the MMAs, one accumulator buffer each (warp 2 also allocates tensor
+//                memory); the whole warp walks the loop so that descriptors stay in the uniform
+//                datapath, one elected lane issues
+//   warps 4..7   split the staged sample tile into hi / lo parts held in TENSOR MEMORY (the A
+//                operand is read from TMEM), then run the argmin epilogue on columns 0..63 of
+//                every accumulator: one sample row per thread = one TMEM lane, a min-tree per 32
+//                accumulator columns; they merge the two halves into the labels
+//   warps 8..11  argmin epilogue on columns 64..127 of every accumulator
+//   warps 4..11  centroid update of the tile, 16 rows per warp: 16-byte vector reductions
+//                (red.global.add.v4.f32) into an L2-resident accumulator copy
 // Tensor memory (512 columns): A_hi [0,128) | A_lo [128,256) | accumulator 0 [256,384) |
 // accumulator 1 [384,512).  Accumulators are double-buffered, so the epilogue of centroid
 // tile j overlaps the MMAs of tile j+1, and the next sample tile is split into TMEM as soon
-// as the last accumulator of the current tile has completed.
+// as the last accumulator of the current tile has completed.  Rows of at most 64 features
+// leave room for two sample tiles in tensor memory (A_hi | A_lo of 64 columns each, twice), and
+// then the split of tile t + 1 overlaps the MMAs of tile t as well.
 //
 // CTAs walk the centroid tiles (and the feature chunks inside a tile) in rotated orders
 // that depend on blockIdx, so that the 148 SMs do not all pull the same L2 lines at the same
@@ -43,10 +48,10 @@ constexpr int TC_BN = 128;          // centroids per MMA / accumulator buffer
 constexpr int TC_KC = 32;           // features per 128-byte swizzle atom
 constexpr int TC_STAGES = 5;        // centroid stages in flight
 constexpr int TC_MAX_D = 128;       // d_pad <= 128: hi and lo parts take 2 x 128 TMEM columns
-constexpr int TC_WARPS = 11;
+constexpr int TC_WARPS = 12;
 constexpr int TC_THREADS = TC_WARPS * 32;
-constexpr int TC_EPI_WARP0 = 3;
-constexpr int TC_UPD_WARP0 = 7;
+constexpr int TC_EPI_WARP0 = 4;
+constexpr int TC_UPD_WARP0 = 8;
 constexpr int TC_ATOM_BYTES = TC_BM * TC_KC * 4;  // 16 KB: 128 rows x 128 B
 constexpr int TC_A_HI_COL = 0, TC_A_LO_COL = 128, TC_ACC_COL = 256, TC_TMEM_COLS = 512;
 constexpr long long TC_TIMEOUT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
@@ -56,14 +61,19 @@ struct TcSmem {
   unsigned char xstage[TC_MAX_D / TC_KC][TC_ATOM_BYTES];
   unsigned char bhi[TC_STAGES][TC_ATOM_BYTES];
   unsigned char blo[TC_STAGES][TC_ATOM_BYTES];
-  uint32_t lab_s[2][TC_BM];       // labels of a finished tile, handed to the update warps
-  unsigned long long x_full, x_conv, x_stage_free;
+  // k <= 65536, so labels fit 16 bits here (shared memory is full to the last kilobyte)
+  uint16_t lab_s[2][TC_BM];       // labels of a finished tile, read by the centroid update
+  float part_v[TC_BM];            // group 1's minimum and index per row, merged by group 0
+  uint16_t part_i[TC_BM];
+  unsigned long long x_full[2], x_conv[2], x_stage_free[2];
   unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
   unsigned long long acc_full[2], acc_empty[2];
-  unsigned long long upd_full[2], upd_empty[2];
+  unsigned long long part_full[2], lab_ready[2];
   unsigned int tmem_base;
   volatile int abort_flag;
 };
+
+static_assert(sizeof(TcSmem) + 1024 <= 232448, "TcSmem exceeds the 227 KB a CTA may use");
 
 struct TcParams {
   const float* X;
@@ -128,9 +138,6 @@ __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
                                             void* bar) {
   asm volatile(
@@ -138,11 +145,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "%4}], [%2];" ::"r"(smem_u32(dst)),
       "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x),
-               "r"(y)
-               : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(void* smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -162,15 +164,6 @@ __device__ __forceinline__ void tc_fence_before() {
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 __device__ __forceinline__ void umma_commit(void* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -258,6 +251,13 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
+// Build with -DKMB_TC_PROFILE to make CTA 0 print how long its MMA warp waited on each barrier.
+#ifdef KMB_TC_PROFILE
+#define KMB_PROF(...) __VA_ARGS__
+#else
+#define KMB_PROF(...)
+#endif
+
 // ------------------------------------------------------------------------- the kernel
 // (value, index) minimum of two candidates where `a` has the lower index: b wins only when it
 // is strictly smaller; a NaN never wins against a number (fminf drops it).
@@ -269,12 +269,12 @@ __device__ __forceinline__ float tf32_round(float x) {
   }
 
 // Minimum of q[j] = h[j] - acc[j] over 32 consecutive centroids, lowest index on ties.
-__device__ __forceinline__ void min_tree32(const uint32_t (&v)[32], const float4* __restrict__ h4,
+__device__ __forceinline__ void min_tree32(const uint32_t (&v)[32], const float4 (&h4)[8],
                                            uint32_t base, float& out_v, uint32_t& out_i) {
   float q[32];
 #pragma unroll
   for (int j4 = 0; j4 < 8; ++j4) {
-    const float4 hv = __ldg(h4 + j4);  // same address in every lane: one broadcast load
+    const float4 hv = h4[j4];
     q[4 * j4 + 0] = hv.x - __uint_as_float(v[4 * j4 + 0]);
     q[4 * j4 + 1] = hv.y - __uint_as_float(v[4 * j4 + 1]);
     q[4 * j4 + 2] = hv.z - __uint_as_float(v[4 * j4 + 2]);
@@ -311,21 +311,31 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const bool update = p.acc != nullptr;
   // rotated walk orders of this CTA
   const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
+  // Rows of at most 64 (padded) features leave room for TWO sample tiles, both in the staging
+  // buffers (2 atoms each) and in tensor memory (hi | lo in 64 + 64 columns each): tile t + 1 is
+  // then split while the MMAs of tile t run, and the MMA warp never waits between tiles.
+  const bool two_tiles = p.d_pad <= 64;
+  // When all centroid stages of a sample tile fit the ring at once they are loaded ONCE per CTA
+  // and stay: stage (i, j) of this CTA's walk order then lives in slot i * n_kc + j for good.
+  const uint32_t n_st = (uint32_t)(n_nt * n_kc);
+  const bool resident = n_st <= (uint32_t)TC_STAGES;
   const int kc0 = (int)((blockIdx.x / (unsigned)n_nt) % (unsigned)n_kc);
 
   if (threadIdx.x == 0) {
-    mbar_init(&sm->x_full, 1);
-    mbar_init(&sm->x_conv, 4);
-    mbar_init(&sm->x_stage_free, 4);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm->x_full[a], 1);
+      mbar_init(&sm->x_conv[a], 4);
+      mbar_init(&sm->x_stage_free[a], 4);
+    }
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
       mbar_init(&sm->b_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm->acc_full[a], 1);
-      mbar_init(&sm->acc_empty[a], 4);
-      mbar_init(&sm->upd_full[a], 4);
-      mbar_init(&sm->upd_empty[a], 4);
+      mbar_init(&sm->acc_empty[a], 8);
+      mbar_init(&sm->part_full[a], 4);
+      mbar_init(&sm->lab_ready[a], 4);
     }
     sm->abort_flag = 0;
     fence_barrier_init();
@@ -344,10 +354,11 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (lane == 0) {
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-        if (!mbar_wait(&sm->x_stage_free, (t & 1) ^ 1, sm, p.error_flag)) break;
-        mbar_expect_tx(&sm->x_full, (uint32_t)n_kc * TC_ATOM_BYTES);
+        const uint32_t xs = two_tiles ? (t & 1) : 0, xu = two_tiles ? (t >> 1) : t;
+        if (!mbar_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag)) break;
+        mbar_expect_tx(&sm->x_full[xs], (uint32_t)n_kc * TC_ATOM_BYTES);
         for (int kc = 0; kc < n_kc; ++kc)
-          tma_load_2d(sm->xstage[kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full);
+          tma_load_2d(sm->xstage[xs * 2 + kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full[xs]);
       }
     }
   } else if (warp == 1) {
@@ -356,6 +367,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        if (resident && it != 0) break;     // everything is in shared memory already
         for (int i = 0; i < n_nt && ok; ++i) {
           const int nt = (nt0 + i) % n_nt;
           for (int j = 0; j < n_kc; ++j, ++it) {
@@ -372,65 +384,119 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
       }
     }
-  } else if (warp == 2) {
+  } else if (warp < TC_EPI_WARP0) {
     // ------------------------------------------------------------------------ MMA
-    uint32_t t = 0, it = 0, g = 0;
+    // Two issuing warps: warp 2 owns accumulator 0, warp 3 accumulator 1, i.e. they take the
+    // centroid tiles of a sample tile in turn.  One thread cannot prepare and issue twelve MMAs
+    // per stage in the 768 cycles the tensor pipe needs for them; two can.  Counters are kept
+    // by increment-and-wrap: every instruction in this loop is on the critical path.
+    const uint32_t mw = (uint32_t)warp - 2u;
+    const uint32_t ring = resident ? n_st : (uint32_t)TC_STAGES;
+    const uint32_t lap_flip = resident ? 0u : 1u;   // resident stages complete one phase only
+    const int ks_last = ((p.d - 1) % TC_KC) / 8 + 1;   // k-steps of the last chunk that hold data
+    uint32_t t = 0, g = 0, s = 0, lap = 0;
     bool ok = true;
+    KMB_PROF(long long w_conv = 0, w_acc = 0, w_b = 0, t_all = clock64(), tw;)
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
+    const uint32_t d_tmem = tmem_base + TC_ACC_COL + mw * TC_BN;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_conv, t & 1, sm, p.error_flag))) break;
+      const uint32_t xs = two_tiles ? (t & 1) : 0, xu = two_tiles ? (t >> 1) : t;
+      const uint32_t a_hi0 = tmem_base + (two_tiles ? xs * 128 : TC_A_HI_COL);
+      const uint32_t a_lo0 = tmem_base + (two_tiles ? xs * 128 + 64 : TC_A_LO_COL);
+      KMB_PROF(tw = clock64();)
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag))) break;
+      KMB_PROF(w_conv += clock64() - tw;)
       tc_fence_after();
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
-        const uint32_t ab = g & 1, ug = g >> 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_empty[ab], (ug & 1) ^ 1, sm, p.error_flag))) {
+        if ((g & 1u) != mw) {                 // the other warp's centroid tile: skip its stages
+          s += (uint32_t)n_kc;
+          if (s >= ring) {
+            s -= ring;
+            lap ^= lap_flip;
+          }
+          continue;
+        }
+        KMB_PROF(tw = clock64();)
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag))) {
           ok = false;
           break;
         }
+        KMB_PROF(w_acc += clock64() - tw;)
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + TC_ACC_COL + ab * TC_BN;
-        for (int j = 0; j < n_kc; ++j, ++it) {
-          const int kc = (kc0 + j) % n_kc;
-          const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
-          if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full[s], u & 1, sm, p.error_flag))) {
+        int kc = kc0;
+        for (int j = 0; j < n_kc; ++j) {
+          KMB_PROF(tw = clock64();)
+          if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
             ok = false;
             break;
           }
+          KMB_PROF(w_b += clock64() - tw;)
           tc_fence_after();
           const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
           const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
-          const uint32_t a_hi = tmem_base + TC_A_HI_COL + kc * TC_KC;
-          const uint32_t a_lo = tmem_base + TC_A_LO_COL + kc * TC_KC;
+          const uint32_t a_hi = a_hi0 + kc * TC_KC;
+          const uint32_t a_lo = a_lo0 + kc * TC_KC;
+          // k-steps whose 8 features all lie in the zero padding are skipped
+          const int ks_n = (kc == n_kc - 1) ? ks_last : TC_KC / 8;
           if (elect_one()) {
 #pragma unroll
             for (int ks = 0; ks < TC_KC / 8; ++ks) {
-              const uint64_t adv = (uint64_t)(ks * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units
-              umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, (j | ks) != 0);
-              umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
-              umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
+              if (ks < ks_n) {
+                const uint64_t adv = (uint64_t)(ks * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units
+                umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, (j | ks) != 0);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
+              }
             }
-            umma_commit(&sm->b_empty[s]);
-            if (j == n_kc - 1) umma_commit(&sm->acc_full[ab]);
+            if (!resident) umma_commit(&sm->b_empty[s]);
+            if (j == n_kc - 1) umma_commit(&sm->acc_full[mw]);
           }
           __syncwarp();
+          if (++kc == n_kc) kc = 0;
+          if (++s == ring) {
+            s = 0;
+            lap ^= lap_flip;
+          }
         }
       }
     }
-  } else if (warp < TC_UPD_WARP0) {
-    // ------------------------------------------------ split into TMEM, argmin epilogue
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0) printf("[tc prof] mma warp %d: total %lld cyc, wait x_conv %lld, acc_empty %lld, b_full %lld, tiles %u\n", warp, clock64() - t_all, w_conv, w_acc, w_b, t);)
+  } else {
+    // ------------------------------------- workers: split into TMEM, argmin, centroid update
+    // Two groups of four warps; warp w of a group owns TMEM lanes 32 * (w % 4) .. + 31, i.e. one
+    // sample row per thread.  Both groups read every accumulator: group 0 folds columns 0..63
+    // of the centroid tile, group 1 columns 64..127, so an accumulator is drained (and handed
+    // back to the MMA warp) in half the time.  At the end of a sample tile group 1 passes its
+    // (minimum, index) pairs through shared memory, group 0 merges them into the labels, and
+    // all eight warps add the tile's rows (16 rows per warp) into the centroid sums.
+    const int grp = warp >= TC_UPD_WARP0 ? 1 : 0;
     const int lane_base = (warp & 3) * 32;
     const int row = lane_base + lane;
     float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
     uint32_t t = 0, g = 0, changed = 0;
     bool ok = true;
+    // update geometry: G lanes (a power of two) of 16 bytes serve one row
+    const int urow0 = (warp - TC_EPI_WARP0) * 16;     // first of the 16 rows this warp adds
+    int G = 1;
+    while (G * 4 < p.d) G <<= 1;
+    const int rpi = 32 / G;                      // rows per warp instruction
+    const int sub = lane / G;                    // which of those rows this lane serves
+    const int col = (lane % G) * 4;              // first feature of this lane
+    const bool col_ok = col < p.d;
+    const int n_instr = (16 + rpi - 1) / rpi;
 
     // Splits the staged tile (row `row`, 128B-swizzled atoms) into TMEM: hi -> columns
-    // [0, d_pad), lo -> [128, 128 + d_pad) of this thread's lane.  False on time-out.
+    // [0, d_pad), lo -> [128, 128 + d_pad) of this thread's lane; with two tiles in flight tile
+    // tt goes to columns (tt & 1) * 128 + [0, d_pad) and + 64 + [0, d_pad).  False on time-out.
     auto convert_tile = [&](uint32_t tt) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full, tt & 1, sm, p.error_flag))) return false;
+      const uint32_t xs = two_tiles ? (tt & 1) : 0, xu = two_tiles ? (tt >> 1) : tt;
+      const uint32_t hi_col = two_tiles ? xs * 128 : TC_A_HI_COL;
+      const uint32_t lo_col = two_tiles ? xs * 128 + 64 : TC_A_LO_COL;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag))) return false;
       for (int kc = 0; kc < n_kc; ++kc) {
         uint32_t hi[32], lo[32];
-        const unsigned char* rowp = sm->xstage[kc] + row * 128;
+        const unsigned char* rowp = sm->xstage[xs * 2 + kc] + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
@@ -442,145 +508,181 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(x.w - h3);
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + kc * TC_KC;
-        tmem_st32(lane_addr + TC_A_HI_COL, hi);
-        tmem_st32(lane_addr + TC_A_LO_COL, lo);
+        tmem_st32(lane_addr + hi_col, hi);
+        tmem_st32(lane_addr + lo_col, lo);
       }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&sm->x_conv);
-        mbar_arrive(&sm->x_stage_free);
+        mbar_arrive(&sm->x_conv[xs]);
+        mbar_arrive(&sm->x_stage_free[xs]);
       }
       return true;
     };
 
-    ok = convert_tile(0);
+    KMB_PROF(long long w_acc = 0, w_part = 0, w_lab = 0, c_conv = 0, c_upd = 0, t_all = clock64(), tw;)
+    if (grp == 0) ok = convert_tile(0);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
       const int64_t m0 = tile * TC_BM;
       const bool has_next = tile + gridDim.x < n_tiles;
+      const uint32_t buf = t & 1, ub = t >> 1;
       float best = __int_as_float(0x7f800000);
       uint32_t bi = 0;
+      // Two tiles in flight: the other tensor-memory half was last read by tile t - 1, whose
+      // accumulators this warp has already consumed, so it is free now.
+      // Short rows (d <= 32): the rows this warp will add into the centroid sums are fetched
+      // now, so that their latency is hidden behind the epilogues instead of following them.
+      const float* xbase = p.X + (m0 + urow0) * (int64_t)p.d + col;
+      const bool pre = update && n_instr <= 4;
+      float4 xpre[4];
+      auto pre_ok = [&](int j) -> bool {
+        const int r = j * rpi + sub;
+        return pre && j < n_instr && r < 16 && col_ok && (m0 + urow0 + r < p.n);
+      };
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        xpre[j] = pre_ok(j) ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(j * rpi + sub) * p.d))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      KMB_PROF(tw = clock64();)
+      if (grp == 0 && two_tiles && has_next && !convert_tile(t + 1)) break;
+      KMB_PROF(c_conv += clock64() - tw;)
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
-        const int cn = ((nt0 + i) % n_nt) * TC_BN;
+        const int cn = ((nt0 + i) % n_nt) * TC_BN + grp * 64;   // first centroid of this half
+        KMB_PROF(tw = clock64();)
         if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
           ok = false;
           break;
         }
+        KMB_PROF(w_acc += clock64() - tw;)
         tc_fence_after();
         // The last accumulator of a tile completing means every MMA of the tile has read its
         // A operand: split the next tile into TMEM first, so that the MMA warp can go on
         // while this tile's last epilogue runs.
-        if (i == n_nt - 1 && has_next) {
+        if (grp == 0 && !two_tiles && i == n_nt - 1 && has_next) {
           if (!convert_tile(t + 1)) {
             ok = false;
             break;
           }
         }
-        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN;
-        float tbest = __int_as_float(0x7f800000);   // minimum over this centroid tile
-        uint32_t tbi = 0;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TC_BN; c0 += 64) {
-          uint32_t va[32], vb[32];
-          tmem_ld32(taddr + c0, va);
-          tmem_ld32(taddr + c0 + 32, vb);
-          tmem_ld_wait();
-          if (p.dots != nullptr && m0 + row < p.n) {
-            float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN + grp * 64;
+        // half norms of this half: same address in every lane (broadcast loads), issued ahead
+        // of the tensor-memory loads so that both latencies overlap
+        const float4* hp = reinterpret_cast<const float4*>(p.h_pad + cn);
+        float4 ha[8], hb[8];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (cn + c0 + j < p.k) drow[cn + c0 + j] = __uint_as_float(va[j]);
-              if (cn + c0 + 32 + j < p.k) drow[cn + c0 + 32 + j] = __uint_as_float(vb[j]);
-            }
-          }
-          float qa, qb;
-          uint32_t ia, ib;
-          min_tree32(va, reinterpret_cast<const float4*>(p.h_pad + cn + c0), (uint32_t)(cn + c0), qa, ia);
-          min_tree32(vb, reinterpret_cast<const float4*>(p.h_pad + cn + c0 + 32),
-                     (uint32_t)(cn + c0 + 32), qb, ib);
-          if (qa < tbest) { tbest = qa; tbi = ia; }   // ascending inside the tile: strict '<'
-          if (qb < tbest) { tbest = qb; tbi = ib; }
-        }
+        for (int j = 0; j < 8; ++j) ha[j] = __ldg(hp + j);
+        uint32_t va[32], vb[32];
+        tmem_ld32(taddr, va);
+        tmem_ld32(taddr + 32, vb);
+        tmem_ld_wait();
+        // the accumulator is in registers now: hand the buffer back before the argmin
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
-        // tiles arrive in rotated order: smaller value wins, equal values -> smaller index
-        if (tbest < best || (tbest == best && tbi < bi)) {
-          best = tbest;
-          bi = tbi;
+        if (p.dots != nullptr && m0 + row < p.n) {
+          float* drow = p.dots + (m0 + row) * (int64_t)p.ldd;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (cn + j < p.k) drow[cn + j] = __uint_as_float(va[j]);
+            if (cn + 32 + j < p.k) drow[cn + 32 + j] = __uint_as_float(vb[j]);
+          }
+        }
+        float qa, qb;
+        uint32_t ia, ib;
+        min_tree32(va, ha, (uint32_t)cn, qa, ia);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hb[j] = __ldg(hp + 8 + j);
+        min_tree32(vb, hb, (uint32_t)(cn + 32), qb, ib);
+        if (qb < qa) { qa = qb; ia = ib; }            // ascending inside the half: strict '<'
+        // halves arrive in rotated order: smaller value wins, equal values -> smaller index
+        if (qa < best || (qa == best && ia < bi)) {
+          best = qa;
+          bi = ia;
         }
       }
       if (!ok) break;
 
-      const bool valid = m0 + row < p.n;
-      if (valid) {
-        p.labels[m0 + row] = bi;
-        if (update) changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
-      }
-      if (update) {
-        // hand the tile's labels to the update warps
-        const uint32_t buf = t & 1, ub = t >> 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->upd_empty[buf], (ub & 1) ^ 1, sm, p.error_flag))) break;
-        sm->lab_s[buf][row] = bi;
+      if (grp == 1) {
+        sm->part_v[row] = best;
+        sm->part_i[row] = (uint16_t)bi;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm->upd_full[buf]);
+        if (lane == 0) mbar_arrive(&sm->part_full[buf]);
+      } else {
+        KMB_PROF(tw = clock64();)
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag))) break;
+        KMB_PROF(w_part += clock64() - tw;)
+        const float ov = sm->part_v[row];
+        const uint32_t oi = sm->part_i[row];
+        if (ov < best || (ov == best && oi < bi)) {
+          best = ov;
+          bi = oi;
+        }
+        if (m0 + row < p.n) {
+          p.labels[m0 + row] = bi;
+          if (update) changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
+        }
+        sm->lab_s[buf][row] = (uint16_t)bi;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->lab_ready[buf]);
       }
-    }
-    if (update) {
-      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
-      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
-    }
-  } else if (update) {
-    // ------------------------------------------------------ centroid update warps
-    const int uw = warp - TC_UPD_WARP0;
-    const int row = uw * 32 + lane;
-    float* acc_copy = p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len;
-    int G = 1;                                   // lanes per sample row
-    while (G * 4 < p.d) G <<= 1;
-    const int rpi = 32 / G;                      // rows per warp instruction
-    const int sub = lane / G;                    // which of those rows this lane serves
-    const int col = (lane % G) * 4;              // first feature of this lane
-    const bool col_ok = col < p.d;
-    uint32_t t = 0;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-      const int64_t m0 = tile * TC_BM;
-      const uint32_t buf = t & 1, ub = t >> 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->upd_full[buf], ub & 1, sm, p.error_flag))) break;
-      const uint32_t bi = sm->lab_s[buf][row];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->upd_empty[buf]);
-      const bool valid = m0 + row < p.n;
-      float wi = 0.f;
-      if (valid) {
-        wi = p.w ? p.w[m0 + row] : 1.f;
-        atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wi);
+      // Every warp waits for the merged labels of the tile (also when nothing is updated, so
+      // that group 1 never runs a whole tile ahead of group 0: part_* have one buffer, read by
+      // group 0 before it arrives here).  lab_s[buf] is reused two tiles later; by then every
+      // warp has passed this point of tile t + 1, which it reaches only after finishing the
+      // update of tile t.
+      KMB_PROF(tw = clock64();)
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag))) break;
+      KMB_PROF(w_lab += clock64() - tw;)
+      if (!update) continue;
+      KMB_PROF(tw = clock64();)
+
+      // ---- centroid update of rows urow0 .. urow0 + 15 of this tile
+      const int my = urow0 + (lane & 15);
+      const uint32_t ubi = sm->lab_s[buf][my];
+      const bool uvalid = m0 + my < p.n;
+      float uwi = 0.f;
+      if (uvalid) uwi = p.w ? p.w[m0 + my] : 1.f;
+      if (uvalid && lane < 16) atomicAdd(&acc_copy[(int64_t)p.k * p.d + ubi], uwi);
+      // The tile's rows come back from L2 (they were streamed through it moments ago).  One
+      // warp instruction adds 32 / G rows; eight instructions are in flight.
+      if (pre) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool okj = pre_ok(j);
+          const int src = okj ? j * rpi + sub : 0;
+          const uint32_t lab = __shfl_sync(0xffffffffu, ubi, src);
+          const float wr = __shfl_sync(0xffffffffu, uwi, src);
+          if (okj) {
+            float4 v;
+            v.x = xpre[j].x * wr; v.y = xpre[j].y * wr; v.z = xpre[j].z * wr; v.w = xpre[j].w * wr;
+            atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + col), v);
+          }
+        }
       }
-      // The tile's rows come back from L2 (they were streamed through it moments ago).  A row
-      // is d floats = d/4 lanes of 16 bytes: G lanes (a power of two) serve one row, so one
-      // warp instruction adds 32/G rows; eight instructions are in flight.
-      const int n_instr = 32 / rpi;
-      const float* xbase = p.X + (m0 + uw * 32) * (int64_t)p.d + col;
 #pragma unroll 1
-      for (int i0 = 0; i0 < n_instr; i0 += 8) {
+      for (int i0 = 0; i0 < (pre ? 0 : n_instr); i0 += 8) {
         float4 xs[8];
         bool oks[8];
         int rs[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          rs[j] = (i0 + j) * rpi + sub;                      // row of this lane, 0..31
-          const bool in_range = (i0 + j) < n_instr;
+          rs[j] = (i0 + j) * rpi + sub;                      // row of this lane, 0..15 when in range
+          const bool in_range = (i0 + j) < n_instr && rs[j] < 16;
           const int src = in_range ? rs[j] : 0;
-          oks[j] = in_range && col_ok && (__shfl_sync(0xffffffffu, (int)valid, src) != 0);
+          // every lane takes part in the shuffle: it must not sit behind a short-circuit '&&'
+          const int row_valid = __shfl_sync(0xffffffffu, (int)uvalid, src);
+          oks[j] = in_range && col_ok && (row_valid != 0);
           xs[j] = oks[j] ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)rs[j] * p.d))
                          : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int src = ((i0 + j) < n_instr) ? rs[j] : 0;
-          const uint32_t lab = __shfl_sync(0xffffffffu, bi, src);
-          const float wr = __shfl_sync(0xffffffffu, wi, src);
+          const int src = oks[j] ? rs[j] : 0;
+          const uint32_t lab = __shfl_sync(0xffffffffu, ubi, src);
+          const float wr = __shfl_sync(0xffffffffu, uwi, src);
           if (oks[j]) {
             float4 v;
             v.x = xs[j].x * wr; v.y = xs[j].y * wr; v.z = xs[j].z * wr; v.w = xs[j].w * wr;
@@ -588,6 +690,12 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           }
         }
       }
+      KMB_PROF(c_upd += clock64() - tw;)
+    }
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0 && (warp == TC_EPI_WARP0 || warp == TC_UPD_WARP0)) printf("[tc prof] worker warp %d: total %lld cyc, wait acc_full %lld, part_full %lld, lab_ready %lld, convert(top) %lld, update %lld, tiles %u\n", warp, clock64() - t_all, w_acc, w_part, w_lab, c_conv, c_upd, t);)
+    if (update && grp == 0) {
+      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
+      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
     }
   }
 

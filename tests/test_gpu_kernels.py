@@ -37,7 +37,9 @@ def _algos(dtype, n, d, k):
     code = _cabi.KMB_F32 if dtype == np.float32 else _cabi.KMB_F64
     if os.environ.get("KMB_TEST_NO_TC") == "1":
         return out
-    if _cabi.lib.kmb_lloyd_resolve_algo(code, _cabi.ALGO_TF32X3, n, d, k) == _cabi.ALGO_TF32X3:
+    # d that is not a multiple of 4 reaches the tensor-core step through a padded working copy
+    d4 = (d + 3) // 4 * 4
+    if _cabi.lib.kmb_lloyd_resolve_algo(code, _cabi.ALGO_TF32X3, n, d4, k) == _cabi.ALGO_TF32X3:
         out.append("tf32x3")
     return out
 
@@ -45,7 +47,8 @@ def _algos(dtype, n, d, k):
 STEP_SHAPES = [
     # (n, d, k): edge tiles on purpose (n, d, k not multiples of the kernel tiles)
     (1, 1, 1), (7, 3, 2), (129, 14, 9), (1000, 17, 127), (513, 130, 5), (2000, 14, 256),
-    (4096, 128, 1025), (3000, 64, 300), (50_000, 14, 127), (777, 32, 64),
+    (4096, 128, 1025), (3000, 64, 300), (50_000, 14, 127), (777, 32, 64), (2000, 20, 130),
+    (1500, 100, 260), (40_000, 8, 128),
 ]
 
 
@@ -79,12 +82,14 @@ def test_lloyd_step_teacher_forced(dtype, shape, weighted):
         # legitimate near-tie does not blur the comparison
         sums, sizes = ref.accumulate_centroids(X.astype(np.float64), w.astype(np.float64), labels, k)
         packed = st.packed.cpu().numpy()
+        dp = st.d  # feature count of the working copy (d rounded up to 4 on the padded path)
         scale = np.abs(X).max() * max(w.max(), 1.0) * max(n / k, 1.0)
         atol = RTOL[dtype] * scale
-        assert_allclose(packed[: k * d].reshape(k, d), sums, rtol=RTOL[dtype], atol=atol,
-                        err_msg=algo)
-        assert_allclose(packed[k * d: k * d + k], sizes, rtol=RTOL[dtype], err_msg=algo)
-        assert packed[k * d + k] == float((labels != prev).sum())
+        got_sums = packed[: k * dp].reshape(k, dp)
+        assert_allclose(got_sums[:, :d], sums, rtol=RTOL[dtype], atol=atol, err_msg=algo)
+        assert not got_sums[:, d:].any()
+        assert_allclose(packed[k * dp: k * dp + k], sizes, rtol=RTOL[dtype], err_msg=algo)
+        assert packed[k * dp + k] == float((labels != prev).sum())
 
         rec = st.status_host  # not read yet: use the device record
         status = st.status_dev.cpu().numpy().view(_status_dtype())[0]
@@ -95,7 +100,7 @@ def test_lloyd_step_teacher_forced(dtype, shape, weighted):
         nz = sizes > 0
         with np.errstate(divide="ignore", invalid="ignore"):
             C_new = sums / sizes[:, None]
-        got_C = st.C_new.cpu().numpy()
+        got_C = st.C_new.cpu().numpy()[:, :d]
         catol = RTOL[dtype] * np.abs(X).max()
         assert_allclose(got_C[nz], C_new[nz], rtol=RTOL[dtype], atol=catol, err_msg=algo)
         if nz.all():
