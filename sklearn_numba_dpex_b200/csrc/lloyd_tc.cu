@@ -324,8 +324,9 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   if (threadIdx.x == 0) {
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm->x_full[a], 1);
-      mbar_init(&sm->x_conv[a], 4);
-      mbar_init(&sm->x_stage_free[a], 4);
+      // both worker groups split the tile when it has more than one 32-feature chunk
+      mbar_init(&sm->x_conv[a], n_kc > 1 ? 8 : 4);
+      mbar_init(&sm->x_stage_free[a], n_kc > 1 ? 8 : 4);
     }
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
@@ -495,6 +496,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const uint32_t lo_col = two_tiles ? xs * 128 + 64 : TC_A_LO_COL;
       if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag))) return false;
       for (int kc = 0; kc < n_kc; ++kc) {
+        if (n_kc > 1 && (kc & 1) != grp) continue;     // the other group's chunk
         uint32_t hi[32], lo[32];
         const unsigned char* rowp = sm->xstage[xs * 2 + kc] + row * 128;
 #pragma unroll
@@ -522,7 +524,8 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     };
 
     KMB_PROF(long long w_acc = 0, w_part = 0, w_lab = 0, c_conv = 0, c_upd = 0, t_all = clock64(), tw;)
-    if (grp == 0) ok = convert_tile(0);
+    const bool converts = grp == 0 || n_kc > 1;
+    if (converts) ok = convert_tile(0);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
       const int64_t m0 = tile * TC_BM;
       const bool has_next = tile + gridDim.x < n_tiles;
@@ -545,7 +548,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         xpre[j] = pre_ok(j) ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(j * rpi + sub) * p.d))
                             : make_float4(0.f, 0.f, 0.f, 0.f);
       KMB_PROF(tw = clock64();)
-      if (grp == 0 && two_tiles && has_next && !convert_tile(t + 1)) break;
+      if (converts && two_tiles && has_next && !convert_tile(t + 1)) break;
       KMB_PROF(c_conv += clock64() - tw;)
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
@@ -560,7 +563,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // The last accumulator of a tile completing means every MMA of the tile has read its
         // A operand: split the next tile into TMEM first, so that the MMA warp can go on
         // while this tile's last epilogue runs.
-        if (grp == 0 && !two_tiles && i == n_nt - 1 && has_next) {
+        if (converts && !two_tiles && i == n_nt - 1 && has_next) {
           if (!convert_tile(t + 1)) {
             ok = false;
             break;
