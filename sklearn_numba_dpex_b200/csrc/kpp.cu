@@ -32,7 +32,22 @@ inline int kpp_threads_per_row(int d, size_t esize) {
   return row_bytes <= 256 ? 1 : (row_bytes <= 512 ? 2 : 4);
 }
 
-template <typename T, int TT>
+// One aligned 16-byte load of VEC consecutive features (no bounds or alignment test).
+template <typename T>
+__device__ __forceinline__ void load16(const T* __restrict__ p, T (&v)[RowVec<T>::VEC]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  } else {
+    const double2 q = *reinterpret_cast<const double2*>(p);
+    v[0] = q.x; v[1] = q.y;
+  }
+}
+
+// FAST = rows are whole 16-byte chunks and 16-byte aligned: the inner loop is then free of
+// bounds tests, and of the `tau < t` test as well (candidates t..TT-1 are zero rows whose sums
+// are computed and dropped).  The general form costs three times the instructions.
+template <typename T, int TT, bool FAST>
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ cand_rows,
                 const T* __restrict__ M_prev, const int32_t* __restrict__ best_prev,
@@ -56,7 +71,8 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     const int rows = (sidx < n_tiles && r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
     issue_row_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, ld, vec_ok);
   }
-  for (int e = threadIdx.x; e < t * d; e += KPP_THREADS) c[e] = cand_rows[e];
+  for (int e = threadIdx.x; e < (FAST ? TT : t) * d; e += KPP_THREADS)
+    c[e] = (e < t * d) ? cand_rows[e] : T(0);
   if (centers0 != nullptr && blockIdx.x == 0)
     for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers0[f] = cand_rows[f];
   const T* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
@@ -79,19 +95,60 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     T s[TT];
 #pragma unroll
     for (int tau = 0; tau < TT; ++tau) s[tau] = T(0);
-    for (int q = li; q < nq; q += G) {
-      const int f0 = q * VEC;
-      T xv[VEC];
-      load_row_vec<T>(row, f0, d, vec_ok, xv);
+    if constexpr (FAST && sizeof(T) == 4) {
+      // packed fp32x2 arithmetic: one instruction subtracts or multiply-adds two features, so
+      // the even features of a row accumulate in the low half and the odd ones in the high half
+      unsigned long long s2[TT];
 #pragma unroll
-      for (int tau = 0; tau < TT; ++tau) {
-        if (tau < t) {
+      for (int tau = 0; tau < TT; ++tau) s2[tau] = 0ull;
+      for (int q = li; q < nq; q += G) {
+        const ulonglong2 xq = *reinterpret_cast<const ulonglong2*>(row + q * VEC);
+        const T* cq = c + q * VEC;
+#pragma unroll
+        for (int tau = 0; tau < TT; ++tau) {
+          const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * d);
+          unsigned long long d0, d1;
+          asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d0) : "l"(cv.x), "l"(xq.x));
+          asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d1) : "l"(cv.y), "l"(xq.y));
+          asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(s2[tau]) : "l"(d0), "l"(s2[tau]));
+          asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(s2[tau]) : "l"(d1), "l"(s2[tau]));
+        }
+      }
+#pragma unroll
+      for (int tau = 0; tau < TT; ++tau)
+        s[tau] = (T)(__uint_as_float((unsigned)(s2[tau] & 0xffffffffull)) +
+                     __uint_as_float((unsigned)(s2[tau] >> 32)));
+    } else if constexpr (FAST) {
+      for (int q = li; q < nq; q += G) {
+        T xv[VEC];
+        load16<T>(row + q * VEC, xv);
+        const T* cq = c + q * VEC;
+#pragma unroll
+        for (int tau = 0; tau < TT; ++tau) {
           T cv[VEC];
-          load_row_vec<T>(c + tau * d, f0, d, c_vec, cv);
+          load16<T>(cq + tau * d, cv);
 #pragma unroll
           for (int jj = 0; jj < VEC; ++jj) {
             const T diff = cv[jj] - xv[jj];
             s[tau] = fma(diff, diff, s[tau]);
+          }
+        }
+      }
+    } else {
+      for (int q = li; q < nq; q += G) {
+        const int f0 = q * VEC;
+        T xv[VEC];
+        load_row_vec<T>(row, f0, d, vec_ok, xv);
+#pragma unroll
+        for (int tau = 0; tau < TT; ++tau) {
+          if (tau < t) {
+            T cv[VEC];
+            load_row_vec<T>(c + tau * d, f0, d, c_vec, cv);
+#pragma unroll
+            for (int jj = 0; jj < VEC; ++jj) {
+              const T diff = cv[jj] - xv[jj];
+              s[tau] = fma(diff, diff, s[tau]);
+            }
           }
         }
       }
@@ -294,8 +351,11 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
   const int G = kpp_threads_per_row(d, sizeof(T));
   const int R = KPP_THREADS / G;
   const int64_t nb = ceil_div(n, KPP_BLOCK);
-  const int c_elems = (int)(((size_t)t * d * sizeof(T) + 15) / 16 * 16 / sizeof(T));
   const int aligned = ((d % VEC == 0) && (((uintptr_t)X & 15) == 0)) ? 1 : 0;
+  // candidate rows in shared memory: the aligned form keeps TT rows (zero rows beyond t)
+  const int tt = t <= 1 ? 1 : (t <= 4 ? 4 : (t <= 6 ? 6 : (t <= 8 ? 8 : (t <= 10 ? 10 : (t <= 12 ? 12 : KPP_MAX_T)))));
+  const int c_rows = aligned ? tt : t;
+  const int c_elems = (int)(((size_t)c_rows * d * sizeof(T) + 15) / 16 * 16 / sizeof(T));
   const int ld = tile_row_pitch<T>(d, aligned != 0);
   const size_t dyn = ((size_t)c_elems + (size_t)KPP_STAGES * R * ld) * sizeof(T);
   KMB_REQUIRE(dyn <= 200 * 1024, "k-means++ pass: rows too long for the staged tiles (d=%d, t=%d)", d, t);
@@ -308,10 +368,20 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
     KMB_CHECK_LAUNCH();
     return KMB_OK;
   };
-  if (t <= 1) return run(kpp_scan_kernel<T, 1>);
-  if (t <= 8) return run(kpp_scan_kernel<T, 8>);
-  if (t <= 12) return run(kpp_scan_kernel<T, 12>);
-  return run(kpp_scan_kernel<T, KPP_MAX_T>);
+  if (aligned) {
+    switch (tt) {
+      case 1: return run(kpp_scan_kernel<T, 1, true>);
+      case 4: return run(kpp_scan_kernel<T, 4, true>);
+      case 6: return run(kpp_scan_kernel<T, 6, true>);
+      case 8: return run(kpp_scan_kernel<T, 8, true>);
+      case 10: return run(kpp_scan_kernel<T, 10, true>);
+      case 12: return run(kpp_scan_kernel<T, 12, true>);
+      default: return run(kpp_scan_kernel<T, KPP_MAX_T, true>);
+    }
+  }
+  if (t <= 1) return run(kpp_scan_kernel<T, 1, false>);
+  if (t <= 8) return run(kpp_scan_kernel<T, 8, false>);
+  return run(kpp_scan_kernel<T, KPP_MAX_T, false>);
 }
 
 }  // namespace kmb

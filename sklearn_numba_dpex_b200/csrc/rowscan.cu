@@ -29,7 +29,8 @@ inline int inertia_threads_per_row(int d, size_t esize) {
   return row_bytes <= 256 ? 1 : (row_bytes <= 512 ? 2 : 4);
 }
 
-template <typename T>
+// FAST = rows of X and of C are whole, aligned 16-byte chunks: no bounds tests in the loop.
+template <typename T, bool FAST>
 __global__ void __launch_bounds__(IN_THREADS)
 inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ C,
                const uint32_t* __restrict__ labels, T* __restrict__ per_sample,
@@ -70,15 +71,29 @@ inertia_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __rest
     const T* crow = C + (int64_t)(lab < (uint32_t)k ? lab : 0u) * d;
     const bool c_vec = ((d % VEC) == 0) && ((((uintptr_t)C) & 15) == 0);
     T s = T(0);
-    for (int q = li; q < nq; q += G) {
-      const int f0 = q * VEC;
-      T xv[VEC], cv[VEC];
-      load_row_vec<T>(row, f0, d, vec_ok, xv);
-      load_row_vec<T>(crow, f0, d, c_vec, cv);
+    if constexpr (FAST) {
+#pragma unroll 4
+      for (int q = li; q < nq; q += G) {
+        T xv[VEC], cv[VEC];
+        load_row_vec<T>(row, q * VEC, q * VEC + VEC, true, xv);
+        load_row_vec<T>(crow, q * VEC, q * VEC + VEC, true, cv);
 #pragma unroll
-      for (int jj = 0; jj < VEC; ++jj) {
-        const T diff = xv[jj] - cv[jj];
-        s = fma(diff, diff, s);
+        for (int jj = 0; jj < VEC; ++jj) {
+          const T diff = xv[jj] - cv[jj];
+          s = fma(diff, diff, s);
+        }
+      }
+    } else {
+      for (int q = li; q < nq; q += G) {
+        const int f0 = q * VEC;
+        T xv[VEC], cv[VEC];
+        load_row_vec<T>(row, f0, d, vec_ok, xv);
+        load_row_vec<T>(crow, f0, d, c_vec, cv);
+#pragma unroll
+        for (int jj = 0; jj < VEC; ++jj) {
+          const T diff = xv[jj] - cv[jj];
+          s = fma(diff, diff, s);
+        }
       }
     }
     if (G > 1) {
@@ -319,7 +334,8 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
   }
   KMB_DISPATCH_DTYPE(dtype, {
     const int aligned = vec ? 1 : 0;
-    auto kern = inertia_kernel<T>;
+    const bool fast = vec && (((uintptr_t)C & 15) == 0);
+    auto kern = fast ? inertia_kernel<T, true> : inertia_kernel<T, false>;
     if (dyn > 48 * 1024)
       KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     kern<<<(unsigned)grid, IN_THREADS, dyn, s>>>((const T*)X, (const T*)w, (const T*)C, labels,
