@@ -482,6 +482,57 @@ def run_fit_arm(args, cfg):
         tdist.destroy_process_group()
 
 
+def run_rowscan_arm(args, cfg):
+    """Times the two row-scan kernels alone on one GPU, on rows of the configuration's shape:
+    the k-means++ pass (`kmb_kpp_step`) for t = 1, 4, 8, 10 candidates and the inertia kernel.
+    One JSON line; bytes are the algorithmic ones (X once, closest in, t outputs)."""
+    import torch
+
+    from sklearn_numba_dpex_b200._cabi import check, lib, ptr, stream_ptr, workspace_for
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    dtype = torch.float32 if cfg["dtype"] == "f32" else torch.float64
+    code, esize = (0, 4) if dtype == torch.float32 else (1, 8)
+    n, d, k = cfg["n"], cfg["d"], cfg["k"]
+    X = generate_rows(cfg, 0, n, torch, device, dtype)
+    w = torch.ones(n, dtype=dtype, device=device)
+    nb = (n + lib.kmb_kpp_block_rows() - 1) // lib.kmb_kpp_block_rows()
+    s = stream_ptr(device)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    out = {"mode": "rowscan", "config": {"workload": cfg["desc"], "n": n, "d": d, "k": k},
+           "l2": "inputs larger than L2" if n * d * esize > 126e6 else "inputs fit L2", "kpp_step": {}}
+    for t in (1, 4, 8, 10):
+        M0 = torch.rand((t, n), dtype=dtype, device=device)
+        M1 = torch.empty((t, n), dtype=dtype, device=device)
+        bs = torch.empty((t, nb), dtype=torch.float64, device=device)
+        best = torch.zeros(1, dtype=torch.int32, device=device)
+        rows = X[:t].contiguous()
+        ms = timed(lambda: check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(rows), ptr(M0), ptr(best),
+                                                  ptr(M1), ptr(bs), n, d, t, s)))
+        gb = (n * d * esize + 2 * n * esize + t * n * esize) / 1e9
+        out["kpp_step"][f"t={t}"] = {"ms": ms, "GB/s": gb / ms * 1e3}
+    C = X[:k].contiguous()
+    labels = torch.randint(0, k, (n,), device=device, dtype=torch.int32)
+    ws, wsb = workspace_for(device, n, d, k)
+    tot = torch.empty(1, dtype=dtype, device=device)
+    ms = timed(lambda: check(lib.kmb_inertia(code, ptr(X), ptr(w), ptr(C), ptr(labels), None, ptr(tot),
+                                             n, d, k, ptr(ws), wsb, s)))
+    out["inertia"] = {"ms": ms, "GB/s": (n * d * esize + 2 * n * esize) / 1e9 / ms * 1e3}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -495,8 +546,9 @@ def main():
     ap.add_argument("--k", type=int, default=None, help="override the number of clusters")
     ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
     ap.add_argument("--cpu-sample-rows", type=int, default=200_000)
-    ap.add_argument("--mode", default="step", choices=["step", "fit"],
-                    help="step: the headline per-iteration benchmark; fit: k-means++ + Lloyd")
+    ap.add_argument("--mode", default="step", choices=["step", "fit", "rowscan"],
+                    help="step: the headline per-iteration benchmark; fit: k-means++ + Lloyd; "
+                         "rowscan: the k-means++ pass and the inertia kernel alone (1 GPU)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
@@ -511,6 +563,8 @@ def main():
         run_reference_arm(args, cfg)
     elif args.mode == "fit":
         run_fit_arm(args, cfg)
+    elif args.mode == "rowscan":
+        run_rowscan_arm(args, cfg)
     else:
         run_gpu_arm(args, cfg)
 
