@@ -235,9 +235,33 @@ def cpu_reference_sample(cfg, sample_rows, iters):
         nz = counts > 0
         C[nz] = sums[nz] / counts[nz, None]
     per_iter_full = float(np.mean(times)) * (cfg["n"] / sample_rows)
-    return dict(value=1.0 / per_iter_full, unit="iterations/s", cores=int(threads), kind="port",
+    base = dict(value=1.0 / per_iter_full, unit="iterations/s", cores=int(threads), kind="port",
                 sample=f"{sample_rows} rows of the same distribution, {iters} iterations of the C "
-                       f"restatement, time scaled by n/{sample_rows}"), times
+                       f"restatement, time scaled by n/{sample_rows}")
+    sk = sklearn_lloyd_sample(X, C, iters, int(threads))
+    if sk is not None:
+        base["sklearn_lloyd"] = dict(value=1.0 / (sk * (cfg["n"] / sample_rows)), unit="iterations/s",
+                                     threads=int(threads),
+                                     what="scikit-learn's own CPU Lloyd (_kmeans_single_lloyd, tol=0) on "
+                                          "the same sample, for context")
+    return base, times
+
+
+def sklearn_lloyd_sample(X, C, iters, threads):
+    """Seconds per iteration of scikit-learn's CPU Lloyd loop on the sample, or None when this
+    scikit-learn does not have the private entry point."""
+    try:
+        from sklearn.cluster._kmeans import _kmeans_single_lloyd
+    except Exception:
+        return None
+    w = np.ones(X.shape[0], dtype=X.dtype)
+    try:
+        _kmeans_single_lloyd(X, w, C.copy(), max_iter=1, tol=0.0, n_threads=threads)   # warm-up
+        t0 = time.perf_counter()
+        _, _, _, n_iter = _kmeans_single_lloyd(X, w, C.copy(), max_iter=iters, tol=0.0, n_threads=threads)
+        return (time.perf_counter() - t0) / max(int(n_iter), 1)
+    except Exception:
+        return None
 
 
 def run_reference_arm(args, cfg):
