@@ -42,7 +42,7 @@ int kmb_lloyd_resolve_algo(int dtype, int algo, int64_t n, int d, int k) {
   const int r = resolve_algo(dtype, algo, n, d, k);
   if (r < 0) {
     set_error("KMB_ALGO_TF32X3 does not support dtype=%d n=%lld d=%d k=%d (fp32 only, "
-              "d <= 256, k <= 65536)", dtype, (long long)n, d, k);
+              "d a multiple of 4 and <= 128, k <= 65536)", dtype, (long long)n, d, k);
     return KMB_ERR_UNSUPPORTED;
   }
   return r;
