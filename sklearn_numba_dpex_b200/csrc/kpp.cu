@@ -191,6 +191,114 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   }
 }
 
+// The same pass for fp32 rows of whole aligned 16-byte chunks and several candidates, with TWO
+// rows per thread: every broadcast read of a candidate chunk from shared memory then serves two
+// rows, which halves the shared-memory reads and the instructions per row (with ten candidates
+// the one-row form spends 46 % of the shared-memory pipe on those reads).  A tile of
+// 2 * KPP_THREADS / G rows is as large as both stages of the one-row form, so there is one
+// buffer per CTA and the three resident CTAs of a SM overlap each other's copies.  Per-row
+// arithmetic is identical to the one-row form (same chunk order, same packed accumulators).
+template <int TT>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_scan2_kernel(const float* __restrict__ X, const float* __restrict__ w,
+                 const float* __restrict__ cand_rows, const float* __restrict__ M_prev,
+                 const int32_t* __restrict__ best_prev, float* __restrict__ M_out,
+                 double* __restrict__ bsum_out, int64_t n, int d, int t, int64_t nb, int G,
+                 int c_elems) {
+  __shared__ double red[32];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  float* c = reinterpret_cast<float*>(dyn_smem);     // TT x d candidates, zero rows beyond t
+  float* tile = c + c_elems;                         // R x ld
+  const int Rh = KPP_THREADS / G;                    // rows per half tile
+  const int R = 2 * Rh;
+  const int ld = tile_row_pitch<float>(d, true);
+  const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
+  const int n_tiles = KPP_BLOCK / R;
+  for (int e = threadIdx.x; e < TT * d; e += KPP_THREADS) c[e] = (e < t * d) ? cand_rows[e] : 0.f;
+  const float* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
+  const int r = threadIdx.x / G, li = threadIdx.x % G;
+  const int nq = d / 4;
+  double acc[TT];
+#pragma unroll
+  for (int tau = 0; tau < TT; ++tau) acc[tau] = 0.0;
+
+  for (int tix = 0; tix < n_tiles; ++tix) {
+    const int64_t r0 = b0 + (int64_t)tix * R;
+    const int rows = (r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
+    issue_row_tile<float, KPP_THREADS>(tile, X, r0, rows, d, ld, true);
+    const int64_t i0 = r0 + r, i1 = i0 + Rh;
+    const bool valid0 = i0 < n, valid1 = i1 < n;
+    // fetched first, so that their latency hides behind the copy and the arithmetic
+    const float w0 = (valid0 && w) ? w[i0] : 1.f, w1 = (valid1 && w) ? w[i1] : 1.f;
+    const float cl0 = (valid0 && closest) ? closest[i0] : inf_value<float>();
+    const float cl1 = (valid1 && closest) ? closest[i1] : inf_value<float>();
+    __pipeline_wait_prior(0);
+    __syncthreads();
+    const float* row0 = tile + (size_t)r * ld;
+    const float* row1 = tile + (size_t)(r + Rh) * ld;
+    unsigned long long sa[TT], sb[TT];
+#pragma unroll
+    for (int tau = 0; tau < TT; ++tau) sa[tau] = sb[tau] = 0ull;
+    for (int q = li; q < nq; q += G) {
+      const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(row0 + q * 4);
+      const ulonglong2 xb = *reinterpret_cast<const ulonglong2*>(row1 + q * 4);
+      const float* cq = c + q * 4;
+#pragma unroll
+      for (int tau = 0; tau < TT; ++tau) {
+        const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * d);
+        unsigned long long d0, d1, e0, e1;
+        asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d0) : "l"(cv.x), "l"(xa.x));
+        asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d1) : "l"(cv.y), "l"(xa.y));
+        asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(e0) : "l"(cv.x), "l"(xb.x));
+        asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(e1) : "l"(cv.y), "l"(xb.y));
+        asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(sa[tau]) : "l"(d0), "l"(sa[tau]));
+        asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(sb[tau]) : "l"(e0), "l"(sb[tau]));
+        asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(sa[tau]) : "l"(d1), "l"(sa[tau]));
+        asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(sb[tau]) : "l"(e1), "l"(sb[tau]));
+      }
+    }
+#pragma unroll
+    for (int tau = 0; tau < TT; ++tau) {
+      if (tau < t) {
+        float s0 = __uint_as_float((unsigned)(sa[tau] & 0xffffffffull)) +
+                   __uint_as_float((unsigned)(sa[tau] >> 32));
+        float s1 = __uint_as_float((unsigned)(sb[tau] & 0xffffffffull)) +
+                   __uint_as_float((unsigned)(sb[tau] >> 32));
+        if (G > 1) {
+          s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+          s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+          if (G > 2) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+          }
+        }
+        if (li == 0) {
+          if (valid0) {
+            float v = s0 * w0;
+            v = (v < cl0) ? v : cl0;
+            M_out[(int64_t)tau * n + i0] = v;
+            acc[tau] += (double)v;
+          }
+          if (valid1) {
+            float v = s1 * w1;
+            v = (v < cl1) ? v : cl1;
+            M_out[(int64_t)tau * n + i1] = v;
+            acc[tau] += (double)v;
+          }
+        }
+      }
+    }
+    __syncthreads();   // the tile is overwritten by the next copy
+  }
+#pragma unroll
+  for (int tau = 0; tau < TT; ++tau) {
+    if (tau < t) {
+      const double tot = block_sum(acc[tau], red);
+      if (threadIdx.x == 0) bsum_out[(int64_t)tau * nb + blockIdx.x] = tot;
+    }
+  }
+}
+
 // One CTA per trial.  r = u * total; walk the block sums, then the elements of the block
 // where the float64 inclusive prefix first reaches r.
 template <typename T>
@@ -368,6 +476,27 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
     KMB_CHECK_LAUNCH();
     return KMB_OK;
   };
+  if constexpr (sizeof(T) == 4) {
+    // several candidates: two rows per thread, one tile buffer (see kpp_scan2_kernel)
+    const size_t dyn2 = ((size_t)c_elems + (size_t)2 * R * ld) * sizeof(T);
+    if (aligned && tt >= 6 && centers0 == nullptr && dyn2 <= 74 * 1024) {
+      auto run2 = [&](auto kern) -> int {
+        if (dyn2 > 48 * 1024)
+          KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn2));
+        kern<<<(unsigned)nb, KPP_THREADS, dyn2, stream>>>(X, w, cand_rows, M_prev, best_prev, M_out,
+                                                          bsum_out, n, d, t, nb, G, c_elems);
+        KMB_CHECK_LAUNCH();
+        return KMB_OK;
+      };
+      switch (tt) {
+        case 6: return run2(kpp_scan2_kernel<6>);
+        case 8: return run2(kpp_scan2_kernel<8>);
+        case 10: return run2(kpp_scan2_kernel<10>);
+        case 12: return run2(kpp_scan2_kernel<12>);
+        default: return run2(kpp_scan2_kernel<KPP_MAX_T>);
+      }
+    }
+  }
   if (aligned) {
     switch (tt) {
       case 1: return run(kpp_scan_kernel<T, 1, true>);
