@@ -49,6 +49,10 @@ STEP_SHAPES = [
     (1, 1, 1), (7, 3, 2), (129, 14, 9), (1000, 17, 127), (513, 130, 5), (2000, 14, 256),
     (4096, 128, 1025), (3000, 64, 300), (50_000, 14, 127), (777, 32, 64), (2000, 20, 130),
     (1500, 100, 260), (40_000, 8, 128),
+    # several sample tiles per CTA on the tensor-core step (buffer reuse and barrier phases across
+    # tiles): odd and even numbers of centroid tiles, 1 to 4 feature chunks, resident and streamed
+    # centroid stages, one and two sample tiles in flight
+    (60_000, 64, 300), (60_000, 96, 200), (60_000, 128, 130), (70_000, 32, 600), (60_000, 20, 700),
 ]
 
 
