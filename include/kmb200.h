@@ -162,8 +162,8 @@ size_t kmb_topk_workspace_bytes(int n_rows, int64_t n_cols, int k);
  * library image; it exists once on every GPU that loads the library and stays until the
  * process ends.  Limits: one row, k <= 4096 (larger k is rejected with KMB_ERR_INVALID; use
  * kmb_topk).  The call allocates and frees nothing.  The first call on each device looks up
- * the array's device address (cudaGetSymbolAddress, with that device current) and should be
- * made before any stream capture begins; later calls only launch kernels.  All calls on a
+ * the array's device address (cudaGetSymbolAddress, with that device current); later calls
+ * only launch kernels.  All calls on a
  * device share the one array: each call clears the parts that must start at zero, but two
  * calls whose kernels overlap on the GPU (different streams, or different host threads) race
  * on it and must be serialised by the caller.  It has no counterpart in the reference. */
