@@ -297,6 +297,43 @@ def test_full_fit_matches_oracle_c1_shape(dtype):
     assert_allclose(float(inertia), float(o_inertia), rtol=1e-5 if dtype == np.float32 else 1e-10)
 
 
+def test_full_fit_on_the_tensor_core_path_matches_oracle():
+    """A shape that the automatic choice sends to the tensor-core step (fp32, n >= 32 768,
+    k >= 128, d a multiple of 4), through the public estimator: fit from given centres,
+    predict and score, against the oracle's Lloyd on the same centred data.  Two iterations
+    only: the blobs overlap, and from the third iteration on a free-running loop drifts by a
+    few dozen boundary samples from the oracle on BOTH kernels (CUDA cores: 1, 3, 11 labels
+    after 3, 4, 6 iterations; tensor cores: 4, 18, 25), each flip moving two small clusters'
+    centres; step-by-step agreement is what the teacher-forced kernel tests check."""
+    from sklearn_numba_dpex_b200 import _cabi
+    from sklearn_numba_dpex_b200.kmeans import KMeans
+
+    rng = np.random.default_rng(3)
+    k, d, n = 160, 24, 40_000
+    assert _cabi.lib.kmb_lloyd_resolve_algo(_cabi.KMB_F32, _cabi.ALGO_AUTO, n, d, k) == _cabi.ALGO_TF32X3
+    centers = rng.uniform(-10, 10, size=(k, d))
+    X = (centers[np.arange(n) % k] + 0.7 * rng.standard_normal((n, d))).astype(np.float32)
+    init = X[rng.choice(n, size=k, replace=False)].copy()
+    w = np.ones(n, dtype=np.float32)
+    max_iter = 2
+    Xc, mean, init_c, _, uni = ref.prepare_data_for_lloyd(X, init, 0.0, w, True)
+    o_labels, o_inertia, o_C, o_iter = ref.lloyd(Xc, w, init_c, uni, max_iter, False, 0.0)
+
+    km = KMeans(n_clusters=k, init=init, n_init=1, max_iter=max_iter, tol=0.0, algorithm="lloyd")
+    km.fit(torch.as_tensor(X).cuda())
+    assert km.n_iter_ == o_iter
+    ok, n_bad, n_unexplained = ref.labels_agree(_np(km.labels_), o_labels, Xc, o_C)
+    assert ok, (n_bad, n_unexplained)
+    assert_allclose(float(km.inertia_), float(o_inertia), rtol=1e-5)
+    if n_bad == 0:
+        o_centres = o_C + (mean if mean is not None else 0.0)
+        assert_allclose(_np(km.cluster_centers_), o_centres, rtol=1e-4, atol=1e-4)
+    # predict and score run the label-only form of the same kernel on the raw data
+    pred = _np(km.predict(torch.as_tensor(X).cuda()))
+    assert (pred != _np(km.labels_)).mean() < 1e-4
+    assert_allclose(float(km.score(torch.as_tensor(X).cuda())), -float(o_inertia), rtol=1e-4)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_strict_convergence_and_tolerance_stop(dtype):
     """The loop must stop at the same iteration as the oracle, by strict convergence
