@@ -44,10 +44,39 @@ __device__ __forceinline__ void load16(const T* __restrict__ p, T (&v)[RowVec<T>
   }
 }
 
-// FAST = rows are whole 16-byte chunks and 16-byte aligned: the inner loop is then free of
-// bounds tests, and of the `tau < t` test as well (candidates t..TT-1 are zero rows whose sums
-// are computed and dropped).  The general form costs three times the instructions.
-template <typename T, int TT, bool FAST>
+// Copies rows [r0, r0 + rows) of X (rows x d) into a tile whose rows are dp = d rounded up to
+// whole 16-byte chunks, pitch ld.  Aligned rows go as 16-byte asynchronous copies; other rows
+// element by element (4- or 8-byte asynchronous copies), the padding features of the tile
+// having been zeroed once by zero_tile_padding.  Either way the arithmetic that follows reads
+// whole aligned chunks and needs no bounds test.  One commit group per call.
+template <typename T, int THREADS>
+__device__ __forceinline__ void issue_padded_tile(T* __restrict__ dst, const T* __restrict__ X,
+                                                  int64_t r0, int rows, int d, int ld, bool vec) {
+  if (vec || rows <= 0) {
+    issue_row_tile<T, THREADS>(dst, X, r0, rows, d, ld, true);
+    return;
+  }
+  const T* src = X + r0 * (int64_t)d;
+  const int total = rows * d;
+  for (int e = threadIdx.x; e < total; e += THREADS) {
+    const int row = e / d, f = e - row * d;
+    __pipeline_memcpy_async(dst + (size_t)row * ld + f, src + e, sizeof(T));
+  }
+  __pipeline_commit();
+}
+
+template <typename T, int THREADS>
+__device__ __forceinline__ void zero_tile_padding(T* __restrict__ tile, int tile_rows, int d, int dp,
+                                                  int ld) {
+  const int pad = dp - d;
+  for (int e = threadIdx.x; e < tile_rows * pad; e += THREADS)
+    tile[(size_t)(e / pad) * ld + d + e % pad] = T(0);
+}
+
+// The inner loop is free of bounds tests, and of the `tau < t` test as well: rows are staged
+// as whole 16-byte chunks (zero padding features) and candidates t..TT-1 are zero rows whose
+// sums are computed and dropped.  (A form with those tests costs three times the instructions.)
+template <typename T, int TT>
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ cand_rows,
                 const T* __restrict__ M_prev, const int32_t* __restrict__ best_prev,
@@ -56,29 +85,32 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   constexpr int VEC = RowVec<T>::VEC;
   __shared__ double red[32];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
-  T* c = reinterpret_cast<T*>(dyn_smem);              // t x d candidates (c_elems, 16B multiple)
-  T* tiles = c + c_elems;                             // KPP_STAGES x (R x d)
+  T* c = reinterpret_cast<T*>(dyn_smem);              // TT x dp candidates, zero padded
+  T* tiles = c + c_elems;                             // KPP_STAGES x (R x ld)
   const int R = KPP_THREADS / G;                      // rows per tile
-  const bool vec_ok = aligned != 0;                   // 16-byte chunks usable for X rows
-  const int ld = tile_row_pitch<T>(d, vec_ok);
+  const bool vec_ok = aligned != 0;                   // 16-byte copies usable for X rows
+  const int dp = (d + VEC - 1) / VEC * VEC;           // row length in shared memory
+  const int ld = tile_row_pitch<T>(dp, true);
   const size_t tile_elems = (size_t)R * ld;
   const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
   const int n_tiles = KPP_BLOCK / R;
 
+  if (dp != d) zero_tile_padding<T, KPP_THREADS>(tiles, KPP_STAGES * R, d, dp, ld);
 #pragma unroll
   for (int sidx = 0; sidx < KPP_STAGES; ++sidx) {
     const int64_t r0 = b0 + (int64_t)sidx * R;
     const int rows = (sidx < n_tiles && r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
-    issue_row_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, ld, vec_ok);
+    issue_padded_tile<T, KPP_THREADS>(tiles + sidx * tile_elems, X, r0, rows, d, ld, vec_ok);
   }
-  for (int e = threadIdx.x; e < (FAST ? TT : t) * d; e += KPP_THREADS)
-    c[e] = (e < t * d) ? cand_rows[e] : T(0);
+  for (int e = threadIdx.x; e < TT * dp; e += KPP_THREADS) {
+    const int tau = e / dp, f = e - tau * dp;
+    c[e] = (tau < t && f < d) ? cand_rows[tau * d + f] : T(0);
+  }
   if (centers0 != nullptr && blockIdx.x == 0)
     for (int f = threadIdx.x; f < d; f += KPP_THREADS) centers0[f] = cand_rows[f];
   const T* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
   const int r = threadIdx.x / G, li = threadIdx.x % G;   // row in the tile, part of the row
-  const int nq = (d + VEC - 1) / VEC;                     // 16-byte chunks per row
-  const bool c_vec = (d % VEC) == 0;                      // candidate rows in smem are 16B aligned
+  const int nq = dp / VEC;                                // 16-byte chunks per row
   double acc[TT];
 #pragma unroll
   for (int tau = 0; tau < TT; ++tau) acc[tau] = 0.0;
@@ -95,7 +127,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     T s[TT];
 #pragma unroll
     for (int tau = 0; tau < TT; ++tau) s[tau] = T(0);
-    if constexpr (FAST && sizeof(T) == 4) {
+    if constexpr (sizeof(T) == 4) {
       // packed fp32x2 arithmetic: one instruction subtracts or multiply-adds two features, so
       // the even features of a row accumulate in the low half and the odd ones in the high half
       unsigned long long s2[TT];
@@ -106,7 +138,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
         const T* cq = c + q * VEC;
 #pragma unroll
         for (int tau = 0; tau < TT; ++tau) {
-          const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * d);
+          const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * dp);
           unsigned long long d0, d1;
           asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d0) : "l"(cv.x), "l"(xq.x));
           asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d1) : "l"(cv.y), "l"(xq.y));
@@ -118,7 +150,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
       for (int tau = 0; tau < TT; ++tau)
         s[tau] = (T)(__uint_as_float((unsigned)(s2[tau] & 0xffffffffull)) +
                      __uint_as_float((unsigned)(s2[tau] >> 32)));
-    } else if constexpr (FAST) {
+    } else {
       for (int q = li; q < nq; q += G) {
         T xv[VEC];
         load16<T>(row + q * VEC, xv);
@@ -126,29 +158,11 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
 #pragma unroll
         for (int tau = 0; tau < TT; ++tau) {
           T cv[VEC];
-          load16<T>(cq + tau * d, cv);
+          load16<T>(cq + tau * dp, cv);
 #pragma unroll
           for (int jj = 0; jj < VEC; ++jj) {
             const T diff = cv[jj] - xv[jj];
             s[tau] = fma(diff, diff, s[tau]);
-          }
-        }
-      }
-    } else {
-      for (int q = li; q < nq; q += G) {
-        const int f0 = q * VEC;
-        T xv[VEC];
-        load_row_vec<T>(row, f0, d, vec_ok, xv);
-#pragma unroll
-        for (int tau = 0; tau < TT; ++tau) {
-          if (tau < t) {
-            T cv[VEC];
-            load_row_vec<T>(c + tau * d, f0, d, c_vec, cv);
-#pragma unroll
-            for (int jj = 0; jj < VEC; ++jj) {
-              const T diff = cv[jj] - xv[jj];
-              s[tau] = fma(diff, diff, s[tau]);
-            }
           }
         }
       }
@@ -179,7 +193,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
     const int nxt = tix + KPP_STAGES;
     const int64_t rn = b0 + (int64_t)nxt * R;
     const int rows = (nxt < n_tiles && rn < n) ? (int)((n - rn < R) ? (n - rn) : R) : 0;
-    issue_row_tile<T, KPP_THREADS>(tiles + (nxt % KPP_STAGES) * tile_elems, X, rn, rows, d, ld, vec_ok);
+    issue_padded_tile<T, KPP_THREADS>(tiles + (nxt % KPP_STAGES) * tile_elems, X, rn, rows, d, ld, vec_ok);
   }
   __pipeline_wait_prior(0);
 #pragma unroll
@@ -191,7 +205,7 @@ kpp_scan_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __res
   }
 }
 
-// The same pass for fp32 rows of whole aligned 16-byte chunks and several candidates, with TWO
+// The same pass for fp32 rows and several candidates, with TWO
 // rows per thread: every broadcast read of a candidate chunk from shared memory then serves two
 // rows, which halves the shared-memory reads and the instructions per row (with ten candidates
 // the one-row form spends 46 % of the shared-memory pipe on those reads).  A tile of
@@ -204,20 +218,25 @@ kpp_scan2_kernel(const float* __restrict__ X, const float* __restrict__ w,
                  const float* __restrict__ cand_rows, const float* __restrict__ M_prev,
                  const int32_t* __restrict__ best_prev, float* __restrict__ M_out,
                  double* __restrict__ bsum_out, int64_t n, int d, int t, int64_t nb, int G,
-                 int c_elems) {
+                 int aligned, int c_elems) {
   __shared__ double red[32];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
-  float* c = reinterpret_cast<float*>(dyn_smem);     // TT x d candidates, zero rows beyond t
+  float* c = reinterpret_cast<float*>(dyn_smem);     // TT x dp candidates, zero padded
   float* tile = c + c_elems;                         // R x ld
   const int Rh = KPP_THREADS / G;                    // rows per half tile
   const int R = 2 * Rh;
-  const int ld = tile_row_pitch<float>(d, true);
+  const int dp = (d + 3) / 4 * 4;
+  const int ld = tile_row_pitch<float>(dp, true);
   const int64_t b0 = (int64_t)blockIdx.x * KPP_BLOCK;
   const int n_tiles = KPP_BLOCK / R;
-  for (int e = threadIdx.x; e < TT * d; e += KPP_THREADS) c[e] = (e < t * d) ? cand_rows[e] : 0.f;
+  if (dp != d) zero_tile_padding<float, KPP_THREADS>(tile, R, d, dp, ld);
+  for (int e = threadIdx.x; e < TT * dp; e += KPP_THREADS) {
+    const int tau = e / dp, f = e - tau * dp;
+    c[e] = (tau < t && f < d) ? cand_rows[tau * d + f] : 0.f;
+  }
   const float* closest = M_prev ? M_prev + (int64_t)(best_prev ? *best_prev : 0) * n : nullptr;
   const int r = threadIdx.x / G, li = threadIdx.x % G;
-  const int nq = d / 4;
+  const int nq = dp / 4;
   double acc[TT];
 #pragma unroll
   for (int tau = 0; tau < TT; ++tau) acc[tau] = 0.0;
@@ -225,7 +244,7 @@ kpp_scan2_kernel(const float* __restrict__ X, const float* __restrict__ w,
   for (int tix = 0; tix < n_tiles; ++tix) {
     const int64_t r0 = b0 + (int64_t)tix * R;
     const int rows = (r0 < n) ? (int)((n - r0 < R) ? (n - r0) : R) : 0;
-    issue_row_tile<float, KPP_THREADS>(tile, X, r0, rows, d, ld, true);
+    issue_padded_tile<float, KPP_THREADS>(tile, X, r0, rows, d, ld, aligned != 0);
     const int64_t i0 = r0 + r, i1 = i0 + Rh;
     const bool valid0 = i0 < n, valid1 = i1 < n;
     // fetched first, so that their latency hides behind the copy and the arithmetic
@@ -245,7 +264,7 @@ kpp_scan2_kernel(const float* __restrict__ X, const float* __restrict__ w,
       const float* cq = c + q * 4;
 #pragma unroll
       for (int tau = 0; tau < TT; ++tau) {
-        const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * d);
+        const ulonglong2 cv = *reinterpret_cast<const ulonglong2*>(cq + tau * dp);
         unsigned long long d0, d1, e0, e1;
         asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d0) : "l"(cv.x), "l"(xa.x));
         asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d1) : "l"(cv.y), "l"(xa.y));
@@ -460,11 +479,12 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
   const int R = KPP_THREADS / G;
   const int64_t nb = ceil_div(n, KPP_BLOCK);
   const int aligned = ((d % VEC == 0) && (((uintptr_t)X & 15) == 0)) ? 1 : 0;
-  // candidate rows in shared memory: the aligned form keeps TT rows (zero rows beyond t)
+  // shared memory holds TT candidate rows (zero rows beyond t) of dp = d rounded up to whole
+  // 16-byte chunks, and tiles whose rows are dp long as well
   const int tt = t <= 1 ? 1 : (t <= 4 ? 4 : (t <= 6 ? 6 : (t <= 8 ? 8 : (t <= 10 ? 10 : (t <= 12 ? 12 : KPP_MAX_T)))));
-  const int c_rows = aligned ? tt : t;
-  const int c_elems = (int)(((size_t)c_rows * d * sizeof(T) + 15) / 16 * 16 / sizeof(T));
-  const int ld = tile_row_pitch<T>(d, aligned != 0);
+  const int dp = (d + VEC - 1) / VEC * VEC;
+  const int c_elems = tt * dp;
+  const int ld = tile_row_pitch<T>(dp, true);
   const size_t dyn = ((size_t)c_elems + (size_t)KPP_STAGES * R * ld) * sizeof(T);
   KMB_REQUIRE(dyn <= 200 * 1024, "k-means++ pass: rows too long for the staged tiles (d=%d, t=%d)", d, t);
   auto run = [&](auto kern) -> int {
@@ -479,12 +499,12 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
   if constexpr (sizeof(T) == 4) {
     // several candidates: two rows per thread, one tile buffer (see kpp_scan2_kernel)
     const size_t dyn2 = ((size_t)c_elems + (size_t)2 * R * ld) * sizeof(T);
-    if (aligned && tt >= 6 && centers0 == nullptr && dyn2 <= 74 * 1024) {
+    if (tt >= 6 && centers0 == nullptr && dyn2 <= 74 * 1024) {
       auto run2 = [&](auto kern) -> int {
         if (dyn2 > 48 * 1024)
           KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn2));
         kern<<<(unsigned)nb, KPP_THREADS, dyn2, stream>>>(X, w, cand_rows, M_prev, best_prev, M_out,
-                                                          bsum_out, n, d, t, nb, G, c_elems);
+                                                          bsum_out, n, d, t, nb, G, aligned, c_elems);
         KMB_CHECK_LAUNCH();
         return KMB_OK;
       };
@@ -497,20 +517,15 @@ static int launch_kpp_scan(const T* X, const T* w, const T* cand_rows, const T* 
       }
     }
   }
-  if (aligned) {
-    switch (tt) {
-      case 1: return run(kpp_scan_kernel<T, 1, true>);
-      case 4: return run(kpp_scan_kernel<T, 4, true>);
-      case 6: return run(kpp_scan_kernel<T, 6, true>);
-      case 8: return run(kpp_scan_kernel<T, 8, true>);
-      case 10: return run(kpp_scan_kernel<T, 10, true>);
-      case 12: return run(kpp_scan_kernel<T, 12, true>);
-      default: return run(kpp_scan_kernel<T, KPP_MAX_T, true>);
-    }
+  switch (tt) {
+    case 1: return run(kpp_scan_kernel<T, 1>);
+    case 4: return run(kpp_scan_kernel<T, 4>);
+    case 6: return run(kpp_scan_kernel<T, 6>);
+    case 8: return run(kpp_scan_kernel<T, 8>);
+    case 10: return run(kpp_scan_kernel<T, 10>);
+    case 12: return run(kpp_scan_kernel<T, 12>);
+    default: return run(kpp_scan_kernel<T, KPP_MAX_T>);
   }
-  if (t <= 1) return run(kpp_scan_kernel<T, 1, false>);
-  if (t <= 8) return run(kpp_scan_kernel<T, 8, false>);
-  return run(kpp_scan_kernel<T, KPP_MAX_T, false>);
 }
 
 }  // namespace kmb
