@@ -341,7 +341,7 @@ def run_gpu_arm(args, cfg):
                                  ptr(state.labels_new), ptr(state.acc), state.n_copies, state.n,
                                  state.d, state.k, ptr(state.ws), state.ws_bytes, stream_ptr(dev)))
         b.record()
-        state.kernel_launches += 1
+        state.kernel_launches += state.step_kernels
         if state.n_copies > 1:
             check(lib.kmb_lloyd_merge_copies(state.dtype, ptr(state.acc), state.n_copies,
                                              state.acc_len, ptr(state.packed), stream_ptr(dev)))

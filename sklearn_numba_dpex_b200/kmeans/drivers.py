@@ -106,6 +106,8 @@ class LloydState:
         self.sq_dist = None
         self.have_prev = False
         self.kernel_launches = 0
+        # kernels behind one kmb_lloyd_step: the tensor-core step first splits the centroids
+        self.step_kernels = 2 if self.algo == ALGO_NAMES["tf32x3"] else 1
         check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
               "kmb_half_l2_norm")
         self.kernel_launches += 1
@@ -126,7 +128,7 @@ class LloydState:
                                  ptr(self.labels_new), ptr(self.acc), self.n_copies, self.n,
                                  self.d, self.k, ptr(self.ws), self.ws_bytes, stream_ptr(dev)),
               "kmb_lloyd_step")
-        self.kernel_launches += 1
+        self.kernel_launches += self.step_kernels
         if self.n_copies > 1:
             check(lib.kmb_lloyd_merge_copies(self.dtype, ptr(self.acc), self.n_copies,
                                              self.acc_len, ptr(self.packed), stream_ptr(dev)),
