@@ -420,7 +420,7 @@ def run_gpu_arm(args, cfg):
             peak_sust = peaks["bf16_tflops_sustained"] / 6.0
             # DRAM bytes per sample row of the d=128 kernel from the ncu capture of n=1M
             # (summary kept with the other ncu summaries of this repository), growing in proportion to n
-            traffic = 539.6 * n_local if d == 128 else None
+            traffic = 540.4 * n_local if d == 128 else None
             roofline = {"bound": "tensor", "achieved": tf_achieved, "peak": peak, "unit": "TFLOP/s",
                         "frac": tf_achieved / peak, "traffic": traffic,
                         "peak_source": f"{peaks['source']} bf16_tflops (burst) / 6: TF32 = half the "
