@@ -137,3 +137,33 @@ def merge_topk(values, global_idx, m):
     order = torch.argsort(idx, stable=True)
     order = order[torch.argsort(vals[order], descending=True, stable=True)]
     return order[:m], vals, idx
+
+
+def shard_prefix(local_total):
+    """Row shards of a prefix-sum search.  `local_total` is a float64 tensor of one element, this
+    rank's share of a global sum.  Returns (ends, offset): the inclusive prefix of the shares
+    over the ranks (the same on every rank) and the exclusive prefix of THIS rank, i.e. the
+    amount a local running sum has to start from."""
+    shares = all_gather_same(local_total.reshape(1))
+    ends = torch.cumsum(shares, 0)
+    return ends, ends[rank()] - shares[rank()]
+
+
+def pick_owned_candidates(thresholds, ends, cand_local, rows_local, rows_offset):
+    """Every rank searched its own shard for each of the t thresholds; the valid answer for a
+    threshold is the one of its OWNER, the first rank whose inclusive prefix `ends` reaches it
+    (the last rank when rounding leaves none).  Gathers all ranks' local candidates
+    (`cand_local` (t,) local row ids, `rows_local` (t, d) the rows themselves) and returns the
+    owners' ones with GLOBAL row ids: (cand_global int32 (t,), rows_global (t, d)), identical
+    on every rank.  `rows_offset` (world,) holds the first global row id of every rank."""
+    world = world_size()
+    t = int(cand_local.shape[0])
+    d = int(rows_local.shape[1])
+    owner = torch.clamp((ends.reshape(1, -1) < thresholds.reshape(-1, 1).to(ends.dtype)).sum(dim=1),
+                        max=world - 1)
+    all_cand = all_gather_same(cand_local.reshape(1, t)).to(torch.int64)      # (world, t)
+    all_rows = all_gather_same(rows_local.reshape(1, t, d))                    # (world, t, d)
+    cand_global = (torch.gather(all_cand, 0, owner.reshape(1, t))[0] + rows_offset[owner])
+    rows_global = torch.gather(all_rows, 0, owner.reshape(1, t, 1).expand(1, t, d))[0]
+    return cand_global.to(torch.int32).contiguous(), rows_global.contiguous()
+

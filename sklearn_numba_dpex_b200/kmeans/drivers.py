@@ -562,21 +562,15 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     cur = 0
     for c in range(1, k):
         nxt = 1 - cur
-        shares = dist.all_gather_same(local_tot)                     # (world,) float64
-        ends = torch.cumsum(shares, 0)
-        offset = (ends[me] - shares[me]).reshape(1).to(dt)
+        ends, my_offset = dist.shard_prefix(local_tot)               # float64
+        offset = my_offset.reshape(1).to(dt)
         check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
                                  ptr(u[c - 1]), ptr(offset), t, ptr(cand), n, s), "kmb_kpp_sample")
         check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),
               "kmb_gather_rows")
         # owner of trial tau: first shard whose inclusive prefix reaches r = u * total
         r = (u[c - 1] * total[0]).to(torch.float64)
-        owner = torch.clamp((ends.reshape(1, -1) < r.reshape(-1, 1)).sum(dim=1), max=world - 1)
-        all_cand = dist.all_gather_same(cand.reshape(1, t)).to(torch.int64)         # (world, t)
-        all_rows = dist.all_gather_same(cand_rows.reshape(1, t, d))                  # (world, t, d)
-        sel = owner.reshape(1, t)
-        cand_glob = (torch.gather(all_cand, 0, sel)[0] + rows_off[owner]).to(torch.int32).contiguous()
-        rows_glob = torch.gather(all_rows, 0, owner.reshape(1, t, 1).expand(1, t, d))[0].contiguous()
+        cand_glob, rows_glob = dist.pick_owned_candidates(r, ends, cand, cand_rows, rows_off)
         check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(rows_glob), ptr(M[cur]), ptr(best),
                                ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
         check(lib.kmb_kpp_potentials(ptr(bsum[nxt]), t, nb, ptr(pots64), s), "kmb_kpp_potentials")

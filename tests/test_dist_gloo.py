@@ -97,6 +97,39 @@ def _case_merge_topk(rank, world, kdist):
     return gidx[winners].tolist()
 
 
+def _case_sharded_sampling(rank, world, kdist):
+    """One sampling round of the row-sharded k-means++: every rank searches its own shard from
+    its exclusive prefix, the owners' answers are picked, and the result equals the search over
+    the unsharded potentials.  Potentials are small integers, so every partial sum is exact."""
+    X, _, _ = _data()
+    n, d = X.shape
+    rng = np.random.default_rng(5)
+    pot = rng.integers(0, 7, size=n).astype(np.float64)
+    pot[:3] = 0.0                                   # leading zeros: index 0 must not win r > 0
+    start, stop = kdist.shard_bounds(n, rank, world)
+    local = torch.as_tensor(pot[start:stop])
+    ends, offset = kdist.shard_prefix(local.sum().reshape(1))
+    total = float(pot.sum())
+    assert float(ends[-1]) == total
+    first_shard_total = float(pot[: kdist.shard_bounds(n, 0, world)[1]].sum())
+    # thresholds: inside each shard, exactly on the shard boundary, the very first and last unit
+    r = torch.tensor([1.0, first_shard_total, first_shard_total + 1.0, total, 0.25 * total,
+                      0.75 * total], dtype=torch.float64)
+    t = r.numel()
+    prefix = offset + torch.cumsum(local, 0)
+    # local answer of every rank (what the sampling kernel returns): first local row whose
+    # inclusive prefix reaches r, the last row when none does
+    cand_local = torch.clamp((prefix.reshape(1, -1) < r.reshape(-1, 1)).sum(dim=1), max=local.numel() - 1)
+    rows_local = torch.as_tensor(X[start:stop])[cand_local]
+    rows_off = torch.tensor([kdist.shard_bounds(n, q, world)[0] for q in range(world)], dtype=torch.int64)
+    cand, rows = kdist.pick_owned_candidates(r, ends, cand_local.to(torch.int32), rows_local, rows_off)
+    expect = np.minimum(np.searchsorted(np.cumsum(pot), r.numpy(), side="left"), n - 1)
+    np.testing.assert_array_equal(cand.numpy(), expect)
+    np.testing.assert_array_equal(rows.numpy(), X[expect])
+    assert cand.dtype == torch.int32 and rows.shape == (t, d)
+    return cand.tolist()
+
+
 def _case_guards(rank, world, kdist):
     kdist.check_same_across_ranks(d=4, k=7)
     with pytest.raises(ValueError, match="ranks disagree"):
@@ -127,6 +160,12 @@ def test_sharded_iteration_equals_single():
 
 def test_merge_topk_across_ranks():
     results = _run("_case_merge_topk")
+    assert [r[1] for r in results] == ["ok", "ok"], results
+    assert results[0][2] == results[1][2]
+
+
+def test_sharded_sampling_round_picks_the_owners_candidates():
+    results = _run("_case_sharded_sampling")
     assert [r[1] for r in results] == ["ok", "ok"], results
     assert results[0][2] == results[1][2]
 
