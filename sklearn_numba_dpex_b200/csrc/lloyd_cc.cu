@@ -192,13 +192,22 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_cc_kernel(CcArgs<T> a) {
     if (UPDATE) {
       const int total = rows * d;
       const T* xt = a.X + m0 * (int64_t)d;
+      // element e = tid + i * CC_THREADS of the tile is (row, f): two divisions per tile, then
+      // both are advanced by increments
+      const int upd_drow = CC_THREADS / d, upd_df = CC_THREADS - upd_drow * d;
+      int row = tid / d, f = tid - row * d;
       for (int e = tid; e < total; e += CC_THREADS) {
-        const int row = e / d, f = e - row * d;
         const T wi = a.w ? a.w[m0 + row] : T(1);
         const T v = xt[e] * wi;
         const uint32_t lab = lab_s[row];
         if (a.smem_priv) atomicAdd(&ssum[lab * d + f], v);
         else atomicAdd(&acc_copy[(int64_t)lab * d + f], v);
+        row += upd_drow;
+        f += upd_df;
+        if (f >= d) {
+          f -= d;
+          ++row;
+        }
       }
     }
   }
