@@ -291,6 +291,36 @@ def test_prepare_and_restore(dtype, shape):
     assert zmean is None
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sum_reductions_reference_cases(dtype):
+    """The cases of the reference's common/tests/test_reductions.py:16-70 that lie on the KMeans
+    path: sums over the samples of every feature (its axis-1 sum of the (d, n) layout) on the
+    small shapes listed there, and the two 1-D sums (0+1+2+3 = 6, 0+..+4 = 10), plus a size
+    that spans many blocks."""
+    from sklearn_numba_dpex_b200._cabi import check, dtype_code, lib, ptr, stream_ptr, workspace_for
+
+    for shape in [(1, 1), (1, 3), (3, 1), (3, 5), (5, 3), (3, 4), (4, 3), (3, 9), (70_001, 5)]:
+        a = np.arange(shape[0] * shape[1], dtype=dtype).reshape(shape) % 1000
+        X = _dev(a)
+        out = torch.empty(shape[1], dtype=torch.float64, device=X.device)
+        ws, ws_bytes = workspace_for(X.device, shape[0], shape[1], 1)
+        check(lib.kmb_col_sums(dtype_code(X.dtype), ptr(X), shape[0], shape[1], ptr(out), ptr(ws),
+                               ws_bytes, stream_ptr(X.device)))
+        assert_allclose(out.cpu().numpy(), a.astype(np.float64).sum(axis=0), rtol=1e-12)
+    for length, expected in [(4, 6.0), (5, 10.0), (100_003, None)]:
+        v = np.arange(length, dtype=dtype) % 100
+        x = _dev(v)
+        ws, ws_bytes = workspace_for(x.device, length, 1, 1)
+        for square in (0, 1):
+            out = torch.empty(1, dtype=torch.float64, device=x.device)
+            check(lib.kmb_sum(dtype_code(x.dtype), ptr(x), length, square, ptr(out), ptr(ws), ws_bytes,
+                              stream_ptr(x.device)))
+            want = float((v.astype(np.float64) ** (2 if square else 1)).sum())
+            assert float(out[0]) == pytest.approx(want, rel=1e-12)
+            if expected is not None and not square:
+                assert float(out[0]) == expected
+
+
 def test_label_utilities():
     # sklearn_numba_dpex/kmeans/tests/test_kmeans.py:448-457
     from sklearn_numba_dpex_b200.kmeans.drivers import (get_nb_distinct_clusters,
