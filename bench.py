@@ -44,6 +44,9 @@ CONFIGS = {
                     "outliers in [-50,50]^64, k-means++ from seed 4"),
 }
 CHUNK = 1 << 20
+# DRAM bytes (read + written) per sample row of one fused-step launch, from the ncu captures
+# summarised under profiles/ (taken at a smaller n; the traffic grows in proportion to n).
+DRAM_BYTES_PER_ROW = {("tf32x3", 128): 540.4}
 
 
 def algorithmic_flops(n, d, k):
@@ -87,6 +90,23 @@ def measure_tf32_cublas(torch, device, size=8192, reps=10):
         return 2.0 * size ** 3 / (best * 1e-3) / 1e12
     except Exception:
         return None
+
+
+def measure_fma_peak(torch, device, dtype_name):
+    """FMA rate (TFLOP/s) of the CUDA cores in the compute dtype, measured now on this GPU."""
+    import ctypes
+
+    from sklearn_numba_dpex_b200._cabi import check, lib, ptr, stream_ptr
+
+    out = ctypes.c_double(0.0)
+    tdt = torch.float32 if dtype_name == "f32" else torch.float64
+    scratch = torch.empty(8 * 256 * 256, dtype=tdt, device=device)
+    try:
+        check(lib.kmb_measure_fma_peak(0 if dtype_name == "f32" else 1, 10, ctypes.byref(out),
+                                       ptr(scratch), stream_ptr(device)), "kmb_measure_fma_peak")
+    except Exception:
+        return None, None
+    return out.value, None
 
 
 # ----------------------------------------------------------------------------- data
@@ -210,41 +230,69 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------- CPU baseline
-def cpu_reference_sample(cfg, sample_rows, iters):
-    """Times the C restatement of the reference's Lloyd iteration (all host threads) on a
-    row sample of the workload and scales linearly in n to whole-job iterations/s."""
+def host_threads():
+    """Host threads this process may use.  Launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1; the CPU arms set their thread count from the affinity mask instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_sample(cfg, sample_rows):
+    """`sample_rows` rows from the benchmark's own seeded generator (its CPU random stream; the
+    GPU arm draws from the CUDA stream of the same generator) and initial centres drawn from
+    them: what both CPU legs
+    (the reference arm and the cpu_baseline of the GPU arm) and the provider-consistency check
+    work on."""
+    import torch
+
+    key = (cfg["seed"], cfg["d"], cfg["k"], cfg["dtype"], int(sample_rows))
+    if key not in _CPU_SAMPLES:
+        dt = torch.float32 if cfg["dtype"] == "f32" else torch.float64
+        sub = dict(cfg)
+        sub["n"] = sample_rows
+        X = generate_rows(sub, 0, sample_rows, torch, torch.device("cpu"), dt).numpy()
+        idx = np.random.RandomState(cfg["seed"]).choice(sample_rows, size=cfg["k"], replace=False)
+        _CPU_SAMPLES.clear()
+        _CPU_SAMPLES[key] = (X, X[idx].copy())
+    X, C = _CPU_SAMPLES[key]
+    return X, C.copy()
+
+
+_CPU_SAMPLES = {}
+
+
+def cpu_reference_sample(cfg, sample_rows, iters, warmup=1):
+    """Times the C restatement of the reference's Lloyd iteration on all host threads on a row
+    sample of the workload and scales linearly in n to whole-job iterations/s."""
     from oracle import c_oracle
 
-    rng = np.random.default_rng(cfg["seed"])
-    d, k = cfg["d"], cfg["k"]
-    dt = np.float32 if cfg["dtype"] == "f32" else np.float64
-    if cfg["noise"] is None:
-        X = rng.random((sample_rows, d)).astype(dt)
-    else:
-        spread = cfg["spread"]
-        off = (rng.standard_normal((k, d)) * spread if spread is not None
-               else rng.uniform(-10, 10, (k, d)))
-        X = (off[rng.integers(0, k, sample_rows)] + cfg["noise"] * rng.standard_normal((sample_rows, d))).astype(dt)
-    C = X[rng.choice(sample_rows, size=k, replace=False)].copy()
-    c_oracle.lloyd_iteration(X, None, C)  # warm-up
-    times, threads = [], 1
+    threads = c_oracle.set_num_threads(host_threads())
+    X, C = cpu_sample(cfg, sample_rows)
+    first_labels = None
+    for _ in range(max(warmup, 1)):
+        first_labels, _, _, _ = c_oracle.lloyd_iteration(X, None, C)
+    times = []
     for _ in range(iters):
         t0 = time.perf_counter()
-        _, sums, counts, threads = c_oracle.lloyd_iteration(X, None, C)
+        _, sums, counts, used = c_oracle.lloyd_iteration(X, None, C)
         times.append(time.perf_counter() - t0)
         nz = counts > 0
         C[nz] = sums[nz] / counts[nz, None]
     per_iter_full = float(np.mean(times)) * (cfg["n"] / sample_rows)
-    base = dict(value=1.0 / per_iter_full, unit="iterations/s", cores=int(threads), kind="port",
-                sample=f"{sample_rows} rows of the same distribution, {iters} iterations of the C "
-                       f"restatement, time scaled by n/{sample_rows}")
-    sk = sklearn_lloyd_sample(X, C, iters, int(threads))
+    base = dict(value=1.0 / per_iter_full, unit="iterations/s", cores=int(used), kind="port",
+                extrapolated=bool(sample_rows < cfg["n"]),
+                sample=f"{sample_rows} rows drawn by the benchmark's generator (same seed and "
+                       f"distribution, CPU random stream), {iters} iterations of the C restatement "
+                       f"on {used} threads, time scaled by n/{sample_rows}")
+    sk = sklearn_lloyd_sample(X, cpu_sample(cfg, sample_rows)[1], min(iters, 5), int(used))
     if sk is not None:
         base["sklearn_lloyd"] = dict(value=1.0 / (sk * (cfg["n"] / sample_rows)), unit="iterations/s",
-                                     threads=int(threads),
+                                     threads=int(used),
                                      what="scikit-learn's own CPU Lloyd (_kmeans_single_lloyd, tol=0) on "
                                           "the same sample, for context")
-    return base, times
+    return base, times, first_labels
 
 
 def sklearn_lloyd_sample(X, C, iters, threads):
@@ -252,16 +300,38 @@ def sklearn_lloyd_sample(X, C, iters, threads):
     scikit-learn does not have the private entry point."""
     try:
         from sklearn.cluster._kmeans import _kmeans_single_lloyd
+        from threadpoolctl import threadpool_limits
     except Exception:
         return None
     w = np.ones(X.shape[0], dtype=X.dtype)
     try:
-        _kmeans_single_lloyd(X, w, C.copy(), max_iter=1, tol=0.0, n_threads=threads)   # warm-up
-        t0 = time.perf_counter()
-        _, _, _, n_iter = _kmeans_single_lloyd(X, w, C.copy(), max_iter=iters, tol=0.0, n_threads=threads)
+        with threadpool_limits(limits=threads):
+            _kmeans_single_lloyd(X, w, C.copy(), max_iter=1, tol=0.0, n_threads=threads)   # warm-up
+            t0 = time.perf_counter()
+            _, _, _, n_iter = _kmeans_single_lloyd(X, w, C.copy(), max_iter=iters, tol=0.0,
+                                                   n_threads=threads)
         return (time.perf_counter() - t0) / max(int(n_iter), 1)
     except Exception:
         return None
+
+
+def provider_consistency(cfg, sample_rows, cpu_labels, torch, device):
+    """The check the reference's benchmark makes between providers (benchmark/kmeans.py:177-183
+    there: every provider ran the same iterations and agrees): the first-iteration labels of the
+    CUDA path on the CPU arm's sample, from the same centres, against the C restatement's.
+    Labels may differ only where the two nearest centres tie within 1e-6 relative."""
+    from oracle import reference_cpu as ref
+    from sklearn_numba_dpex_b200.kmeans.drivers import get_labels_inertia
+
+    X, C = cpu_sample(cfg, sample_rows)
+    Xd, Cd = torch.as_tensor(X).to(device), torch.as_tensor(C).to(device)
+    labels, _ = get_labels_inertia(Xd.T, Cd.T, None, False)
+    ok, n_bad, n_unexplained = ref.labels_agree(labels.cpu().numpy(), cpu_labels, X, C)
+    if not ok:
+        raise AssertionError(f"providers disagree: {n_unexplained} of {n_bad} label mismatches on the "
+                             f"{sample_rows}-row sample are not near-ties")
+    return {"rows": int(sample_rows), "label_mismatches": int(n_bad), "unexplained": int(n_unexplained),
+            "what": "first-iteration labels, CUDA path vs C restatement, same rows and centres"}
 
 
 def run_reference_arm(args, cfg):
@@ -269,9 +339,7 @@ def run_reference_arm(args, cfg):
     if rank != 0:
         return
     sample_rows = max(cfg["k"] * 4, min(cfg["n"], args.cpu_sample_rows))
-    for _ in range(max(args.warmup, 0)):
-        cpu_reference_sample(cfg, sample_rows, 1)
-    base, times = cpu_reference_sample(cfg, sample_rows, max(args.steps, 1))
+    base, times, _ = cpu_reference_sample(cfg, sample_rows, max(args.steps, 1), warmup=max(args.warmup, 1))
     ms = float(np.mean(times)) * (cfg["n"] / sample_rows) * 1e3
     line = {"impl": "reference", "metric": "Lloyd iterations/s", "value": base["value"],
             "unit": "iterations/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -326,28 +394,15 @@ def run_gpu_arm(args, cfg):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
-    orig_launch = state.launch_step
-
     step_idx = {"i": 0}
-    from sklearn_numba_dpex_b200._cabi import check, lib, ptr, stream_ptr
 
     def timed_launch_step():
-        # same sequence as LloydState.launch_step with events around the fused kernel
-        dev = state.X.device
+        # LloydState.launch_step with events around the fused kernel
         a, b = kev[step_idx["i"]]
         a.record()
-        check(lib.kmb_lloyd_step(state.dtype, state.algo, ptr(state.X), ptr(state.w), ptr(state.C),
-                                 ptr(state.h), ptr(state.labels) if state.have_prev else None,
-                                 ptr(state.labels_new), ptr(state.acc), state.n_copies, state.n,
-                                 state.d, state.k, ptr(state.ws), state.ws_bytes, stream_ptr(dev)))
+        state.launch_fused_step()
         b.record()
-        state.kernel_launches += state.step_kernels
-        if state.n_copies > 1:
-            check(lib.kmb_lloyd_merge_copies(state.dtype, ptr(state.acc), state.n_copies,
-                                             state.acc_len, ptr(state.packed), stream_ptr(dev)))
-            state.kernel_launches += 1
-        kdist.all_reduce_sum_(state.packed)
-        state._finalize()
+        state.launch_reduce_finalize()
         step_idx["i"] += 1
 
     state.launch_step = timed_launch_step
@@ -358,7 +413,7 @@ def run_gpu_arm(args, cfg):
     ev1.record()
     barrier()
     t_end = time.time()
-    state.launch_step = orig_launch
+    del state.launch_step
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     elapsed_ms = ev0.elapsed_time(ev1)
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
@@ -370,39 +425,90 @@ def run_gpu_arm(args, cfg):
     ms_per_step = elapsed_ms / args.steps
     value = 1e3 / ms_per_step
 
-    # ---- end to end through the driver API, host buffers in, host results out
+    # ---- end to end through the plugin: host buffers in, host results out
     e2e = None
     if not args.skip_e2e:
+        n_local = stop - start
         Xh = torch.empty(X.shape, dtype=dtype).pin_memory()
         Xh.copy_(X)
         Ch = C0.cpu().pin_memory()
-        wh = torch.ones(X.shape[0], dtype=dtype).pin_memory()
+        # scaling cross-check, outside every timed region: the counts of the last step add up to
+        # n and every rank holds the same total shift
+        counts_total = float(state.packed[k * state.d: k * state.d + k].double().sum())
+        shift_bits = torch.tensor([state.status_host.numpy().view(np.float64)[1]], dtype=torch.float64,
+                                  device=device)
+        if world > 1:
+            lo, hi = shift_bits.clone(), shift_bits.clone()
+            tdist.all_reduce(lo, op=tdist.ReduceOp.MIN)
+            tdist.all_reduce(hi, op=tdist.ReduceOp.MAX)
+            assert float(lo[0]) == float(hi[0]), "ranks disagree on the total shift"
+        assert counts_total == float(n), (counts_total, n)
         del state
         del X
         torch.cuda.empty_cache()
         e2e_iters = args.steps
-        barrier()
-        t0 = time.perf_counter()
-        Xd = Xh.to(device, non_blocking=True)
-        wd = wh.to(device, non_blocking=True)
-        Cd = Ch.to(device, non_blocking=True)
-        labels, inertia, C_t, n_iter = lloyd(Xd.T, wd, Cd.T, True, e2e_iters, False, 0.0,
-                                             algo=args.algo)
-        labels_h = labels.cpu()
-        centres_h = C_t.T.contiguous().cpu()
-        torch.cuda.synchronize()
-        dt_e2e = time.perf_counter() - t0
-        t = torch.tensor([dt_e2e], dtype=torch.float64, device=device)
-        if world > 1:
-            tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-        dt_e2e = float(t[0])
-        assert n_iter == e2e_iters, (n_iter, e2e_iters)
-        h2d = (Xh.numel() + wh.numel() + Ch.numel()) * esize * world
-        d2h = labels_h.numel() * 4 * world + centres_h.numel() * esize + esize
-        e2e = {"value": e2e_iters / dt_e2e, "unit": "iterations/s",
+        X_np, C_np = Xh.numpy(), Ch.numpy()      # page-locked numpy views: what a user hands in
+
+        def engine_fit(copy_x):
+            from sklearn_numba_dpex_b200.kmeans import KMeans, KMeansEngine
+
+            KMeansEngine._CONFIG.update(device=local_rank, algo=args.algo)
+            try:
+                est = KMeans(n_clusters=k, init=C_np, n_init=1, max_iter=e2e_iters, tol=0.0,
+                             copy_x=copy_x, algorithm="lloyd")
+                barrier()
+                t0 = time.perf_counter()
+                engine = KMeansEngine(est)
+                Xp, _, sw = engine.prepare_fit(X_np, sample_weight=None)
+                centers_init = engine.init_centroids(Xp, sw)
+                labels, inertia, centers, n_iter = engine.kmeans_single(Xp, sw, centers_init)
+                engine.unshift_centers(Xp, centers)
+                labels_h = labels.cpu()
+                centres_h = centers.contiguous().cpu()
+                torch.cuda.synchronize()
+                dt_fit = time.perf_counter() - t0
+            finally:
+                KMeansEngine._CONFIG.clear()
+            assert n_iter == e2e_iters, (n_iter, e2e_iters)
+            t = torch.tensor([dt_fit], dtype=torch.float64, device=device)
+            if world > 1:
+                tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+            return float(t[0]), labels_h.numel(), centres_h.numel()
+
+        def drivers_fit():
+            wh = torch.ones(n_local, dtype=dtype).pin_memory()
+            barrier()
+            t0 = time.perf_counter()
+            Xd = Xh.to(device, non_blocking=True)
+            wd = wh.to(device, non_blocking=True)
+            Cd = Ch.to(device, non_blocking=True)
+            labels, inertia, C_t, n_iter = lloyd(Xd.T, wd, Cd.T, True, e2e_iters, False, 0.0,
+                                                 algo=args.algo)
+            labels.cpu()
+            C_t.T.contiguous().cpu()
+            torch.cuda.synchronize()
+            dt_fit = time.perf_counter() - t0
+            t = torch.tensor([dt_fit], dtype=torch.float64, device=device)
+            if world > 1:
+                tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+            return float(t[0])
+
+        engine_fit(True)                          # untimed dry run (allocator, lazy initialisation)
+        dt_copy, n_lab, n_cen = engine_fit(True)
+        dt_inplace, _, _ = engine_fit(False)
+        dt_drivers = drivers_fit()
+        h2d = (Xh.numel() + Ch.numel()) * esize * world
+        d2h = n_lab * 4 * world + n_cen * esize + esize
+        e2e = {"value": e2e_iters / dt_copy, "unit": "iterations/s",
                "h2d_bytes_per_step": int(h2d // e2e_iters), "d2h_bytes_per_step": int(d2h // e2e_iters),
-               "what": f"one lloyd() call of {e2e_iters} iterations + final assignment and inertia, "
-                       "X/weights/centres from pinned host memory, labels/centres/inertia back to host"}
+               "what": f"KMeansEngine.prepare_fit -> init_centroids (array) -> kmeans_single "
+                       f"({e2e_iters} iterations, tol=0) -> unshift_centers on a page-locked numpy X "
+                       "(validation, upload, centring, tolerance scaling, Lloyd loop, final assignment "
+                       "and inertia), labels and centres copied back; copy_x=True",
+               "copy_x_false": {"value": e2e_iters / dt_inplace, "unit": "iterations/s"},
+               "drivers_lloyd": {"value": e2e_iters / dt_drivers, "unit": "iterations/s",
+                                 "what": "one drivers.lloyd() call on tensors uploaded from pinned "
+                                         "memory, no validation or centring"}}
 
     tf32_live = measure_tf32_cublas(torch, device) if (rank == 0 and algo_name == "tf32x3") else None
     if rank == 0:
@@ -420,7 +526,7 @@ def run_gpu_arm(args, cfg):
             peak_sust = peaks["bf16_tflops_sustained"] / 6.0
             # DRAM bytes per sample row of the d=128 kernel from the ncu capture of n=1M
             # (summary kept with the other ncu summaries of this repository), growing in proportion to n
-            traffic = 540.4 * n_local if d == 128 else None
+            traffic = DRAM_BYTES_PER_ROW.get(("tf32x3", d), 0) * n_local or None
             roofline = {"bound": "tensor", "achieved": tf_achieved, "peak": peak, "unit": "TFLOP/s",
                         "frac": tf_achieved / peak, "traffic": traffic,
                         "peak_source": f"{peaks['source']} bf16_tflops (burst) / 6: TF32 = half the "
@@ -429,12 +535,23 @@ def run_gpu_arm(args, cfg):
                         "tf32_cublas_tflops_live": tf32_live,
                         "hbm_frac": gb_achieved / peaks["hbm_gbs"]}
         else:
-            roofline = {"bound": "hbm", "achieved": gb_achieved, "peak": peaks["hbm_gbs"],
-                        "unit": "GB/s", "frac": gb_achieved / peaks["hbm_gbs"], "traffic": None,
-                        "peak_source": peaks["source"] + " hbm_gbs",
-                        "fp_tflops_achieved": tf_achieved,
-                        "note": "the contraction runs on the FP32/FP64 FMA pipe, which binds before "
-                                "HBM at this arithmetic intensity"}
+            # CUDA-core step: the FMA pipe of the compute dtype binds long before HBM at this
+            # arithmetic intensity; its ceiling is measured live by a register-resident kernel.
+            fma_peak, fma_clock = measure_fma_peak(torch, device, cfg["dtype"])
+            hbm_ms = abytes / peaks["hbm_gbs"] / 1e6
+            fma_ms = flops / (fma_peak * 1e9) if fma_peak else None
+            if fma_peak and fma_ms >= hbm_ms:
+                roofline = {"bound": "fma_pipe", "achieved": tf_achieved, "peak": fma_peak,
+                            "unit": "TFLOP/s", "frac": tf_achieved / fma_peak, "traffic": None,
+                            "peak_source": f"live {'FP32' if cfg['dtype'] == 'f32' else 'FP64'} FMA rate of "
+                                           "a register-resident kernel (kmb_measure_fma_peak), best of 10",
+                            "hbm_frac": gb_achieved / peaks["hbm_gbs"],
+                            "ideal_ms": {"fma_pipe": fma_ms, "hbm": hbm_ms}}
+            else:
+                roofline = {"bound": "hbm", "achieved": gb_achieved, "peak": peaks["hbm_gbs"],
+                            "unit": "GB/s", "frac": gb_achieved / peaks["hbm_gbs"], "traffic": None,
+                            "peak_source": peaks["source"] + " hbm_gbs",
+                            "fp_tflops_achieved": tf_achieved, "fma_peak_tflops": fma_peak}
         roofline["kernel_ms"] = kernel_ms
         line = {"metric": "Lloyd iterations/s", "value": value, "unit": "iterations/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -448,7 +565,9 @@ def run_gpu_arm(args, cfg):
         if e2e is not None:
             line["e2e"] = e2e
         if world == 1 and not args.skip_cpu:
-            line["cpu_baseline"], _ = cpu_reference_sample(cfg, min(n, args.cpu_sample_rows), 3)
+            rows = max(cfg["k"] * 4, min(n, args.cpu_sample_rows))
+            line["cpu_baseline"], _, cpu_labels = cpu_reference_sample(cfg, rows, 3)
+            line["provider_consistency"] = provider_consistency(cfg, rows, cpu_labels, torch, device)
         print(json.dumps(line), flush=True)
     if world > 1:
         tdist.barrier()
@@ -489,7 +608,9 @@ def run_fit_arm(args, cfg):
     centers_t, indices = kmeans_plusplus(X.T, w, k, np.random.RandomState(cfg["seed"]))
     sync()
     t1 = time.perf_counter()
-    labels, inertia, C_t, n_iter = lloyd(X.T, w, centers_t, True, args.steps, False, 0.0, algo=args.algo)
+    stats = {}
+    labels, inertia, C_t, n_iter = lloyd(X.T, w, centers_t, True, args.steps, False, 0.0, algo=args.algo,
+                                         stats=stats)
     sync()
     t2 = time.perf_counter()
     distinct = int(torch.unique(indices).numel())
@@ -500,6 +621,8 @@ def run_fit_arm(args, cfg):
             "kmeanspp_distinct_centres": distinct,
             "lloyd_seconds_incl_final_pass": t2 - t1, "lloyd_iterations": int(n_iter),
             "lloyd_iterations_per_s": n_iter / (t2 - t1), "inertia": float(inertia),
+            "n_relocation_events": stats.get("n_relocation_events"),
+            "n_empty_max": stats.get("n_empty_max"),
             "data": "synthetic"}), flush=True)
     if world > 1:
         tdist.barrier()
@@ -554,6 +677,35 @@ def run_rowscan_arm(args, cfg):
     ms = timed(lambda: check(lib.kmb_inertia(code, ptr(X), ptr(w), ptr(C), ptr(labels), None, ptr(tot),
                                              n, d, k, ptr(ws), wsb, s)))
     out["inertia"] = {"ms": ms, "GB/s": (n * d * esize + 2 * n * esize) / 1e9 / ms * 1e3}
+    peak = load_peaks()["hbm_gbs"]
+
+    def line(ms_, nbytes):
+        return {"ms": ms_, "GB/s": nbytes / 1e9 / ms_ * 1e3, "frac_of_hbm_peak": nbytes / 1e9 / ms_ * 1e3 / peak}
+
+    # column sums (centring) and the in-place shift
+    col = torch.empty(d, dtype=torch.float64, device=device)
+    ms = timed(lambda: check(lib.kmb_col_sums(code, ptr(X), n, d, ptr(col), ptr(ws), wsb, s)))
+    out["col_sums"] = line(ms, n * d * esize)
+    vec = torch.zeros(d, dtype=dtype, device=device)
+    ms = timed(lambda: check(lib.kmb_add_row_vector(code, ptr(X), n, d, ptr(vec), 1.0, s)))
+    out["add_row_vector"] = line(ms, 2 * n * d * esize)
+    # radix top-k over n values (the relocation's search), m = 1, 64, 4096
+    vals = torch.rand(n, dtype=dtype, device=device)
+    out["topk"] = {}
+    for m in (1, 64, 4096):
+        tws = torch.empty(lib.kmb_topk_workspace_bytes(1, n, m) + 256, dtype=torch.uint8, device=device)
+        idx = torch.empty(m, dtype=torch.int64, device=device)
+        ms = timed(lambda: check(lib.kmb_topk(code, ptr(vals), 1, n, m, None, ptr(idx), ptr(tws),
+                                              tws.numel(), s)))
+        out["topk"][f"m={m}"] = line(ms, n * esize)
+    # euclidean distances (transform): n x k outputs, chunked so that the output stays modest
+    kt = min(k, 256)
+    rows = min(n, max(1, (1 << 30) // (kt * esize)))
+    Y = X[:kt].contiguous()
+    Dt = torch.empty((kt, rows), dtype=dtype, device=device)
+    Xr = X[:rows]
+    ms = timed(lambda: check(lib.kmb_euclidean_distances(code, ptr(Xr), ptr(Y), ptr(Dt), rows, d, kt, s)))
+    out["euclidean_distances"] = dict(line(ms, rows * d * esize + rows * kt * esize), rows=rows, k=kt)
     print(json.dumps(out), flush=True)
 
 
@@ -569,7 +721,7 @@ def main():
                          "parser claims the --n prefix)")
     ap.add_argument("--k", type=int, default=None, help="override the number of clusters")
     ap.add_argument("--algo", default="auto", choices=["auto", "cuda_core", "tf32x3"])
-    ap.add_argument("--cpu-sample-rows", type=int, default=200_000)
+    ap.add_argument("--cpu-sample-rows", type=int, default=1_000_000)
     ap.add_argument("--mode", default="step", choices=["step", "fit", "rowscan"],
                     help="step: the headline per-iteration benchmark; fit: k-means++ + Lloyd; "
                          "rowscan: the k-means++ pass and the inertia kernel alone (1 GPU)")

@@ -53,8 +53,26 @@ typedef struct {
   int32_t changed;     /* 1 if any label differs from the previous labels, else 0     */
   double shift_total;  /* sum_j sum_f (C_old - C_new)^2                               */
   double inertia;      /* reserved (0)                                                */
-  double reserved;
+  int32_t wait_error;  /* copy of the workspace's time-out flag (see kmb_lloyd_wait_error) */
+  int32_t reserved;
 } kmb_lloyd_status;
+
+/* Flags of kmb_lloyd_step. */
+enum {
+  KMB_STEP_ACC_CLEARED = 1,    /* every copy of `acc` is already zero: skip the clearing     */
+  KMB_STEP_OPERANDS_READY = 2  /* KMB_ALGO_TF32X3: the split operands of C already sit in the
+                                  workspace (written by kmb_lloyd_finalize with
+                                  KMB_FIN_PREPARE_TF32X3 on the same workspace, C being that
+                                  call's C_new): skip the split kernel                       */
+};
+/* Flags of kmb_lloyd_finalize. */
+enum {
+  KMB_FIN_MERGE = 1,          /* merged[e] = sum over copies of acc[c][e] is computed here;
+                                 without it `merged` is the input (e.g. after an all-reduce)  */
+  KMB_FIN_CLEAR_ACC = 2,      /* zero every copy of `acc` once it has been read               */
+  KMB_FIN_PREPARE_TF32X3 = 4  /* also write the tensor-core operands of C_new into the
+                                 workspace for the next kmb_lloyd_step (fp32 only)           */
+};
 
 const char* kmb_last_error(void);
 int kmb_version(void);
@@ -76,41 +94,57 @@ int kmb_lloyd_resolve_algo(int dtype, int algo, int64_t n, int d, int k);
  * Replaces make_half_l2_norm_2d_axis0_kernel, sklearn_numba_dpex/common/kernels.py:117-145. */
 int kmb_half_l2_norm(int dtype, const void* C, void* half_norms, int k, int d, void* stream);
 
+/* Lloyd workspace.  kmb_lloyd_step, kmb_assign_labels, kmb_lloyd_finalize and
+ * kmb_matmul_nt keep a small control block (a sticky time-out flag of the tensor-core kernel
+ * and a counter of the finalize kernel) at the start of the workspace they are given, and the
+ * tensor-core operands behind it.  Clear the control block ONCE after allocating a
+ * workspace, and again to acknowledge a reported time-out; the calls themselves never clear
+ * it.  A workspace that also serves other entry points (kmb_inertia, kmb_sum, ...) must be
+ * re-initialised before it is handed to the Lloyd calls again.  No counterpart in the
+ * reference. */
+int kmb_lloyd_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
 /* One fused Lloyd step over n samples: label_i = argmin_j (half_norms[j] - x_i.c_j)
  * (lowest j on ties), labels written, number of labels differing from prev_labels
  * counted (prev_labels may be NULL: counts n), and w_i*x_i / w_i accumulated into
  * copy (blockIdx % n_copies) of `acc` (n_copies x kmb_lloyd_acc_len).  `acc` is
- * cleared by this call.
+ * cleared by this call unless KMB_STEP_ACC_CLEARED is given.
  * Replaces make_lloyd_single_step_fixed_window_kernel,
  * sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:35-424, and the two
  * make_initialize_to_zeros_kernel launches of kmeans/drivers.py:195-196. */
 int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void* C,
                    const void* half_norms, const uint32_t* prev_labels, uint32_t* labels,
-                   void* acc, int n_copies, int64_t n, int d, int k, void* workspace,
+                   void* acc, int n_copies, int64_t n, int d, int k, int flags, void* workspace,
                    size_t workspace_bytes, void* stream);
 
-/* After a KMB_ALGO_TF32X3 step or assignment on `workspace`: copies the kernel's time-out
- * flag to *host_flag (host memory), waits for the stream, and returns KMB_ERR_CUDA if a
- * bounded wait inside that kernel ran out (its outputs are then invalid).  No counterpart in
- * the reference, whose kernels have no device-side waits. */
-int kmb_lloyd_tc_error(const void* workspace, int d, int k, int* host_flag, void* stream);
+/* Copies the workspace's time-out flag to *host_flag (host memory), waits for the stream,
+ * and returns KMB_ERR_CUDA if a bounded wait inside a KMB_ALGO_TF32X3 kernel ran out on this
+ * workspace since its last kmb_lloyd_workspace_init (outputs computed since are invalid).
+ * The same flag travels in kmb_lloyd_status.wait_error.  No counterpart in the reference,
+ * whose kernels have no device-side waits. */
+int kmb_lloyd_wait_error(const void* workspace, int* host_flag, void* stream);
 
-/* out[e] = sum over copies of acc[c][e], copies added in ascending order.
- * Replaces the private-copy summation of make_reduce_centroid_data_kernel,
- * sklearn_numba_dpex/kmeans/kernels/utils.py:130-157. */
-int kmb_lloyd_merge_copies(int dtype, const void* acc, int n_copies, int64_t acc_len,
-                           void* out, void* stream);
+/* out[e] = sum over copies of acc[c][e], copies added in ascending order; with clear_acc
+ * the copies are zeroed afterwards.  Replaces the private-copy summation of
+ * make_reduce_centroid_data_kernel, sklearn_numba_dpex/kmeans/kernels/utils.py:130-157. */
+int kmb_lloyd_merge_copies(int dtype, void* acc, int n_copies, int64_t acc_len, void* out,
+                           int clear_acc, void* stream);
 
-/* From one merged accumulator (kmb_lloyd_acc_len elements): C_new = sums / counts,
- * half norms of C_new, total squared shift against C_old, ascending list of empty
- * clusters, and the status record.  `shifts` is k elements of scratch in `dtype`.
- * Replaces make_reduce_centroid_data_kernel's empty-cluster list (utils.py:159-167),
+/* From the accumulator (its copies merged here with KMB_FIN_MERGE, or `merged` given):
+ * C_new = sums / counts, half norms of C_new, total squared shift against C_old, ascending
+ * list of empty clusters, and the status record; one kernel.  `merged` holds
+ * kmb_lloyd_acc_len elements, `shifts` k elements of scratch, both in `dtype`; `acc` may be
+ * NULL when neither KMB_FIN_MERGE nor KMB_FIN_CLEAR_ACC is given.  The workspace must have
+ * been initialised with kmb_lloyd_workspace_init.
+ * Replaces make_reduce_centroid_data_kernel (kmeans/kernels/utils.py:114-195),
  * make_broadcast_division_1d_2d_axis0_kernel (common/kernels.py:61-82),
- * make_centroid_shifts_kernel (kmeans/kernels/utils.py:80-110) with its sum
- * reduction, and make_half_l2_norm_2d_axis0_kernel of the next iteration. */
-int kmb_lloyd_finalize(int dtype, const void* acc, const void* C_old, void* C_new,
-                       void* half_norms_new, void* shifts, uint32_t* empty_list,
-                       kmb_lloyd_status* status, int k, int d, void* stream);
+ * make_centroid_shifts_kernel (kmeans/kernels/utils.py:80-110) with its sum reduction, the
+ * make_half_l2_norm_2d_axis0_kernel of the next iteration, and (KMB_FIN_CLEAR_ACC) the
+ * make_initialize_to_zeros_kernel launches of the next iteration. */
+int kmb_lloyd_finalize(int dtype, void* acc, int n_copies, void* merged, int flags,
+                       const void* C_old, void* C_new, void* half_norms_new, void* shifts,
+                       uint32_t* empty_list, kmb_lloyd_status* status, int k, int d,
+                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* labels only.  Replaces make_label_assignment_fixed_window_kernel,
  * sklearn_numba_dpex/kmeans/kernels/compute_labels.py:19-185. */
@@ -163,7 +197,9 @@ size_t kmb_topk_workspace_bytes(int n_rows, int64_t n_cols, int k);
  * process ends.  Limits: one row, k <= 4096 (larger k is rejected with KMB_ERR_INVALID; use
  * kmb_topk).  The call allocates and frees nothing.  The first call on each device looks up
  * the array's device address (cudaGetSymbolAddress, with that device current); later calls
- * only launch kernels.  All calls on a
+ * only launch kernels.  The array is chosen by the CURRENT device of the calling thread, so
+ * `stream` and `values` must belong to that device: a stream of another GPU would be handed
+ * the wrong GPU's array, and nothing here can detect that.  All calls on a
  * device share the one array: each call clears the parts that must start at zero, but two
  * calls whose kernels overlap on the GPU (different streams, or different host threads) race
  * on it and must be serialised by the caller.  It has no counterpart in the reference. */
@@ -186,11 +222,11 @@ int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, const v
 /* For each trial tau < t: r = u[tau] * total, cand[tau] = first i whose inclusive prefix
  * sum of closest reaches r (0 if r <= 0, n-1 if never).  closest is row *best of
  * M (.., n) and its block sums row *best of bsum (.., nb); the prefix is taken in
- * float64.  offset (one element, may be NULL) is subtracted from r: the potential held by
+ * float64.  offset (one float64, may be NULL) is subtracted from r: the potential held by
  * the row shards before this one.  Replaces make_sample_center_candidates_kernel,
  * kmeans/kernels/kmeans_plusplus.py:61-103 (a sequential running sum there). */
 int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
-                   const void* total, const void* u, const void* offset, int t, int32_t* cand,
+                   const void* total, const void* u, const double* offset, int t, int32_t* cand,
                    int64_t n, void* stream);
 
 /* out[tau, :] = X[ids[tau], :]  (ids on device). */
@@ -223,7 +259,9 @@ int kmb_kpp_select(int dtype, const double* bsum, const double* pots_in, int t, 
  * axis=1 (common/reductions.py:214-393) at drivers.py:478. */
 int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* workspace,
                  size_t workspace_bytes, void* stream);
-/* *out = sum_i v[i] (square=0) or sum_i v[i]^2 (square=1), float64, fixed order.
+/* *out = sum_i v[i] (square=0), sum_i v[i]^2 (square=1) or sum_i (v[i] - v[i]) (square=2:
+ * 0 when every element is finite, NaN otherwise -- the finiteness test of the input
+ * validation, sklearn_numba_dpex/kmeans/engine.py:319-331), float64, fixed order.
  * Replaces the 1-D make_sum_reduction_2d_kernel uses at drivers.py:470-476, 516-524,
  * 533-540. */
 int kmb_sum(int dtype, const void* v, int64_t len, int square, double* out, void* workspace,
@@ -258,6 +296,13 @@ double kmb_u64_to_unit_f64(uint64_t x);
  * path itself never calls. */
 int kmb_matmul_nt(int dtype, int algo, const void* X, const void* Y, void* out, int64_t m,
                   int n, int kdim, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Measurement hook for the benchmark: best-of-`repeats` FMA rate (TFLOP/s, 2 flops per FMA) of
+ * the CUDA cores in `dtype`, from a register-resident kernel timed with CUDA events; it is the
+ * roofline denominator of the KMB_ALGO_CUDA_CORE step.  `scratch` is any device buffer of at
+ * least 8 * 256 * (SM count) elements of `dtype` (never written in practice).  Waits for the
+ * stream.  No counterpart in the reference. */
+int kmb_measure_fma_peak(int dtype, int repeats, double* tflops, void* scratch, void* stream);
 
 #ifdef __cplusplus
 }

@@ -95,6 +95,14 @@
 DEFINE_ORACLE(float, f32)
 DEFINE_ORACLE(double, f64)
 
+void oracle_set_num_threads(int count) {
+#ifdef _OPENMP
+  if (count > 0) omp_set_num_threads(count);
+#else
+  (void)count;
+#endif
+}
+
 int oracle_num_threads(void) {
   int n = 1;
 #pragma omp parallel

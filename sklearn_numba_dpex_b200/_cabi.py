@@ -18,6 +18,8 @@ KMB_F32, KMB_F64 = 0, 1
 KMB_OK, KMB_ERR_INVALID, KMB_ERR_CUDA, KMB_ERR_UNSUPPORTED, KMB_ERR_WORKSPACE = 0, -1, -2, -3, -4
 ALGO_AUTO, ALGO_CUDA_CORE, ALGO_TF32X3 = 0, 1, 2
 ALGO_NAMES = {"auto": ALGO_AUTO, "cuda_core": ALGO_CUDA_CORE, "tf32x3": ALGO_TF32X3}
+STEP_ACC_CLEARED, STEP_OPERANDS_READY = 1, 2
+FIN_MERGE, FIN_CLEAR_ACC, FIN_PREPARE_TF32X3 = 1, 2, 4
 
 
 class KmbError(RuntimeError):
@@ -45,11 +47,13 @@ _SIGNATURES = {
     "kmb_lloyd_acc_copies": (c_int, [c_int, c_int, c_int64, c_int, c_int]),
     "kmb_lloyd_resolve_algo": (c_int, [c_int, c_int, c_int64, c_int, c_int]),
     "kmb_half_l2_norm": (c_int, [c_int, _P, _P, c_int, c_int, _P]),
+    "kmb_lloyd_workspace_init": (c_int, [_P, c_size_t, _P]),
     "kmb_lloyd_step": (c_int, [c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int64, c_int,
-                               c_int, _P, c_size_t, _P]),
-    "kmb_lloyd_tc_error": (c_int, [_P, c_int, c_int, POINTER(c_int), _P]),
-    "kmb_lloyd_merge_copies": (c_int, [c_int, _P, c_int, c_int64, _P, _P]),
-    "kmb_lloyd_finalize": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P]),
+                               c_int, c_int, _P, c_size_t, _P]),
+    "kmb_lloyd_wait_error": (c_int, [_P, POINTER(c_int), _P]),
+    "kmb_lloyd_merge_copies": (c_int, [c_int, _P, c_int, c_int64, _P, c_int, _P]),
+    "kmb_lloyd_finalize": (c_int, [c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, c_int,
+                                   c_int, _P, c_size_t, _P]),
     "kmb_assign_labels": (c_int, [c_int, c_int, _P, _P, _P, _P, c_int64, c_int, c_int, _P,
                                   c_size_t, _P]),
     "kmb_inertia": (c_int, [c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t,
@@ -77,6 +81,7 @@ _SIGNATURES = {
     "kmb_xoroshiro_next": (c_uint64, [POINTER(c_uint64), c_int]),
     "kmb_u64_to_unit_f32": (c_float, [c_uint64]),
     "kmb_u64_to_unit_f64": (c_double, [c_uint64]),
+    "kmb_measure_fma_peak": (c_int, [c_int, c_int, POINTER(c_double), _P, _P]),
     "kmb_matmul_nt": (c_int, [c_int, c_int, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t, _P]),
 }
 
@@ -152,9 +157,32 @@ class Workspace:
 
 
 def workspace_for(device, n, d, k):
+    """The shared scratch buffer of `device`, large enough for any call on these sizes.  Its
+    contents do not survive the next call that uses it."""
     nbytes = lib.kmb_workspace_bytes(int(n), int(d), int(k))
     buf = Workspace.get(device, nbytes)
     return buf, buf.numel()
+
+
+def lloyd_workspace(device, n, d, k, own=False):
+    """A workspace for the Lloyd entry points with its control block cleared: the shared
+    buffer, or (own=True) a buffer of its own whose tensor-core operands and time-out flag
+    persist between calls."""
+    if own:
+        nbytes = lib.kmb_workspace_bytes(int(n), int(d), int(k))
+        buf = torch.empty(int(nbytes) + 256, dtype=torch.uint8, device=device)
+    else:
+        buf, _ = workspace_for(device, n, d, k)
+    check(lib.kmb_lloyd_workspace_init(ptr(buf), buf.numel(), stream_ptr(device)),
+          "kmb_lloyd_workspace_init")
+    return buf, buf.numel()
+
+
+def check_wait_error(ws, device):
+    """Raises KmbError if a bounded wait of the tensor-core kernel ran out on `ws`."""
+    flag = c_int(0)
+    check(lib.kmb_lloyd_wait_error(ptr(ws), ctypes.byref(flag), stream_ptr(device)),
+          "kmb_lloyd_wait_error")
 
 
 def device_info(index=0):
@@ -164,5 +192,5 @@ def device_info(index=0):
 
 
 STATUS_DTYPE = np.dtype([("n_empty", np.int32), ("changed", np.int32), ("shift_total", np.float64),
-                         ("inertia", np.float64), ("reserved", np.float64)])
+                         ("inertia", np.float64), ("wait_error", np.int32), ("reserved", np.int32)])
 assert STATUS_DTYPE.itemsize == 32

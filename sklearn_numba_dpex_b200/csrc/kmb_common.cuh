@@ -63,6 +63,40 @@ inline int sm_count() {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Control block shared by the fused step and the finalize kernel.  It opens the Lloyd
+// workspace and is cleared by kmb_lloyd_workspace_init, never by a step.
+struct LloydControl {
+  int wait_error;        // raised by a bounded wait of the tensor-core kernel that ran out; sticky
+  unsigned int ticket;   // CTAs of the finalize kernel that have finished; reset by the last one
+};
+
+// Layout of the Lloyd workspace: [control block, 256 B | C_hi | C_lo | padded half norms], the
+// two matrices (k_pad x d_pad, fp32, rounded to tf32) being the B operands of the tensor-core
+// step.  k_pad = k rounded up to 128, d_pad = d rounded up to 32.
+struct LloydWorkspace {
+  LloydControl* ctl;
+  float* chi;
+  float* clo;
+  float* h_pad;
+  int k_pad, d_pad;
+  size_t bytes;          // from the caller's pointer to the end of the last array
+};
+
+inline LloydWorkspace lloyd_carve(void* workspace, int d, int k) {
+  LloydWorkspace w;
+  w.d_pad = (d + 31) / 32 * 32;
+  w.k_pad = (k + 127) / 128 * 128;
+  unsigned char* p = (unsigned char*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
+  const size_t mat = ((size_t)w.k_pad * w.d_pad * sizeof(float) + 255) / 256 * 256;
+  const size_t hb = ((size_t)w.k_pad * sizeof(float) + 255) / 256 * 256;
+  w.ctl = (LloydControl*)p;
+  w.chi = (float*)(p + 256);
+  w.clo = (float*)(p + 256 + mat);
+  w.h_pad = (float*)(p + 256 + 2 * mat);
+  w.bytes = (size_t)(p - (unsigned char*)workspace) + 256 + 2 * mat + hb;
+  return w;
+}
+
 // 16-byte vectors of consecutive features: 4 floats or 2 doubles per lane.
 template <typename T>
 struct RowVec;

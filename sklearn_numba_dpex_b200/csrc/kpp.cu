@@ -324,7 +324,7 @@ template <typename T>
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
                   const int32_t* __restrict__ best, const T* __restrict__ total,
-                  const T* __restrict__ u, const T* __restrict__ offset,
+                  const T* __restrict__ u, const double* __restrict__ offset,
                   int32_t* __restrict__ cand, int64_t n, int64_t nb) {
   __shared__ double scan_s[KPP_THREADS];
   __shared__ double carry_s;
@@ -335,7 +335,7 @@ kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
   const double* bs = bsum + (int64_t)b * nb;
   const T r_t = u[blockIdx.x] * total[0];
   // on a row shard the threshold is taken relative to the potential held by earlier shards
-  const double r = (double)r_t - (offset ? (double)offset[0] : 0.0);
+  const double r = (double)r_t - (offset ? offset[0] : 0.0);
   if (!(r > 0.0)) {
     if (tid == 0) cand[blockIdx.x] = 0;
     return;
@@ -554,14 +554,14 @@ int kmb_kpp_init(int dtype, const void* X, const void* w, int64_t first, const v
 }
 
 int kmb_kpp_sample(int dtype, const void* M, const double* bsum, const int32_t* best,
-                   const void* total, const void* u, const void* offset, int t, int32_t* cand,
+                   const void* total, const void* u, const double* offset, int t, int32_t* cand,
                    int64_t n, void* stream) {
   KMB_REQUIRE(M && bsum && total && u && cand, "kmb_kpp_sample: NULL argument");
   KMB_REQUIRE(n > 0 && t > 0 && t <= KPP_MAX_T, "kmb_kpp_sample: bad sizes");
   const int64_t nb = ceil_div(n, KPP_BLOCK);
   KMB_DISPATCH_DTYPE(dtype, {
     kpp_sample_kernel<T><<<t, KPP_THREADS, 0, (cudaStream_t)stream>>>(
-        (const T*)M, bsum, best, (const T*)total, (const T*)u, (const T*)offset, cand, n, nb);
+        (const T*)M, bsum, best, (const T*)total, (const T*)u, offset, cand, n, nb);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;

@@ -14,10 +14,9 @@ bool lloyd_tc_supported(int dtype, int64_t n, int d, int k);
 bool lloyd_tc_preferred(int dtype, int64_t n, int d, int k);
 int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
                  const uint32_t* prev, uint32_t* labels, float* acc, int n_copies,
-                 int64_t acc_len, int64_t n, int d, int k, bool update, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream);
+                 int64_t acc_len, int64_t n, int d, int k, bool update, bool operands_ready,
+                 void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int lloyd_tc_acc_copies(int d, int k);
-int lloyd_tc_error_flag_offset(void* workspace, int d, int k, size_t* offset);
 }  // namespace kmb
 
 using namespace kmb;
@@ -55,15 +54,15 @@ int kmb_lloyd_acc_copies(int dtype, int algo, int64_t n, int d, int k) {
   return lloyd_cc_privatises(dtype, d, k) ? 1 : 8;
 }
 
-int kmb_lloyd_tc_error(const void* workspace, int d, int k, int* host_flag, void* stream) {
-  KMB_REQUIRE(workspace && host_flag && d > 0 && k > 0, "kmb_lloyd_tc_error: bad arguments");
-  size_t off = 0;
-  lloyd_tc_error_flag_offset(const_cast<void*>(workspace), d, k, &off);
-  KMB_CHECK_CUDA(cudaMemcpyAsync(host_flag, (const unsigned char*)workspace + off, sizeof(int),
+int kmb_lloyd_wait_error(const void* workspace, int* host_flag, void* stream) {
+  KMB_REQUIRE(workspace && host_flag, "kmb_lloyd_wait_error: bad arguments");
+  LloydWorkspace ws = lloyd_carve(const_cast<void*>(workspace), 1, 1);
+  KMB_CHECK_CUDA(cudaMemcpyAsync(host_flag, &ws.ctl->wait_error, sizeof(int),
                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   KMB_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (*host_flag != 0) {
-    set_error("a bounded wait inside the tcgen05 Lloyd kernel ran out; its results are invalid");
+    set_error("a bounded wait inside the tcgen05 Lloyd kernel ran out; results computed on this "
+              "workspace since its last kmb_lloyd_workspace_init are invalid");
     return KMB_ERR_CUDA;
   }
   return KMB_OK;
@@ -71,21 +70,25 @@ int kmb_lloyd_tc_error(const void* workspace, int d, int k, int* host_flag, void
 
 int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void* C,
                    const void* half_norms, const uint32_t* prev_labels, uint32_t* labels,
-                   void* acc, int n_copies, int64_t n, int d, int k, void* workspace,
+                   void* acc, int n_copies, int64_t n, int d, int k, int flags, void* workspace,
                    size_t workspace_bytes, void* stream) {
   KMB_REQUIRE(X && C && half_norms && labels && acc, "kmb_lloyd_step: NULL argument");
   KMB_REQUIRE(n >= 0 && d > 0 && k > 0 && n_copies >= 1, "kmb_lloyd_step: bad sizes");
   KMB_REQUIRE((int64_t)k * d < (1ll << 31), "kmb_lloyd_step: k*d must be below 2^31");
   const int r = kmb_lloyd_resolve_algo(dtype, algo, n, d, k);
   if (r < 0) return r;
+  KMB_REQUIRE((flags & ~(KMB_STEP_ACC_CLEARED | KMB_STEP_OPERANDS_READY)) == 0,
+              "kmb_lloyd_step: unknown flag bits %d", flags);
   const int64_t acc_len = kmb_lloyd_acc_len(d, k);
   const size_t esize = dtype == KMB_F32 ? 4 : 8;
-  KMB_CHECK_CUDA(cudaMemsetAsync(acc, 0, (size_t)n_copies * acc_len * esize, (cudaStream_t)stream));
+  if (!(flags & KMB_STEP_ACC_CLEARED))
+    KMB_CHECK_CUDA(cudaMemsetAsync(acc, 0, (size_t)n_copies * acc_len * esize, (cudaStream_t)stream));
   if (n == 0) return KMB_OK;
   if (r == KMB_ALGO_TF32X3)
     return lloyd_tc_run((const float*)X, (const float*)w, (const float*)C,
                         (const float*)half_norms, prev_labels, labels, (float*)acc, n_copies,
-                        acc_len, n, d, k, true, workspace, workspace_bytes, (cudaStream_t)stream);
+                        acc_len, n, d, k, true, (flags & KMB_STEP_OPERANDS_READY) != 0, workspace,
+                        workspace_bytes, (cudaStream_t)stream);
   return lloyd_cc_step(dtype, X, w, C, half_norms, prev_labels, labels, acc, n_copies, acc_len, n,
                        d, k, (cudaStream_t)stream);
 }
@@ -101,7 +104,7 @@ int kmb_assign_labels(int dtype, int algo, const void* X, const void* C, const v
   if (n == 0) return KMB_OK;
   if (r == KMB_ALGO_TF32X3)
     return lloyd_tc_run((const float*)X, nullptr, (const float*)C, (const float*)half_norms,
-                        nullptr, labels, nullptr, 1, 0, n, d, k, false, workspace,
+                        nullptr, labels, nullptr, 1, 0, n, d, k, false, false, workspace,
                         workspace_bytes, (cudaStream_t)stream);
   return lloyd_cc_assign(dtype, X, C, half_norms, labels, n, d, k, (cudaStream_t)stream);
 }

@@ -775,7 +775,7 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols,
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 bool lloyd_tc_supported(int dtype, int64_t n, int d, int k) {
-  return dtype == KMB_F32 && n >= 1 && n < (1ll << 31) - TC_BM && d >= 4 && d % 4 == 0 &&
+  return dtype == KMB_F32 && n >= 0 && n < (1ll << 31) - TC_BM && d >= 4 && d % 4 == 0 &&
          d <= TC_MAX_D && k >= 1 && k <= 65536;
 }
 
@@ -789,31 +789,11 @@ bool lloyd_tc_preferred(int dtype, int64_t n, int d, int k) {
 
 int lloyd_tc_acc_copies(int, int) { return 16; }
 
-struct TcWorkspace {
-  float* chi;
-  float* clo;
-  float* h_pad;
-  int* error_flag;
-  size_t bytes;
-};
-
-static TcWorkspace carve(void* workspace, int k_pad, int d_pad) {
-  TcWorkspace w;
-  unsigned char* p = (unsigned char*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
-  const size_t mat = ((size_t)k_pad * d_pad * sizeof(float) + 255) / 256 * 256;
-  w.chi = (float*)p;
-  w.clo = (float*)(p + mat);
-  w.h_pad = (float*)(p + 2 * mat);
-  const size_t hb = ((size_t)k_pad * sizeof(float) + 255) / 256 * 256;
-  w.error_flag = (int*)(p + 2 * mat + hb);
-  w.bytes = (size_t)(p - (unsigned char*)workspace) + 2 * mat + hb + 256;
-  return w;
-}
-
 static int tc_launch(const float* X, const float* w, const float* C, const float* h,
                      const uint32_t* prev, uint32_t* labels, float* acc, int n_copies,
-                     int64_t acc_len, float* dots, int ldd, int64_t n, int d, int k, void* workspace,
-                     size_t workspace_bytes, cudaStream_t stream) {
+                     int64_t acc_len, float* dots, int ldd, int64_t n, int d, int k,
+                     bool operands_ready, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream) {
   KMB_REQUIRE(lloyd_tc_supported(KMB_F32, n, d, k), "tcgen05 step: unsupported shape n=%lld d=%d k=%d",
               (long long)n, d, k);
   KMB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)C & 15) == 0,
@@ -821,13 +801,13 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   KMB_REQUIRE(acc == nullptr || ((uintptr_t)acc & 15) == 0, "tcgen05 step: acc must be 16-byte aligned");
   const int d_pad = round_up(d, TC_KC), k_pad = round_up(k, TC_BN);
   KMB_REQUIRE(workspace != nullptr, "tcgen05 step: workspace is NULL");
-  TcWorkspace ws = carve(workspace, k_pad, d_pad);
+  LloydWorkspace ws = lloyd_carve(workspace, d, k);
   if (ws.bytes > workspace_bytes) {
     set_error("tcgen05 step: workspace of %zu bytes needed, %zu given", ws.bytes, workspace_bytes);
     return KMB_ERR_WORKSPACE;
   }
-  KMB_CHECK_CUDA(cudaMemsetAsync(ws.error_flag, 0, sizeof(int), stream));
-  {
+  // The time-out flag in the control block is sticky: only kmb_lloyd_workspace_init clears it.
+  if (!operands_ready) {
     const int64_t total = (int64_t)k_pad * d_pad;
     int grid = (int)ceil_div(total, 256);
     if (grid > 1184) grid = 1184;
@@ -843,7 +823,7 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
 
   TcParams p;
   p.X = X; p.w = w; p.h_pad = ws.h_pad; p.prev = prev; p.labels = labels; p.acc = acc;
-  p.dots = dots; p.error_flag = ws.error_flag; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
+  p.dots = dots; p.error_flag = &ws.ctl->wait_error; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
 
   const int64_t n_tiles = ceil_div(n, TC_BM);
@@ -859,17 +839,16 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
 
 int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
                  const uint32_t* prev, uint32_t* labels, float* acc, int n_copies, int64_t acc_len,
-                 int64_t n, int d, int k, bool update, void* workspace, size_t workspace_bytes,
-                 cudaStream_t stream) {
+                 int64_t n, int d, int k, bool update, bool operands_ready, void* workspace,
+                 size_t workspace_bytes, cudaStream_t stream) {
   return tc_launch(X, w, C, h, prev, labels, update ? acc : nullptr, n_copies, acc_len, nullptr, 0, n,
-                   d, k, workspace, workspace_bytes, stream);
+                   d, k, operands_ready, workspace, workspace_bytes, stream);
 }
 
 // out[i, j] = X[i, :] . Y[j, :] with the 3xTF32 pipeline; labels go to scratch in the workspace.
 int lloyd_tc_matmul(const float* X, const float* Y, float* out, int64_t m, int n, int kdim,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-  const int d_pad = round_up(kdim, TC_KC), k_pad = round_up(n, TC_BN);
-  TcWorkspace ws = carve(workspace, k_pad, d_pad);
+  LloydWorkspace ws = lloyd_carve(workspace, kdim, n);
   const size_t lab_bytes = ((size_t)m * sizeof(uint32_t) + 255) / 256 * 256;
   if (workspace == nullptr || ws.bytes + lab_bytes > workspace_bytes) {
     set_error("kmb_matmul_nt: workspace of %zu bytes needed, %zu given", ws.bytes + lab_bytes,
@@ -877,16 +856,8 @@ int lloyd_tc_matmul(const float* X, const float* Y, float* out, int64_t m, int n
     return KMB_ERR_WORKSPACE;
   }
   uint32_t* labels = (uint32_t*)((unsigned char*)workspace + ws.bytes);
-  return tc_launch(X, nullptr, Y, nullptr, nullptr, labels, nullptr, 1, 0, out, n, m, kdim, n,
+  return tc_launch(X, nullptr, Y, nullptr, nullptr, labels, nullptr, 1, 0, out, n, m, kdim, n, false,
                    workspace, workspace_bytes, stream);
-}
-
-// Non-zero when a bounded wait inside the last tcgen05 step on this workspace ran out.
-int lloyd_tc_error_flag_offset(void* workspace, int d, int k, size_t* offset) {
-  const int d_pad = round_up(d, TC_KC), k_pad = round_up(k, TC_BN);
-  TcWorkspace ws = carve(workspace, k_pad, d_pad);
-  *offset = (size_t)((unsigned char*)ws.error_flag - (unsigned char*)workspace);
-  return KMB_OK;
 }
 
 }  // namespace kmb

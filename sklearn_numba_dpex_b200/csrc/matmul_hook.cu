@@ -72,3 +72,62 @@ extern "C" int kmb_matmul_nt(int dtype, int algo, const void* X, const void* Y, 
   });
   return KMB_OK;
 }
+
+// ---- measurement hook: FMA issue rate of the CUDA cores ------------------------------------
+// Every thread runs 16 independent register-resident FMA chains; nothing touches memory until
+// the final store, so the figure is the pipe's own ceiling for the CUDA-core step.
+namespace kmb {
+template <typename T>
+__global__ void __launch_bounds__(256) fma_peak_kernel(T* out, int iters, T a, T b) {
+  T acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = (T)(threadIdx.x + i);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = fma(acc[i], a, b);
+  }
+  T s = T(0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += acc[i];
+  if (s == (T)-1.2345) out[blockIdx.x * blockDim.x + threadIdx.x] = s;   // keeps the chains alive
+}
+}  // namespace kmb
+
+extern "C" int kmb_measure_fma_peak(int dtype, int repeats, double* tflops, void* scratch,
+                                    void* stream) {
+  KMB_REQUIRE(tflops && scratch && repeats >= 1, "kmb_measure_fma_peak: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = sm_count() * 8, threads = 256;
+  const int iters = dtype == KMB_F32 ? 16384 : 2048;
+  cudaEvent_t e0, e1;
+  KMB_CHECK_CUDA(cudaEventCreate(&e0));
+  KMB_CHECK_CUDA(cudaEventCreate(&e1));
+  double best = 0.0;
+  int rc = KMB_OK;
+  for (int r = 0; r < repeats + 2 && rc == KMB_OK; ++r) {
+    cudaEventRecord(e0, s);
+    if (dtype == KMB_F32)
+      fma_peak_kernel<float><<<blocks, threads, 0, s>>>((float*)scratch, iters, 0.999f, 0.001f);
+    else if (dtype == KMB_F64)
+      fma_peak_kernel<double><<<blocks, threads, 0, s>>>((double*)scratch, iters, 0.999, 0.001);
+    else {
+      set_error("dtype must be KMB_F32 or KMB_F64, got %d", dtype);
+      rc = KMB_ERR_INVALID;
+      break;
+    }
+    cudaEventRecord(e1, s);
+    if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+      set_error("kmb_measure_fma_peak: kernel failed");
+      rc = KMB_ERR_CUDA;
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    const double tf = 2.0 * 16.0 * iters * (double)blocks * threads / (ms * 1e-3) / 1e12;
+    if (r >= 2 && tf > best) best = tf;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *tflops = best;
+  return rc;
+}

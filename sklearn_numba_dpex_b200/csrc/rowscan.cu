@@ -204,7 +204,7 @@ sum_kernel(const T* __restrict__ v, int64_t len, int square, double* __restrict_
   for (int64_t e = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x; e < len;
        e += (int64_t)gridDim.x * RS_THREADS) {
     const double x = (double)v[e];
-    s += square ? x * x : x;
+    s += square == 1 ? x * x : (square == 2 ? x - x : x);   // x - x: 0 when finite, else NaN
   }
   const double tot = block_sum(s, red);
   if (threadIdx.x == 0) partial[blockIdx.x] = tot;
@@ -405,7 +405,7 @@ int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* 
 
 int kmb_sum(int dtype, const void* v, int64_t len, int square, double* out, void* workspace,
             size_t workspace_bytes, void* stream) {
-  KMB_REQUIRE(out && len >= 0 && (v || len == 0), "kmb_sum: bad arguments");
+  KMB_REQUIRE(out && len >= 0 && (v || len == 0) && square >= 0 && square <= 2, "kmb_sum: bad arguments");
   cudaStream_t s = (cudaStream_t)stream;
   const int grid = scan_grid(RS_THREADS * 8, len > 0 ? len : 1);
   const size_t need = (size_t)grid * sizeof(double);

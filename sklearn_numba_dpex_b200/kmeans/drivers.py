@@ -16,8 +16,10 @@ import numpy as np
 import torch
 
 from .. import dist
-from .._cabi import (ALGO_AUTO, ALGO_NAMES, STATUS_DTYPE, c_void_p, check, dtype_code, lib, ptr,
-                     stream_ptr, workspace_for)
+from .._cabi import (ALGO_AUTO, ALGO_NAMES, FIN_CLEAR_ACC, FIN_MERGE, FIN_PREPARE_TF32X3,
+                     STATUS_DTYPE, STEP_ACC_CLEARED, STEP_OPERANDS_READY, KmbError, c_void_p, check,
+                     check_wait_error, dtype_code, lib, lloyd_workspace, ptr, stream_ptr,
+                     workspace_for)
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -57,6 +59,9 @@ def _read_status(status_dev, status_host):
     status_host.copy_(status_dev, non_blocking=True)
     torch.cuda.current_stream(status_dev.device).synchronize()
     rec = status_host.numpy().view(STATUS_DTYPE)[0]
+    if int(rec["wait_error"]) != 0:
+        raise KmbError("a bounded wait inside the tcgen05 Lloyd kernel ran out; the results of "
+                       "this iteration are invalid")
     return int(rec["n_empty"]), int(rec["changed"]), float(rec["shift_total"])
 
 
@@ -74,9 +79,13 @@ class LloydState:
         # The tensor-core step moves sample tiles with TMA, whose row pitch must be a multiple
         # of 16 bytes: when it is wanted and d is not a multiple of 4, work on a copy of the
         # samples and centres padded with zero features (distances and sums are unchanged).
+        # Over row shards the choice follows the TOTAL number of rows, so that every rank takes
+        # the same kernel and the same padding whatever the size of its own shard.
+        n_policy = int(sum(dist.all_gather_object(int(n)))) if dist.active() else n
         d4 = (d + 3) // 4 * 4
         if (dt == torch.float32 and d4 != d and want != ALGO_NAMES["cuda_core"]
-                and lib.kmb_lloyd_resolve_algo(self.dtype, want, n, d4, k) == ALGO_NAMES["tf32x3"]):
+                and lib.kmb_lloyd_resolve_algo(self.dtype, want, n_policy, d4, k)
+                == ALGO_NAMES["tf32x3"]):
             Xp = torch.zeros((n, d4), dtype=dt, device=dev)
             Xp[:, :d] = X
             Cp = torch.zeros((k, d4), dtype=dt, device=dev)
@@ -85,7 +94,7 @@ class LloydState:
         self.X = X
         self.w = sample_weight
         self.n, self.d, self.k = n, d, k
-        self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, want, n, d, k),
+        self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, want, n_policy, d, k),
                           "kmb_lloyd_resolve_algo")
         self.acc_len = lib.kmb_lloyd_acc_len(d, k)
         self.n_copies = check(lib.kmb_lloyd_acc_copies(self.dtype, self.algo, n, d, k))
@@ -96,46 +105,68 @@ class LloydState:
         self.shifts = torch.empty(k, dtype=dt, device=dev)
         self.labels = torch.empty(n, dtype=torch.int32, device=dev)
         self.labels_new = torch.empty(n, dtype=torch.int32, device=dev)
-        self.acc = torch.empty((self.n_copies, self.acc_len), dtype=dt, device=dev)
-        self.packed = (self.acc[0] if self.n_copies == 1
-                       else torch.empty(self.acc_len, dtype=dt, device=dev))
+        # The copies start at zero and every finalize (or merge) clears them again once read,
+        # so no step has to clear them.
+        self.acc = torch.zeros((self.n_copies, self.acc_len), dtype=dt, device=dev)
+        self.packed = torch.empty(self.acc_len, dtype=dt, device=dev)
         self.empty_list = torch.empty(k, dtype=torch.int32, device=dev)
         self.status_dev = torch.empty(32, dtype=torch.uint8, device=dev)
         self.status_host = torch.empty(32, dtype=torch.uint8).pin_memory()
-        self.ws, self.ws_bytes = workspace_for(dev, n, d, k)
+        # A workspace of this state's own: the tensor-core operands that a finalize writes for
+        # the next step, and the sticky time-out flag, live there between calls.  The row-scan
+        # calls of this state (inertia, top-k) use the shared scratch buffer instead.
+        self.ws, self.ws_bytes = lloyd_workspace(dev, n, d, k, own=True)
+        self.scratch, self.scratch_bytes = workspace_for(dev, n, d, k)
         self.sq_dist = None
         self.have_prev = False
+        self.operands_ready = False
         self.kernel_launches = 0
-        # kernels behind one kmb_lloyd_step: the tensor-core step first splits the centroids
-        self.step_kernels = 2 if self.algo == ALGO_NAMES["tf32x3"] else 1
+        self.is_tc = self.algo == ALGO_NAMES["tf32x3"]
         check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
               "kmb_half_l2_norm")
         self.kernel_launches += 1
 
     # -- pieces -----------------------------------------------------------------------
-    def _finalize(self):
-        check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.packed), ptr(self.C), ptr(self.C_new),
-                                     ptr(self.h_new), ptr(self.shifts), ptr(self.empty_list),
-                                     ptr(self.status_dev), self.k, self.d,
+    def _finalize(self, merge, clear):
+        """One kernel: (merge of the copies,) division, shifts, next half norms, operands of
+        the next tensor-core step, empty list, status record."""
+        flags = (FIN_MERGE if merge else 0) | (FIN_CLEAR_ACC if clear else 0) | \
+            (FIN_PREPARE_TF32X3 if self.is_tc else 0)
+        check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.acc), self.n_copies, ptr(self.packed),
+                                     flags, ptr(self.C), ptr(self.C_new), ptr(self.h_new),
+                                     ptr(self.shifts), ptr(self.empty_list), ptr(self.status_dev),
+                                     self.k, self.d, ptr(self.ws), self.ws_bytes,
                                      stream_ptr(self.X.device)), "kmb_lloyd_finalize")
-        self.kernel_launches += 2
+        self.kernel_launches += 1
 
-    def launch_step(self):
-        """E-step + accumulation + reduction + finalize, all enqueued (no host read)."""
-        dev = self.X.device
+    def launch_fused_step(self):
+        """The fused kernel alone: labels of the new assignment and the accumulator copies."""
+        flags = STEP_ACC_CLEARED | (STEP_OPERANDS_READY if self.operands_ready else 0)
         check(lib.kmb_lloyd_step(self.dtype, self.algo, ptr(self.X), ptr(self.w), ptr(self.C),
                                  ptr(self.h), ptr(self.labels) if self.have_prev else None,
                                  ptr(self.labels_new), ptr(self.acc), self.n_copies, self.n,
-                                 self.d, self.k, ptr(self.ws), self.ws_bytes, stream_ptr(dev)),
-              "kmb_lloyd_step")
-        self.kernel_launches += self.step_kernels
-        if self.n_copies > 1:
+                                 self.d, self.k, flags, ptr(self.ws), self.ws_bytes,
+                                 stream_ptr(self.X.device)), "kmb_lloyd_step")
+        self.kernel_launches += 1 + (1 if self.is_tc and not self.operands_ready else 0)
+
+    def launch_reduce_finalize(self):
+        """Everything of an iteration after the fused kernel, enqueued without a host read:
+        one kernel on one GPU; merge, all-reduce, finalize over row shards."""
+        if dist.active():
             check(lib.kmb_lloyd_merge_copies(self.dtype, ptr(self.acc), self.n_copies,
-                                             self.acc_len, ptr(self.packed), stream_ptr(dev)),
-                  "kmb_lloyd_merge_copies")
+                                             self.acc_len, ptr(self.packed), 1,
+                                             stream_ptr(self.X.device)), "kmb_lloyd_merge_copies")
             self.kernel_launches += 1
-        dist.all_reduce_sum_(self.packed)
-        self._finalize()
+            dist.all_reduce_sum_(self.packed)
+            self._finalize(merge=False, clear=False)
+        else:
+            self._finalize(merge=True, clear=True)
+        self.operands_ready = self.is_tc
+
+    def launch_step(self):
+        """E-step + accumulation + reduction + finalize, all enqueued (no host read)."""
+        self.launch_fused_step()
+        self.launch_reduce_finalize()
 
     def _relocate(self, n_empty):
         """kmeans/drivers.py:238-272 and 396-433 of the reference.  The distances that rank
@@ -146,7 +177,8 @@ class LloydState:
             self.sq_dist = torch.empty(self.n, dtype=dt, device=dev)
         check(lib.kmb_inertia(self.dtype, ptr(self.X), None, ptr(self.packed),
                               ptr(self.labels_new), ptr(self.sq_dist), None, self.n, self.d,
-                              self.k, ptr(self.ws), self.ws_bytes, stream_ptr(dev)), "kmb_inertia")
+                              self.k, ptr(self.scratch), self.scratch_bytes, stream_ptr(dev)),
+              "kmb_inertia")
         m_local = min(n_empty, self.n)
         far = topk_idx_1d(self.sq_dist, m_local) if m_local > 0 else \
             torch.empty(0, dtype=torch.int64, device=dev)
@@ -160,12 +192,34 @@ class LloydState:
                                               ptr(self.packed), self.d, self.k, stream_ptr(dev)),
               "kmb_relocate_empty_clusters")
         self.kernel_launches += 2
-        self._finalize()
+        self._finalize(merge=False, clear=False)
 
-    def step(self):
-        """One Lloyd iteration.  Returns (n_empty_before_relocation, changed, shift_total)."""
+    def inertia_against_sums(self):
+        """What the reference prints per iteration when verbose: the weighted inertia of the
+        NEW assignments against `new_centroids_t` as it stands at that point of the loop, i.e.
+        the merged sums before relocation and before the division by the cluster sizes
+        (kmeans/drivers.py:223-236 of the reference run ahead of :275)."""
+        dev = self.X.device
+        total = torch.empty(1, dtype=self.X.dtype, device=dev)
+        check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.packed),
+                              ptr(self.labels_new), None, ptr(total), self.n, self.d, self.k,
+                              ptr(self.scratch), self.scratch_bytes, stream_ptr(dev)), "kmb_inertia")
+        self.kernel_launches += 2
+        dist.all_reduce_sum_(total)
+        return float(total[0])
+
+    def step(self, before_relocation=None):
+        """One Lloyd iteration.  Returns (n_empty_before_relocation, changed, shift_total).
+        `before_relocation`, when given, is called once the merged sums and the new labels
+        exist and before empty clusters are relocated."""
         self.launch_step()
-        n_empty, changed, shift = _read_status(self.status_dev, self.status_host)
+        try:
+            n_empty, changed, shift = _read_status(self.status_dev, self.status_host)
+        except KmbError:
+            self.operands_ready = False     # the buffers were not swapped: C_new's operands are not C's
+            raise
+        if before_relocation is not None:
+            before_relocation(self)
         if n_empty > 0:
             self._relocate(n_empty)
             _, _, shift = _read_status(self.status_dev, self.status_host)
@@ -180,11 +234,12 @@ class LloydState:
         check(lib.kmb_assign_labels(self.dtype, self.algo, ptr(self.X), ptr(self.C), ptr(self.h),
                                     ptr(self.labels), self.n, self.d, self.k, ptr(self.ws),
                                     self.ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+        self.operands_ready = False
         total = torch.empty(1, dtype=self.X.dtype, device=dev)
         check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.C), ptr(self.labels),
-                              None, ptr(total), self.n, self.d, self.k, ptr(self.ws),
-                              self.ws_bytes, stream_ptr(dev)), "kmb_inertia")
-        self.kernel_launches += 3
+                              None, ptr(total), self.n, self.d, self.k, ptr(self.scratch),
+                              self.scratch_bytes, stream_ptr(dev)), "kmb_inertia")
+        self.kernel_launches += 3 + (1 if self.is_tc else 0)
         dist.all_reduce_sum_(total)
         self.check_device_waits()
         return self.labels, total
@@ -196,12 +251,10 @@ class LloydState:
         return self.C[:, : self.d_orig].contiguous()
 
     def check_device_waits(self):
-        """Raises if a bounded wait inside the tensor-core kernel ran out on this workspace."""
-        if self.algo != ALGO_NAMES["tf32x3"]:
-            return
-        flag = ctypes.c_int(0)
-        check(lib.kmb_lloyd_tc_error(ptr(self.ws), self.d, self.k, ctypes.byref(flag),
-                                     stream_ptr(self.X.device)), "kmb_lloyd_tc_error")
+        """Raises if a bounded wait inside the tensor-core kernel ran out on this state's
+        workspace (the flag is sticky, so this covers every launch since the state was made)."""
+        if self.is_tc:
+            check_wait_error(self.ws, self.X.device)
 
 
 def _gather_relocation_candidates(state, far_local, n_empty):
@@ -234,7 +287,7 @@ def _gather_relocation_candidates(state, far_local, n_empty):
 
 # -------------------------------------------------------------------------------- lloyd
 def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, verbose=False,
-          tol=1e-4, algo="auto"):
+          tol=1e-4, algo="auto", stats=None):
     """Lloyd's algorithm.  Same contract as `lloyd` of the reference
     (sklearn_numba_dpex/kmeans/drivers.py:43-393): returns
     ``(labels (n,), inertia (host scalar of the compute dtype), centroids_t (d, k), n_iter)``.
@@ -242,6 +295,9 @@ def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, ve
     Labels are int32 holding the reference's uint32 values.  The strict-convergence test
     follows the reference: the flag is first armed after the second iteration, so the loop
     can stop on unchanged labels at the end of the third iteration at the earliest.
+
+    `stats`, when a dict, receives `n_relocation_events` (iterations that had to relocate empty
+    clusters), `n_empty_max` and `kernel_launches`.
     """
     X = _rows(X_t)
     C0 = _rows(centroids_t, "centroids_t")
@@ -261,17 +317,14 @@ def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, ve
     armed = False
     strict = False
     verbose = bool(verbose)
+    n_reloc_events, n_empty_max = 0, 0
     while n_iteration < max_iter and shift > tol:
-        _, changed, shift_total = state.step()
-        if verbose:
-            # the reference prints the inertia of the new assignments; here it is taken
-            # against the centroids the assignments were made with
-            total = torch.empty(1, dtype=X.dtype, device=X.device)
-            check(lib.kmb_inertia(state.dtype, ptr(X), ptr(w), ptr(state.C_new), ptr(state.labels),
-                                  None, ptr(total), state.n, state.d, state.k, ptr(state.ws),
-                                  state.ws_bytes, stream_ptr(X.device)))
-            dist.all_reduce_sum_(total)
-            print(f"Iteration {n_iteration}, inertia {float(total[0]):5.3e}")
+        def report(st, it=n_iteration):
+            print(f"Iteration {it}, inertia {st.inertia_against_sums():5.3e}")
+
+        n_empty, changed, shift_total = state.step(report if verbose else None)
+        n_reloc_events += int(n_empty > 0)
+        n_empty_max = max(n_empty_max, n_empty)
         n_iteration += 1
         if n_iteration > 1:
             if armed and changed == 0:
@@ -290,6 +343,9 @@ def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, ve
 
     labels, total = state.final_labels_inertia()
     inertia = total.cpu().numpy()[0]
+    if isinstance(stats, dict):
+        stats.update(n_relocation_events=n_reloc_events, n_empty_max=n_empty_max,
+                     kernel_launches=state.kernel_launches)
     return labels, inertia, state.centers().T, n_iteration
 
 
@@ -334,6 +390,33 @@ def _device_sum(t, square):
     ws, ws_bytes = workspace_for(dev, flat.numel(), 1, 1)
     check(lib.kmb_sum(dtype_code(t.dtype), ptr(flat), flat.numel(), int(square), ptr(out), ptr(ws),
                       ws_bytes, stream_ptr(dev)), "kmb_sum")
+    return out
+
+
+def all_finite(t):
+    """True when no element of the tensor is NaN or infinite (one pass on the device)."""
+    if t.numel() == 0:
+        return True
+    dev = t.device
+    t = t if t.is_contiguous() else t.contiguous()
+    out = torch.empty(1, dtype=torch.float64, device=dev)
+    flat = t.reshape(-1)
+    ws, ws_bytes = workspace_for(dev, flat.numel(), 1, 1)
+    check(lib.kmb_sum(dtype_code(t.dtype), ptr(flat), flat.numel(), 2, ptr(out), ptr(ws), ws_bytes,
+                      stream_ptr(dev)), "kmb_sum")
+    return float(out[0]) == 0.0
+
+
+def gather_rows(X, row_ids):
+    """X[row_ids] for host or device integer ids, gathered by the library (k, d)."""
+    dev = X.device
+    ids = torch.as_tensor(np.asarray(row_ids), dtype=torch.int32).to(dev) \
+        if not isinstance(row_ids, torch.Tensor) else row_ids.to(device=dev, dtype=torch.int32)
+    ids = ids.contiguous()
+    X = X if X.is_contiguous() else X.contiguous()
+    out = torch.empty((ids.numel(), X.shape[1]), dtype=X.dtype, device=dev)
+    check(lib.kmb_gather_rows(dtype_code(X.dtype), ptr(X), ptr(ids), ids.numel(), X.shape[1],
+                              ptr(out), stream_ptr(dev)), "kmb_gather_rows")
     return out
 
 
@@ -452,10 +535,12 @@ def get_labels_inertia(X_t, centroids_t, sample_weight, with_inertia, algo="auto
     code = dtype_code(X.dtype)
     h = torch.empty(k, dtype=X.dtype, device=dev)
     labels = torch.empty(n, dtype=torch.int32, device=dev)
-    ws, ws_bytes = workspace_for(dev, n, d, k)
+    ws, ws_bytes = lloyd_workspace(dev, n, d, k)
     check(lib.kmb_half_l2_norm(code, ptr(C), ptr(h), k, d, stream_ptr(dev)), "kmb_half_l2_norm")
     check(lib.kmb_assign_labels(code, _algo_code(algo), ptr(X), ptr(C), ptr(h), ptr(labels), n, d,
                                 k, ptr(ws), ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+    if lib.kmb_lloyd_resolve_algo(code, _algo_code(algo), n, d, k) == ALGO_NAMES["tf32x3"]:
+        check_wait_error(ws, dev)      # before the inertia call reuses the shared buffer
     if not with_inertia:
         return labels, None
     total = torch.empty(1, dtype=X.dtype, device=dev)
@@ -563,7 +648,7 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     for c in range(1, k):
         nxt = 1 - cur
         ends, my_offset = dist.shard_prefix(local_tot)               # float64
-        offset = my_offset.reshape(1).to(dt)
+        offset = my_offset.reshape(1).contiguous()                    # float64, as the kernel's scan
         check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
                                  ptr(u[c - 1]), ptr(offset), t, ptr(cand), n, s), "kmb_kpp_sample")
         check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),

@@ -16,9 +16,9 @@ import torch
 from sklearn.utils import check_array, check_random_state
 from sklearn.utils.validation import _is_arraylike_not_scalar
 
-from .drivers import (get_euclidean_distances, get_labels_inertia, get_nb_distinct_clusters,
-                      is_same_clustering, kmeans_plusplus, lloyd, prepare_data_for_lloyd,
-                      restore_data_after_lloyd)
+from .drivers import (all_finite, gather_rows, get_euclidean_distances, get_labels_inertia,
+                      get_nb_distinct_clusters, is_same_clustering, kmeans_plusplus, lloyd,
+                      prepare_data_for_lloyd, restore_data_after_lloyd)
 
 try:  # scikit-learn feature/engine-api branch
     from sklearn.cluster._kmeans import KMeansCythonEngine as _BaseEngine
@@ -34,6 +34,21 @@ except ImportError:  # released scikit-learn: no engine API
 
 
 TESTING_MODE_ENV = "SKLEARN_NUMBA_DPEX_B200_TESTING_MODE"
+
+
+def _check_array_no_finite_pass(array, **kwargs):
+    """sklearn's check_array without its host-side finiteness scan (the keyword changed name in
+    scikit-learn 1.6)."""
+    try:
+        return check_array(array, ensure_all_finite=False, **kwargs)
+    except TypeError:
+        return check_array(array, force_all_finite=False, **kwargs)
+
+
+def _upload(host_array, device):
+    """Host numpy array -> device tensor; asynchronous when the memory is page-locked."""
+    t = torch.as_tensor(host_array)
+    return t.to(device, non_blocking=t.is_pinned())
 
 
 class _DeviceUnset:
@@ -134,12 +149,20 @@ class KMeansEngine(_BaseEngine):
             centers = init(X, self.estimator.n_clusters, random_state=self.random_state)
             centers_t = self._check_init(centers, X)
         else:
-            # sampling without replacement is sequential: host numpy, as the reference
-            # (engine.py:188-196)
-            sample_weight_numpy = sample_weight.cpu().numpy()
+            # Sampling without replacement is sequential: host numpy, as the reference
+            # (engine.py:188-196), and the same index stream.  Uniform weights (known from
+            # prepare_fit) are rebuilt on the host from their first element instead of being
+            # copied back, which gives numpy the very same probabilities; the chosen rows are
+            # gathered on the device.
+            n_samples = X.shape[0]
+            if getattr(self, "sample_weight_is_uniform", False):
+                w0 = sample_weight[:1].cpu().numpy()[0]
+                sample_weight_numpy = np.full(n_samples, w0, dtype=w0.dtype)
+            else:
+                sample_weight_numpy = sample_weight.cpu().numpy()
             p = sample_weight_numpy / sample_weight_numpy.sum()
-            centers_idx = self.random_state.choice(X.shape[0], size=n_clusters, replace=False, p=p)
-            centers_t = X[torch.as_tensor(centers_idx, device=X.device)].T
+            centers_idx = self.random_state.choice(n_samples, size=n_clusters, replace=False, p=p)
+            centers_t = gather_rows(X, centers_idx).T
         return centers_t
 
     def _kmeans_plusplus(self, X, sample_weight):
@@ -231,12 +254,19 @@ class KMeansEngine(_BaseEngine):
                 Xd = Xd.contiguous()
             if Xd.shape[0] < 1:
                 raise ValueError("Found array with 0 sample(s) while a minimum of 1 is required.")
+            if not all_finite(Xd):
+                raise ValueError("Input X contains NaN or infinity.")
         else:
-            Xn = check_array(X, accept_sparse=False, dtype=[np.float64, np.float32], order="C",
-                             copy=False, estimator=estimator)
+            # shape / dtype / layout are validated on the host; the finiteness pass over the
+            # n x d values runs on the device after the upload (one kernel at HBM speed, where
+            # check_array would walk the array with the host cores first)
+            Xn = _check_array_no_finite_pass(X, accept_sparse=False, dtype=[np.float64, np.float32],
+                                             order="C", copy=False, estimator=estimator)
             if self._is_in_testing_mode and reset:
                 estimator._output_dtype = Xn.dtype.type
-            Xd = torch.as_tensor(Xn).to(device)
+            Xd = _upload(Xn, device)
+            if not all_finite(Xd):
+                raise ValueError("Input X contains NaN or infinity.")
         n_features = Xd.shape[1]
         if reset:
             estimator.n_features_in_ = n_features
@@ -255,6 +285,8 @@ class KMeansEngine(_BaseEngine):
             return torch.full((n_samples,), float(sample_weight), dtype=X.dtype, device=X.device)
         if isinstance(sample_weight, torch.Tensor):
             sw = sample_weight.to(device=X.device, dtype=X.dtype).contiguous()
+            if not all_finite(sw):
+                raise ValueError("Input sample_weight contains NaN or infinity.")
         else:
             sw = check_array(sample_weight, accept_sparse=False, order="C",
                              dtype=np.float64 if X.dtype == torch.float64 else np.float32,
@@ -274,6 +306,8 @@ class KMeansEngine(_BaseEngine):
             if init.dim() != 2:
                 raise ValueError(f"Expected 2D array, got {init.dim()}D array instead")
             init_d = init.to(device=X.device, dtype=X.dtype).contiguous().clone()
+            if not all_finite(init_d):
+                raise ValueError("Input init contains NaN or infinity.")
         else:
             init_n = check_array(init, dtype=np.float64 if X.dtype == torch.float64 else np.float32,
                                  accept_sparse=False, copy=True, order="C", ensure_2d=True,

@@ -103,9 +103,19 @@ def test_null_and_size_arguments_are_rejected_before_any_launch():
     lib = _cabi.lib
     p = ctypes.c_void_p(256)   # never dereferenced: every call below must fail validation first
     with pytest.raises(ValueError):
-        _cabi.check(lib.kmb_lloyd_step(0, 0, None, None, p, p, None, p, p, 1, 10, 4, 2, None, 0, None))
+        _cabi.check(lib.kmb_lloyd_step(0, 0, None, None, p, p, None, p, p, 1, 10, 4, 2, 0, None, 0, None))
     with pytest.raises(ValueError):
         _cabi.check(lib.kmb_assign_labels(0, 0, p, p, p, None, 10, 4, 2, None, 0, None))
+    with pytest.raises(ValueError):                                     # unknown flag bits
+        _cabi.check(lib.kmb_lloyd_step(0, 0, p, None, p, p, None, p, p, 1, 10, 4, 2, 64, p, 1 << 20, None))
+    with pytest.raises(ValueError):                                     # merge without the copies
+        _cabi.check(lib.kmb_lloyd_finalize(0, None, 1, p, _cabi.FIN_MERGE, p, p, p, p, p, p, 2, 4, p,
+                                           1 << 20, None))
+    with pytest.raises(ValueError):                                     # tensor-core operands are fp32
+        _cabi.check(lib.kmb_lloyd_finalize(1, p, 1, p, _cabi.FIN_PREPARE_TF32X3, p, p, p, p, p, p, 2, 4,
+                                           p, 1 << 20, None))
+    with pytest.raises(_cabi.KmbError):                                 # workspace too small
+        _cabi.check(lib.kmb_lloyd_finalize(0, None, 1, p, 0, p, p, p, p, p, p, 2, 4, p, 16, None))
     with pytest.raises(ValueError):
         _cabi.check(lib.kmb_inertia(0, None, None, p, p, p, p, 10, 4, 2, None, 0, None))
     with pytest.raises(ValueError):
@@ -115,3 +125,33 @@ def test_null_and_size_arguments_are_rejected_before_any_launch():
     with pytest.raises(ValueError):
         _cabi.check(lib.kmb_gather_rows(0, p, None, 1, 4, p, None))
     assert _cabi.last_error() != ""
+
+
+def test_reference_arm_uses_all_host_threads_under_a_launcher_that_exports_one():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm must set its
+    own thread count from the affinity mask and say how many threads it used."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", RANK="0", WORLD_SIZE="2", LOCAL_RANK="0")
+    out = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps",
+         "1", "--warmup", "0", "--cpu-sample-rows", "20000", "--config", "c2"],
+        capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][0])
+    assert line["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert line["cpu_baseline"]["extrapolated"] is True
+    # the other ranks of the launch print nothing and exit 0
+    env["RANK"] = "1"
+    out = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps",
+         "1", "--warmup", "0", "--cpu-sample-rows", "20000", "--config", "c2"],
+        capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_cpu_sample_is_deterministic_and_drawn_by_the_benchmark_generator():
+    cfg = dict(bench.CONFIGS["c2"])
+    X1, C1 = bench.cpu_sample(cfg, 5000)
+    bench._CPU_SAMPLES.clear()
+    X2, C2 = bench.cpu_sample(cfg, 5000)
+    assert X1.shape == (5000, cfg["d"]) and C1.shape == (cfg["k"], cfg["d"])
+    assert np.array_equal(X1, X2) and np.array_equal(C1, C2)

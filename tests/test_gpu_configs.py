@@ -1,0 +1,243 @@
+"""Parity at (or near) the shapes of the benchmark configurations that the small kernel tests
+do not reach: the fp64 configuration (n = 2 M, d = 32, k = 64: teacher-forced sums at the
+stated 1e-12, and a free-running tolerance stop), the seeding / relocation stress
+configuration (d = 64, k = 4096 with empty clusters on the tensor-core step), and the
+verbose loop on the padded tensor-core path.
+
+The checker for these sizes is the C restatement of the reference's iteration
+(oracle/lloyd_oracle.c, itself checked against the numpy oracle in tests/test_oracle_cport.py);
+everything after the E-step is the numpy oracle."""
+import re
+
+import numpy as np
+import pytest
+import torch
+from numpy.testing import assert_allclose, assert_array_equal
+
+from oracle import c_oracle
+from oracle import reference_cpu as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.as_tensor(np.ascontiguousarray(a)).cuda()
+
+
+def _exact_cluster_sums(X, w, labels, k):
+    """Cluster sums accumulated in extended precision (rows sorted by label, one segmented sum),
+    so that the comparison at 1e-12 is against a value with no rounding of its own."""
+    order = np.argsort(labels, kind="stable")
+    prod = (X * w[:, None]).astype(X.dtype)[order].astype(np.longdouble)
+    starts = np.searchsorted(labels[order], np.arange(k))
+    present = np.bincount(labels, minlength=k) > 0
+    sums = np.zeros((k, X.shape[1]), dtype=np.longdouble)
+    red = np.add.reduceat(prod, np.minimum(starts, len(order) - 1), axis=0)
+    sums[present] = red[present]
+    sizes = np.zeros(k, dtype=np.longdouble)
+    sizes[present] = np.add.reduceat(w[order].astype(np.longdouble),
+                                     np.minimum(starts, len(order) - 1))[present]
+    return sums.astype(np.float64), sizes.astype(np.float64)
+
+
+# --------------------------------------------------------------------------- fp64 (c4)
+@pytest.mark.parametrize("weighted", [False, True])
+def test_fp64_step_at_config_shape_teacher_forced(weighted):
+    """n = 200 000 rows of U[0,1]^32, k = 64, float64: one fused step from given centres.
+    Labels equal the C restatement's; sums, counts and new centres agree at rtol 1e-12 with an
+    extended-precision accumulation over the GPU's own labels (about 3 100 terms per sum)."""
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    n, d, k = 200_000, 32, 64
+    rng = np.random.default_rng(3)
+    X = rng.random((n, d))
+    C = X[rng.choice(n, size=k, replace=False)].copy()
+    w = rng.uniform(0.5, 2.0, n) if weighted else np.ones(n)
+    ref_labels, _, _, _ = c_oracle.lloyd_iteration(X, w if weighted else None, C)
+
+    st = LloydState(_dev(X), _dev(w) if weighted else None, _dev(C), "auto")
+    st.launch_step()
+    torch.cuda.synchronize()
+    labels = st.labels_new.cpu().numpy().astype(np.int64)
+    ok, n_bad, n_unexplained = ref.labels_agree(labels, ref_labels, X, C, rtol=1e-6)
+    assert ok and n_bad <= 2, (n_bad, n_unexplained)
+
+    sums, sizes = _exact_cluster_sums(X, w, labels, k)
+    packed = st.packed.cpu().numpy()
+    assert_allclose(packed[: k * d].reshape(k, d), sums, rtol=1e-12)
+    assert_allclose(packed[k * d: k * d + k], sizes, rtol=1e-12)
+    assert (sizes > 0).all()
+    assert_allclose(st.C_new.cpu().numpy(), sums / sizes[:, None], rtol=1e-12)
+    status = st.status_dev.cpu().numpy().view(_status_dtype())[0]
+    shift = ((C - sums / sizes[:, None]) ** 2).sum()
+    assert_allclose(status["shift_total"], shift, rtol=1e-10)
+    assert status["n_empty"] == 0 and status["wait_error"] == 0
+
+
+def test_fp64_config_free_running_tolerance_stop():
+    """The fp64 configuration as the estimator runs it (k-means++ from seed 3, tol = 1e-4
+    relative, max_iter = 300) on 200 000 rows of U[0,1]^32: the loop stops at the iteration the
+    restatement stops at (kmeans/drivers.py:188, 334-343 of the reference), with the same
+    labels and centres within 1e-12 x a small factor for the accumulated iterations."""
+    from sklearn_numba_dpex_b200.kmeans.drivers import kmeans_plusplus, lloyd
+
+    n, d, k = 200_000, 32, 64
+    X = np.random.default_rng(3).random((n, d))
+    w = np.ones(n)
+    Xc, _, _, tol, uni = ref.prepare_data_for_lloyd(X, "k-means++", 1e-4, w, True)
+    Xd, wd = _dev(Xc), _dev(w)
+    centers_t, _ = kmeans_plusplus(Xd.T, wd, k, np.random.RandomState(3))
+    init = centers_t.T.contiguous().cpu().numpy()
+
+    o_labels, o_C, o_iter, shifts = c_oracle.lloyd(Xc, None, init, 300, tol)
+    labels, inertia, C_t, n_iter = lloyd(Xd.T, wd, _dev(init).T, uni, 300, False, tol)
+    assert 3 < o_iter < 300, o_iter
+    # the stop must not hinge on rounding: the deciding shift is clear of the tolerance
+    assert shifts[-1] < tol * (1 - 1e-9) and shifts[-2] > tol * (1 + 1e-9)
+    assert n_iter == o_iter
+    got = labels.cpu().numpy()
+    ok, n_bad, n_unexplained = ref.labels_agree(got, o_labels, Xc, o_C)
+    assert ok, (n_bad, n_unexplained)
+    if n_bad == 0:
+        assert_allclose(C_t.T.cpu().numpy(), o_C, rtol=1e-10, atol=1e-12)
+    o_inertia = float((((Xc - o_C[o_labels.astype(np.int64)]) ** 2).sum(axis=1)).sum())
+    assert_allclose(float(inertia), o_inertia, rtol=1e-10)
+
+
+# ----------------------------------------------- seeding / relocation stress shape (c5)
+def _stress_rows(rng, n, d, blobs=512, outliers=0.1, box=50.0, std=0.1):
+    centres = rng.uniform(-box, box, size=(blobs, d))
+    X = centres[rng.integers(0, blobs, n)] + std * rng.standard_normal((n, d))
+    out = rng.random(n) < outliers
+    X[out] = rng.uniform(-box, box, size=(int(out.sum()), d))
+    return X.astype(np.float32)
+
+
+def test_relocation_stress_shape_on_the_tensor_core_step():
+    """d = 64, k = 4096, 90 % of the rows in 512 tight blobs and 10 % uniform outliers, on the
+    tensor-core step, with initial centres that contain duplicates so that clusters come out
+    empty: labels against the C restatement, then sums / counts / empty list and the relocation
+    (far samples ranked by their distance to the UN-NORMALISED sums, kmeans/drivers.py:238-272
+    and kmeans/kernels/utils.py:21-76 of the reference) against the numpy oracle."""
+    from sklearn_numba_dpex_b200 import _cabi
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    n, d, k = 400_000, 64, 4096
+    rng = np.random.default_rng(4)
+    X = _stress_rows(rng, n, d)
+    init = X[rng.choice(n, size=k, replace=False)].copy()
+    init[1::64] = init[0::64]            # 64 duplicated centres: the higher index never wins
+    w = np.ones(n, dtype=np.float32)
+    assert _cabi.lib.kmb_lloyd_resolve_algo(_cabi.KMB_F32, _cabi.ALGO_AUTO, n, d, k) == _cabi.ALGO_TF32X3
+
+    ref_labels, _, _, _ = c_oracle.lloyd_iteration(X, None, init, update=False)
+    st = LloydState(_dev(X), None, _dev(init), "auto")
+    st.launch_step()
+    torch.cuda.synchronize()
+    st.check_device_waits()
+    labels = st.labels_new.cpu().numpy().astype(np.int64)
+    ok, n_bad, n_unexplained = ref.labels_agree(labels, ref_labels, X, init, rtol=1e-6)
+    assert ok, (n_bad, n_unexplained)
+
+    sums, sizes = ref.accumulate_centroids(X.astype(np.float64), w.astype(np.float64), labels, k)
+    empty = np.nonzero(sizes == 0)[0]
+    assert empty.size >= 64
+    status = st.status_dev.cpu().numpy().view(_status_dtype())[0]
+    assert status["n_empty"] == empty.size
+    assert_array_equal(st.empty_list.cpu().numpy()[: empty.size], empty)
+    packed = st.packed.cpu().numpy().astype(np.float64)
+    scale = np.abs(X).max() * max(n / k, 1.0)
+    assert_allclose(packed[: k * d].reshape(k, d), sums, rtol=1e-5, atol=1e-5 * scale)
+    assert_array_equal(packed[k * d: k * d + k], sizes)
+
+    # relocation, from the GPU's own un-normalised sums.  Inside a tight blob the distances to
+    # the un-normalised sum differ by ~1e-8 relative from one member to the next, less than the
+    # rounding of an fp32 distance, so WHICH members rank highest legitimately depends on the
+    # arithmetic: the kernel's distances are checked against the oracle's within the fp32
+    # tolerance, and the selection / pairing rule (descending distance, ties by ascending index,
+    # paired with the empty clusters in ascending order) is then checked exactly on the kernel's
+    # own values.
+    sums32 = st.packed.cpu().numpy()[: k * d].reshape(k, d).copy()
+    sizes32 = st.packed.cpu().numpy()[k * d: k * d + k].copy()
+    m = int(empty.size)
+    st._relocate(m)
+    torch.cuda.synchronize()
+    sq_gpu = st.sq_dist.cpu().numpy()
+    sq = ref.compute_inertia_per_sample(X, np.ones_like(w), sums32, labels, exact=True)
+    assert_allclose(sq_gpu, sq, rtol=1e-5)
+    far = np.lexsort((np.arange(n), -sq_gpu.astype(np.float64)))[:m]
+    ref.relocate_empty_clusters(X, w, sums32, sizes32, labels, empty, far)
+
+    after = st.packed.cpu().numpy()
+    got_sums = after[: k * d].reshape(k, d)
+    got_sizes = after[k * d: k * d + k]
+    rest = np.setdiff1d(np.arange(k), empty)
+    assert_allclose(got_sums[rest], sums32[rest], rtol=1e-5, atol=1e-5 * scale)
+    assert_allclose(got_sizes[rest], sizes32[rest])
+    assert_array_equal(got_sizes[empty], np.ones(m, dtype=np.float32))
+    assert_array_equal(got_sums[empty], X[far])
+    # the centres of the relocated clusters are those rows, the status reports no empty cluster
+    status = st.status_dev.cpu().numpy().view(_status_dtype())[0]
+    assert status["n_empty"] == 0
+    assert_array_equal(st.C_new.cpu().numpy()[empty], X[far])
+
+
+def test_relocation_stress_fit_reports_events():
+    """A short free-running fit on the stress data with duplicated initial centres: the loop
+    relocates (events are counted), ends with no empty cluster and k distinct labels' worth of
+    centres that are all finite."""
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    n, d, k = 150_000, 64, 1024
+    rng = np.random.default_rng(4)
+    X = _stress_rows(rng, n, d)
+    init = X[rng.choice(n, size=k, replace=False)].copy()
+    init[1::32] = init[0::32]
+    st = LloydState(_dev(X), None, _dev(init), "auto")
+    events, n_empty_max = 0, 0
+    for _ in range(4):
+        n_empty, _, _ = st.step()
+        events += int(n_empty > 0)
+        n_empty_max = max(n_empty_max, n_empty)
+    assert events >= 1 and n_empty_max >= 32
+    assert torch.isfinite(st.C).all()
+    status = st.status_dev.cpu().numpy().view(_status_dtype())[0]
+    assert status["n_empty"] == 0
+
+
+# --------------------------------------------------------------------------- verbose
+def test_verbose_prints_the_reference_quantity_on_the_padded_path(capsys):
+    """lloyd(verbose=True) on a shape that runs on a zero-padded working copy (fp32, d = 14 ->
+    16, k = 256, n = 40 000): every iteration prints the inertia of the new assignments against
+    `new_centroids_t` as the reference has it at that point, i.e. the un-normalised sums
+    (kmeans/drivers.py:223-236 run before the division at :275)."""
+    from sklearn_numba_dpex_b200 import _cabi
+    from sklearn_numba_dpex_b200.kmeans.drivers import lloyd
+
+    n, d, k = 40_000, 14, 256
+    assert _cabi.lib.kmb_lloyd_resolve_algo(_cabi.KMB_F32, _cabi.ALGO_AUTO, n, 16, k) == _cabi.ALGO_TF32X3
+    rng = np.random.default_rng(1)
+    centres = rng.uniform(-10, 10, size=(k, d))
+    X = (centres[rng.integers(0, k, n)] + 1.5 * rng.standard_normal((n, d))).astype(np.float32)
+    w = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    init = X[rng.choice(n, size=k, replace=False)].copy()
+
+    labels, inertia, C_t, n_iter = lloyd(_dev(X).T, _dev(w), _dev(init).T, False, 2, True, 0.0)
+    out = capsys.readouterr().out
+    printed = [float(m) for m in re.findall(r"Iteration \d+, inertia ([0-9.e+-]+)", out)]
+    assert len(printed) == 2 and n_iter == 2
+
+    C = init
+    for it in range(2):
+        lab = ref.assign_labels(X, C).astype(np.int64)
+        sums, sizes = ref.accumulate_centroids(X, w, lab, k)
+        assert (sizes > 0).all()
+        expected = float(ref.compute_inertia_per_sample(X, w, sums, lab, exact=True).sum())
+        assert_allclose(printed[it], expected, rtol=2e-3)      # printed with 4 significant digits
+        C = (sums / sizes[:, None]).astype(np.float32)
+
+
+def _status_dtype():
+    from sklearn_numba_dpex_b200._cabi import STATUS_DTYPE
+
+    return STATUS_DTYPE

@@ -359,3 +359,113 @@ def test_strict_convergence_and_tolerance_stop(dtype):
         assert ok, (n_bad, n_unexplained)
         if n_bad == 0:
             assert_allclose(_np(g[2].T), o[2], rtol=1e-5 if dtype == np.float32 else 1e-11, atol=1e-5)
+
+
+# ------------------------------------------------------------------ testing mode
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_testing_mode_conversions(dtype, monkeypatch):
+    """With the testing-mode variable set the engine hands scikit-learn's own types around, as
+    the reference does for scikit-learn's test-suite (engine.py:108-115, 156-170, 219-225,
+    253-255, 287-290 there): numpy int32 labels, centres in the estimator's output dtype,
+    numpy distances, and label utilities that accept numpy labels."""
+    from sklearn_numba_dpex_b200.kmeans import KMeans, KMeansEngine
+    from sklearn_numba_dpex_b200.kmeans.engine import TESTING_MODE_ENV, NotSupportedByEngineError
+
+    monkeypatch.setenv(TESTING_MODE_ENV, "1")
+    X, _ = make_blobs(n_samples=300, centers=4, n_features=5, random_state=3)
+    X = X.astype(dtype)
+    init = X[:4].copy()
+    est = KMeans(n_clusters=4, init=init, n_init=1, max_iter=5, tol=0.0, copy_x=False)
+    engine = KMeansEngine(est)
+    assert engine._is_in_testing_mode
+    X_before = X.copy()
+    Xp, _, sw = engine.prepare_fit(X)
+    assert est._output_dtype == dtype
+    centers_init_t = engine.init_centroids(Xp, sw)
+    labels, inertia, centers, n_iter = engine.kmeans_single(Xp, sw, centers_init_t)
+    assert isinstance(labels, np.ndarray) and labels.dtype == np.int32 and labels.shape == (300,)
+    assert isinstance(centers, np.ndarray) and centers.dtype == dtype and centers.shape == (4, 5)
+    assert centers.flags["C_CONTIGUOUS"]           # the transpose of the F-ordered (d, k) array
+    engine.unshift_centers(Xp, centers)            # numpy centres, in place; X restored (copy_x=False)
+    o = ref.lloyd(*_oracle_prepared(X_before, init, tol=0.0)[:4], 5, False, 0.0)
+    mean = X_before.mean(axis=0, dtype=dtype)
+    assert_array_equal(labels, o[0].astype(np.int32))
+    assert_allclose(centers, o[2] + mean, rtol=_rtol(dtype) * 10, atol=1e-5)
+    assert_allclose(_np(Xp), X_before, rtol=1e-6, atol=1e-6)
+
+    # label utilities on numpy labels
+    perm = np.array([2, 0, 3, 1], dtype=np.int32)
+    assert engine.is_same_clustering(labels, perm[labels], 4) is True
+    other = labels.copy()
+    other[0] = (other[0] + 1) % 4
+    assert engine.is_same_clustering(labels, other, 4) is False
+    assert int(engine.count_distinct_clusters(labels)) == 4
+
+    # prediction side
+    est.cluster_centers_ = centers
+    Xq, swq = engine.prepare_prediction(X_before, None)
+    pred = engine.get_labels(Xq, swq)
+    assert isinstance(pred, np.ndarray) and pred.dtype == np.int32
+    assert_array_equal(pred, labels)
+    dist = engine.get_euclidean_distances(X_before)
+    assert isinstance(dist, np.ndarray) and dist.dtype == dtype and dist.shape == (300, 4)
+    assert_allclose(dist, ref.euclidean_distances(X_before, centers), rtol=1e-4, atol=1e-5)
+    assert np.isscalar(engine.get_score(Xq, swq)) or np.ndim(engine.get_score(Xq, swq)) == 0
+
+    # unsupported requests raise instead of declining
+    est2 = KMeans(n_clusters=2, algorithm="elkan")
+    with pytest.raises(NotSupportedByEngineError):
+        KMeansEngine(est2).accepts(X, None, None)
+    monkeypatch.setenv(TESTING_MODE_ENV, "0")
+    assert KMeansEngine(est2).accepts(X, None, None) is False
+    monkeypatch.setenv(TESTING_MODE_ENV, "yes")
+    with pytest.raises(ValueError, match="expected to take"):
+        KMeansEngine(est2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_non_finite_inputs_are_rejected_for_every_array_type(dtype):
+    # engine.py:319-331 of the reference validates every array type with force_all_finite=True
+    from sklearn_numba_dpex_b200.kmeans import KMeans
+
+    X = np.random.default_rng(0).standard_normal((50, 3)).astype(dtype)
+    for bad in (np.nan, np.inf, -np.inf):
+        Xb = X.copy()
+        Xb[17, 1] = bad
+        for arr in (Xb, torch.as_tensor(Xb), torch.as_tensor(Xb).cuda()):
+            with pytest.raises(ValueError, match="NaN|infinity|inf"):
+                KMeans(n_clusters=2, n_init=1).fit(arr)
+    w = np.ones(50, dtype=dtype)
+    w[3] = np.nan
+    with pytest.raises(ValueError, match="NaN|infinity|inf"):
+        KMeans(n_clusters=2, n_init=1).fit(torch.as_tensor(X).cuda(), sample_weight=torch.as_tensor(w).cuda())
+    init = X[:2].copy()
+    init[0, 0] = np.inf
+    with pytest.raises(ValueError, match="NaN|infinity|inf"):
+        KMeans(n_clusters=2, n_init=1, init=torch.as_tensor(init).cuda()).fit(torch.as_tensor(X).cuda())
+    # finite data still pass
+    KMeans(n_clusters=2, n_init=1, max_iter=2).fit(torch.as_tensor(X).cuda())
+
+
+@pytest.mark.parametrize("weights", ["none", "uniform", "random"])
+def test_random_init_keeps_numpys_index_stream(weights):
+    """init="random" draws with numpy's RandomState.choice(n, k, replace=False, p=w/sum(w)) as the
+    reference does (engine.py:188-196); with uniform weights the probabilities are rebuilt on the
+    host instead of copying the weights back, and must give the very same rows."""
+    from sklearn.utils import check_random_state
+
+    from sklearn_numba_dpex_b200.kmeans import KMeans, KMeansEngine
+
+    rng = np.random.default_rng(9)
+    n, d, k = 5000, 6, 17
+    X = rng.standard_normal((n, d)).astype(np.float32) + 3.0
+    sw = {"none": None, "uniform": np.full(n, 2.5, dtype=np.float32),
+          "random": rng.uniform(0.1, 3.0, n).astype(np.float32)}[weights]
+    est = KMeans(n_clusters=k, init="random", n_init=1, random_state=11)
+    engine = KMeansEngine(est)
+    Xp, _, swp = engine.prepare_fit(X, sample_weight=sw)
+    assert engine.sample_weight_is_uniform == (weights != "random")
+    centers = _np(engine.init_centroids(Xp, swp).T)
+    w_np = np.ones(n, dtype=np.float32) if sw is None else sw
+    idx = check_random_state(11).choice(n, size=k, replace=False, p=w_np / w_np.sum())
+    assert_allclose(centers, _np(Xp)[idx])

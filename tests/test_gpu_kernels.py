@@ -345,7 +345,7 @@ def test_label_utilities():
 def test_matmul_hook(dtype, algo):
     # sklearn_numba_dpex/common/tests/test_matmul.py:71-164 (prime-sized case included)
     from sklearn_numba_dpex_b200 import _cabi
-    from sklearn_numba_dpex_b200._cabi import check, lib, ptr, stream_ptr, workspace_for
+    from sklearn_numba_dpex_b200._cabi import check, check_wait_error, lib, lloyd_workspace, ptr, stream_ptr
 
     code = _cabi.KMB_F32 if dtype == np.float32 else _cabi.KMB_F64
     rng = np.random.default_rng(3)
@@ -359,10 +359,43 @@ def test_matmul_hook(dtype, algo):
         B = rng.standard_normal((n, kd)).astype(dtype)
         Ad, Bd = _dev(A), _dev(B)
         out = torch.empty((m, n), dtype=Ad.dtype, device="cuda")
-        ws, wsb = workspace_for(out.device, m, kd, n)
+        ws, wsb = lloyd_workspace(out.device, m, kd, n)
         check(lib.kmb_matmul_nt(code, _cabi.ALGO_NAMES[algo], ptr(Ad), ptr(Bd), ptr(out),
                                 m, n, kd, ptr(ws), wsb, stream_ptr()))
         torch.cuda.synchronize()
+        check_wait_error(ws, out.device)
         expect = A.astype(np.float64) @ B.astype(np.float64).T
         tol = 2e-6 if dtype == np.float32 else 1e-13
         assert_allclose(out.cpu().numpy(), expect, rtol=0, atol=tol * np.sqrt(kd) * 4)
+
+
+def test_wait_error_flag_is_sticky_and_reaches_the_status_record():
+    """The time-out flag of the tensor-core kernel, exercised from the host only (no kernel is
+    made to wait): a flag raised in the workspace's control block is reported by
+    kmb_lloyd_wait_error, survives further steps (no launch clears it), travels in the status
+    record of the next finalize, and is cleared by kmb_lloyd_workspace_init."""
+    from sklearn_numba_dpex_b200._cabi import (KmbError, check, check_wait_error, lib, ptr, stream_ptr)
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    rng = np.random.default_rng(0)
+    n, d, k = 40_000, 16, 128
+    X, _ = _blobs(rng, n, d, k, np.float32)
+    C = X[rng.choice(n, size=k, replace=False)].copy()
+    st = LloydState(_dev(X), None, _dev(C), "auto")
+    assert st.is_tc
+    st.step()
+    st.check_device_waits()                       # clean so far
+    flag = torch.tensor([1], dtype=torch.int32, device="cuda").view(torch.uint8)
+    base = (st.ws.data_ptr() + 255) // 256 * 256 - st.ws.data_ptr()
+    st.ws[base: base + 4] = flag                  # what a timed-out wait would have stored
+    with pytest.raises(KmbError, match="bounded wait"):
+        st.check_device_waits()
+    with pytest.raises(KmbError, match="bounded wait"):
+        st.step()                                 # the flag rides on the status record
+    with pytest.raises(KmbError, match="bounded wait"):
+        st.check_device_waits()                   # and nothing has cleared it
+    check(lib.kmb_lloyd_workspace_init(ptr(st.ws), st.ws_bytes, stream_ptr(st.X.device)))
+    st.operands_ready = False
+    st.check_device_waits()
+    st.step()                                     # usable again
+    check_wait_error(st.ws, st.X.device)
