@@ -469,11 +469,12 @@ def run_gpu_arm(args, cfg):
                 dt_fit = time.perf_counter() - t0
             finally:
                 KMeansEngine._CONFIG.clear()
-            assert n_iter == e2e_iters, (n_iter, e2e_iters)
+            # tol = 0 leaves strict convergence (labels unchanged) as the only early stop; well
+            # separated data (the small configuration) reach it before max_iter
             t = torch.tensor([dt_fit], dtype=torch.float64, device=device)
             if world > 1:
                 tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-            return float(t[0]), labels_h.numel(), centres_h.numel()
+            return float(t[0]), labels_h.numel(), centres_h.numel(), int(n_iter)
 
         def drivers_fit():
             wh = torch.ones(n_local, dtype=dtype).pin_memory()
@@ -491,22 +492,23 @@ def run_gpu_arm(args, cfg):
             t = torch.tensor([dt_fit], dtype=torch.float64, device=device)
             if world > 1:
                 tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-            return float(t[0])
+            return float(t[0]), int(n_iter)
 
         engine_fit(True)                          # untimed dry run (allocator, lazy initialisation)
-        dt_copy, n_lab, n_cen = engine_fit(True)
-        dt_inplace, _, _ = engine_fit(False)
-        dt_drivers = drivers_fit()
+        dt_copy, n_lab, n_cen, it_copy = engine_fit(True)
+        dt_inplace, _, _, it_inplace = engine_fit(False)
+        dt_drivers, it_drivers = drivers_fit()
         h2d = (Xh.numel() + Ch.numel()) * esize * world
         d2h = n_lab * 4 * world + n_cen * esize + esize
-        e2e = {"value": e2e_iters / dt_copy, "unit": "iterations/s",
-               "h2d_bytes_per_step": int(h2d // e2e_iters), "d2h_bytes_per_step": int(d2h // e2e_iters),
+        e2e = {"value": it_copy / dt_copy, "unit": "iterations/s",
+               "h2d_bytes_per_step": int(h2d // it_copy), "d2h_bytes_per_step": int(d2h // it_copy),
+               "iterations_run": it_copy,
                "what": f"KMeansEngine.prepare_fit -> init_centroids (array) -> kmeans_single "
-                       f"({e2e_iters} iterations, tol=0) -> unshift_centers on a page-locked numpy X "
+                       f"(max_iter={e2e_iters}, tol=0) -> unshift_centers on a page-locked numpy X "
                        "(validation, upload, centring, tolerance scaling, Lloyd loop, final assignment "
                        "and inertia), labels and centres copied back; copy_x=True",
-               "copy_x_false": {"value": e2e_iters / dt_inplace, "unit": "iterations/s"},
-               "drivers_lloyd": {"value": e2e_iters / dt_drivers, "unit": "iterations/s",
+               "copy_x_false": {"value": it_inplace / dt_inplace, "unit": "iterations/s"},
+               "drivers_lloyd": {"value": it_drivers / dt_drivers, "unit": "iterations/s",
                                  "what": "one drivers.lloyd() call on tensors uploaded from pinned "
                                          "memory, no validation or centring"}}
 

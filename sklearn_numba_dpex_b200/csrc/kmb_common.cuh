@@ -82,6 +82,33 @@ struct LloydWorkspace {
   size_t bytes;          // from the caller's pointer to the end of the last array
 };
 
+// The tensor-core step can fold the half norms into the contraction when the padded feature
+// count leaves two spare features: the sample operand carries 1.0 in features d and d + 1, the
+// centroid operands carry -h split over the same two features, and the accumulator comes out
+// as x.c - h directly (one argmax, no half-norm loads, no subtraction per element).
+__host__ __device__ inline bool lloyd_tc_folds(int d) {
+  return d % 4 == 0 && (d % 32) != 0 && (d % 32) <= 28;
+}
+
+// Round-to-nearest (ties away) to the 10-bit mantissa of tf32.
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Values of the two fold features of a centroid with half norm h: (hi, lo) pairs, each a tf32
+// number, whose sum is -h to beyond fp32 precision.
+__device__ __forceinline__ void lloyd_tc_fold_values(float h, float (&hi)[2], float (&lo)[2]) {
+  const float nh = -h;
+  hi[0] = tf32_rna(nh);
+  const float r0 = nh - hi[0];
+  lo[0] = tf32_rna(r0);
+  const float r1 = r0 - lo[0];
+  hi[1] = tf32_rna(r1);
+  lo[1] = tf32_rna(r1 - hi[1]);
+}
+
 inline LloydWorkspace lloyd_carve(void* workspace, int d, int k) {
   LloydWorkspace w;
   w.d_pad = (d + 31) / 32 * 32;

@@ -51,12 +51,6 @@ struct FinArgs {
   int k, d, k_pad, d_pad;
 };
 
-__device__ __forceinline__ float fin_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-
 // One warp per cluster: (merge of the accumulator copies), C_new = sums / count, squared shift,
 // half norm of C_new, and the hi / lo split of C_new for the next tensor-core step.  The CTA
 // that finishes last then writes the status record: fixed-order total of the shifts and the
@@ -97,9 +91,9 @@ __global__ void __launch_bounds__(256) finalize_fused_kernel(FinArgs<T> a) {
       shift += (double)diff * (double)diff;
       norm += (double)cn * (double)cn;
       if (a.chi != nullptr) {
-        const float hi = fin_tf32((float)cn);
+        const float hi = tf32_rna((float)cn);
         a.chi[(int64_t)j * a.d_pad + f] = hi;
-        a.clo[(int64_t)j * a.d_pad + f] = fin_tf32((float)cn - hi);
+        a.clo[(int64_t)j * a.d_pad + f] = tf32_rna((float)cn - hi);
       }
     }
     shift = warp_sum(shift);
@@ -123,14 +117,28 @@ __global__ void __launch_bounds__(256) finalize_fused_kernel(FinArgs<T> a) {
         a.chi[(int64_t)j * a.d_pad + f] = 0.f;
         a.clo[(int64_t)j * a.d_pad + f] = 0.f;
       }
+      __syncwarp();
+      if (lane == 0 && lloyd_tc_folds(d)) {
+        float fhi[2], flo[2];
+        lloyd_tc_fold_values((float)(norm * 0.5), fhi, flo);
+        a.chi[(int64_t)j * a.d_pad + d] = fhi[0];
+        a.clo[(int64_t)j * a.d_pad + d] = flo[0];
+        a.chi[(int64_t)j * a.d_pad + d + 1] = fhi[1];
+        a.clo[(int64_t)j * a.d_pad + d + 1] = flo[1];
+      }
     }
   } else if (a.chi != nullptr && j < a.k_pad) {
-    // padding centroids of the tensor-core operands: zero rows that can never win
+    // padding centroids of the tensor-core operands: zero rows that can never win (half norm
+    // +inf; with folded half norms a NaN in the fold feature, which makes their scores NaN)
     for (int f = lane; f < a.d_pad; f += 32) {
       a.chi[(int64_t)j * a.d_pad + f] = 0.f;
       a.clo[(int64_t)j * a.d_pad + f] = 0.f;
     }
-    if (lane == 0) a.h_pad[j] = __int_as_float(0x7f800000);
+    __syncwarp();
+    if (lane == 0) {
+      a.h_pad[j] = __int_as_float(0x7f800000);
+      if (lloyd_tc_folds(d)) a.chi[(int64_t)j * a.d_pad + d] = __int_as_float(0x7fc00000);
+    }
   }
   if (blockIdx.x == 0 && tid == 0) {
     // the "labels changed" counter follows the counts

@@ -245,11 +245,6 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
                               ((uint32_t)(TC_BM >> 4) << 24);
 
-__device__ __forceinline__ float tf32_round(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
 
 // Build with -DKMB_TC_PROFILE to make CTA 0 print how long its MMA warp waited on each barrier.
 #ifdef KMB_TC_PROFILE
@@ -259,49 +254,56 @@ __device__ __forceinline__ float tf32_round(float x) {
 #endif
 
 // ------------------------------------------------------------------------- the kernel
-// (value, index) minimum of two candidates where `a` has the lower index: b wins only when it
-// is strictly smaller; a NaN never wins against a number (fminf drops it).
-#define KMB_MIN2(va, ia, vb, ib, vo, io)          \
-  {                                               \
-    const float _m = fminf(va, vb);               \
-    io = (_m == (va)) ? (ia) : (ib);              \
-    vo = _m;                                      \
-  }
-
-// Minimum of q[j] = h[j] - acc[j] over 32 consecutive centroids, lowest index on ties.
-__device__ __forceinline__ void min_tree32(const uint32_t (&v)[32], const float4 (&h4)[8],
-                                           uint32_t base, float& out_v, uint32_t& out_i) {
-  float q[32];
-#pragma unroll
-  for (int j4 = 0; j4 < 8; ++j4) {
-    const float4 hv = h4[j4];
-    q[4 * j4 + 0] = hv.x - __uint_as_float(v[4 * j4 + 0]);
-    q[4 * j4 + 1] = hv.y - __uint_as_float(v[4 * j4 + 1]);
-    q[4 * j4 + 2] = hv.z - __uint_as_float(v[4 * j4 + 2]);
-    q[4 * j4 + 3] = hv.w - __uint_as_float(v[4 * j4 + 3]);
-  }
-  float v16[16];
-  uint32_t i16[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) KMB_MIN2(q[2 * j], base + 2 * j, q[2 * j + 1], base + 2 * j + 1, v16[j], i16[j]);
-  float v8[8];
-  uint32_t i8[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) KMB_MIN2(v16[2 * j], i16[2 * j], v16[2 * j + 1], i16[2 * j + 1], v8[j], i8[j]);
-  float v4[4];
-  uint32_t i4[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) KMB_MIN2(v8[2 * j], i8[2 * j], v8[2 * j + 1], i8[2 * j + 1], v4[j], i4[j]);
-  float va, vb;
-  uint32_t ia, ib;
-  KMB_MIN2(v4[0], i4[0], v4[1], i4[1], va, ia);
-  KMB_MIN2(v4[2], i4[2], v4[3], i4[3], vb, ib);
-  KMB_MIN2(va, ia, vb, ib, out_v, out_i);
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 
+// Maximum of the scores s[j] of 32 consecutive centroids and the LOWEST index that attains it.
+// The score is acc[j] - h[j] (the negated pseudo-inertia), or acc[j] itself when the half norms
+// were folded into the contraction.  A NaN score never wins (max drops it); 32 NaNs give
+// (-inf, base).  Values first with three-input maxima, then one equality scan from the top
+// index down, so that the lowest equal index is the last one written.
+template <bool FOLD>
+__device__ __forceinline__ void argmax32(const uint32_t (&v)[32], const float4 (&h4)[8],
+                                         uint32_t base, float& out_v, uint32_t& out_i) {
+  float q[32];
+  if (FOLD) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) q[j] = __uint_as_float(v[j]);
+  } else {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 hv = h4[j4];
+      q[4 * j4 + 0] = __uint_as_float(v[4 * j4 + 0]) - hv.x;
+      q[4 * j4 + 1] = __uint_as_float(v[4 * j4 + 1]) - hv.y;
+      q[4 * j4 + 2] = __uint_as_float(v[4 * j4 + 2]) - hv.z;
+      q[4 * j4 + 3] = __uint_as_float(v[4 * j4 + 3]) - hv.w;
+    }
+  }
+  float a[11];
+#pragma unroll
+  for (int j = 0; j < 10; ++j) a[j] = fmax3(q[3 * j], q[3 * j + 1], q[3 * j + 2]);
+  a[10] = fmaxf(q[30], q[31]);
+  const float b0 = fmax3(a[0], a[1], a[2]), b1 = fmax3(a[3], a[4], a[5]);
+  const float b2 = fmax3(a[6], a[7], a[8]), b3 = fmaxf(a[9], a[10]);
+  float m = fmaxf(fmax3(b0, b1, b2), b3);
+  uint32_t idx = 0;
+#pragma unroll
+  for (int j = 31; j >= 1; --j) idx = (q[j] == m) ? (uint32_t)j : idx;
+  idx = (q[0] == m) ? 0u : idx;
+  out_v = (m == m) ? m : __int_as_float(0xff800000);
+  out_i = base + idx;
+}
+
+template <bool FOLD>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                 const __grid_constant__ CUtensorMap map_clo, TcParams p) {
+  // FOLD: features d and d + 1 of the padded operands carry the half norms (see lloyd_tc_folds)
+  const int d_eff = FOLD ? p.d + 2 : p.d;
+  const int fold_chunk = FOLD ? p.d / 4 : -1;      // 16-byte chunk of a row that holds them
   extern __shared__ unsigned char smem_raw[];
   TcSmem* sm = reinterpret_cast<TcSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -394,7 +396,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const uint32_t mw = (uint32_t)warp - 2u;
     const uint32_t ring = resident ? n_st : (uint32_t)TC_STAGES;
     const uint32_t lap_flip = resident ? 0u : 1u;   // resident stages complete one phase only
-    const int ks_last = ((p.d - 1) % TC_KC) / 8 + 1;   // k-steps of the last chunk that hold data
+    const int ks_last = ((d_eff - 1) % TC_KC) / 8 + 1;   // k-steps of the last chunk that hold data
     uint32_t t = 0, g = 0, s = 0, lap = 0;
     bool ok = true;
     KMB_PROF(long long w_conv = 0, w_acc = 0, w_b = 0, t_all = clock64(), tw;)
@@ -501,13 +503,19 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const unsigned char* rowp = sm->xstage[xs * 2 + kc] + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+          float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+          if (FOLD && kc * 8 + c == fold_chunk) {   // the sample side of the folded half norms
+            x.x = 1.f;
+            x.y = 1.f;
+          }
+          // the tensor core reads the top 19 bits of each word: round the low part as well
+          // instead of letting it be truncated
           const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
           const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
-          hi[4 * c + 0] = __float_as_uint(h0); lo[4 * c + 0] = __float_as_uint(x.x - h0);
-          hi[4 * c + 1] = __float_as_uint(h1); lo[4 * c + 1] = __float_as_uint(x.y - h1);
-          hi[4 * c + 2] = __float_as_uint(h2); lo[4 * c + 2] = __float_as_uint(x.z - h2);
-          hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(x.w - h3);
+          hi[4 * c + 0] = __float_as_uint(h0); lo[4 * c + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
+          hi[4 * c + 1] = __float_as_uint(h1); lo[4 * c + 1] = __float_as_uint(tf32_round_alu(x.y - h1));
+          hi[4 * c + 2] = __float_as_uint(h2); lo[4 * c + 2] = __float_as_uint(tf32_round_alu(x.z - h2));
+          hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(tf32_round_alu(x.w - h3));
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + kc * TC_KC;
         tmem_st32(lane_addr + hi_col, hi);
@@ -530,7 +538,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const int64_t m0 = tile * TC_BM;
       const bool has_next = tile + gridDim.x < n_tiles;
       const uint32_t buf = t & 1, ub = t >> 1;
-      float best = __int_as_float(0x7f800000);
+      float best = __int_as_float(0xff800000);      // scores: larger is nearer
       uint32_t bi = 0;
       // Two tiles in flight: the other tensor-memory half was last read by tile t - 1, whose
       // accumulators this warp has already consumed, so it is free now.
@@ -571,17 +579,20 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         const uint32_t taddr =
             tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN + grp * 64;
-        // half norms of this half: same address in every lane (broadcast loads), issued ahead
-        // of the tensor-memory loads so that both latencies overlap
+        // half norms of this half (unless folded into the contraction): same address in every
+        // lane (broadcast loads), issued ahead of the tensor-memory loads so that both
+        // latencies overlap
         const float4* hp = reinterpret_cast<const float4*>(p.h_pad + cn);
         float4 ha[8], hb[8];
+        if (!FOLD) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ha[j] = __ldg(hp + j);
+          for (int j = 0; j < 8; ++j) ha[j] = __ldg(hp + j);
+        }
         uint32_t va[32], vb[32];
         tmem_ld32(taddr, va);
         tmem_ld32(taddr + 32, vb);
         tmem_ld_wait();
-        // the accumulator is in registers now: hand the buffer back before the argmin
+        // the accumulator is in registers now: hand the buffer back before the argmax
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
@@ -595,13 +606,15 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         float qa, qb;
         uint32_t ia, ib;
-        min_tree32(va, ha, (uint32_t)cn, qa, ia);
+        argmax32<FOLD>(va, ha, (uint32_t)cn, qa, ia);
+        if (!FOLD) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) hb[j] = __ldg(hp + 8 + j);
-        min_tree32(vb, hb, (uint32_t)(cn + 32), qb, ib);
-        if (qb < qa) { qa = qb; ia = ib; }            // ascending inside the half: strict '<'
-        // halves arrive in rotated order: smaller value wins, equal values -> smaller index
-        if (qa < best || (qa == best && ia < bi)) {
+          for (int j = 0; j < 8; ++j) hb[j] = __ldg(hp + 8 + j);
+        }
+        argmax32<FOLD>(vb, hb, (uint32_t)(cn + 32), qb, ib);
+        if (qb > qa) { qa = qb; ia = ib; }            // ascending inside the half: strict '>'
+        // halves arrive in rotated order: larger score wins, equal scores -> smaller index
+        if (qa > best || (qa == best && ia < bi)) {
           best = qa;
           bi = ia;
         }
@@ -619,7 +632,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         KMB_PROF(w_part += clock64() - tw;)
         const float ov = sm->part_v[row];
         const uint32_t oi = sm->part_i[row];
-        if (ov < best || (ov == best && oi < bi)) {
+        if (ov > best || (ov == best && oi < bi)) {
           best = ov;
           bi = oi;
         }
@@ -710,11 +723,368 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   }
 }
 
+// ------------------------------------------------------- the kernel for short rows
+// Rows of at most 28 features (one 32-feature chunk including the two fold features).  With so
+// little contraction per accumulator element the step is bound by the epilogue, not by the
+// tensor pipe: per 128-row tile the MMAs need 64 cycles per k-step and centroid tile, the
+// argmax about 2.5 instructions per accumulator element.  So this kernel spends its warps
+// there: 20 warps, of which 16 are workers (four per scheduler).
+//   warp 0       TMA producer of the sample tiles (two in flight)
+//   warp 1       TMA producer of the centroid stages (resident when all of them fit)
+//   warps 2, 3   issue the MMAs, one accumulator buffer each (warp 2 owns tensor memory)
+//   warps 4..19  worker (lq, cq) = (warp % 4, (warp - 4) / 4): TMEM lanes 32 lq .. 32 lq + 31,
+//                i.e. one sample row per thread.  It splits features 8 cq .. 8 cq + 7 of its row
+//                into hi / lo parts in tensor memory (the slice that holds features d, d + 1
+//                writes the ones of the folded half norms), folds columns 32 cq .. 32 cq + 31 of
+//                every accumulator into a running (score, index), and adds 8 of the tile's rows
+//                into the centroid sums.  Quarter 0 merges the four partial results of a row.
+// Tensor memory: sample tile slot s (s = 0, 1): hi at columns 64 s, lo at 64 s + 32;
+// accumulators at 256 and 384.
+constexpr int TS_WARPS = 20;
+constexpr int TS_THREADS = TS_WARPS * 32;
+constexpr int TS_WORKER0 = 4;
+constexpr int TS_WORKERS = 16;
+
+struct TsSmem {
+  unsigned char xstage[2][TC_ATOM_BYTES];
+  unsigned char bhi[TC_STAGES][TC_ATOM_BYTES];
+  unsigned char blo[TC_STAGES][TC_ATOM_BYTES];
+  uint16_t lab_s[2][TC_BM];
+  float part_v[3][TC_BM];         // quarters 1..3: best score and index per row, merged by quarter 0
+  uint16_t part_i[3][TC_BM];
+  unsigned long long x_full[2], x_conv[2], x_stage_free[2];
+  unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
+  unsigned long long acc_full[2], acc_empty[2];
+  unsigned long long part_full[2], lab_ready[2];
+  unsigned int tmem_base;
+  volatile int abort_flag;
+};
+static_assert(sizeof(TsSmem) + 1024 <= 232448, "TsSmem exceeds the 227 KB a CTA may use");
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+      : "memory");
+}
+
+// Bounded wait on a barrier of the short-row kernel (same rule as mbar_wait).
+__device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, int* error_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm->abort_flag) return false;
+    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+      sm->abort_flag = 1;
+      atomicExch(error_flag, 1);
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TS_THREADS, 1)
+lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
+                      const __grid_constant__ CUtensorMap map_clo, TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  TsSmem* sm = reinterpret_cast<TsSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_nt = p.k_pad / TC_BN;
+  const int64_t n_tiles = (p.n + TC_BM - 1) / TC_BM;
+  const bool update = p.acc != nullptr;
+  const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
+  const bool resident = n_nt <= TC_STAGES;
+  const int d_eff = p.d + 2;                       // data features + the two fold features
+  const int n_ks = (d_eff + 7) / 8;                // k-steps (of 8 features) that hold data: 1..4
+  const int fold_chunk = p.d / 4;                  // 16-byte chunk of a row holding features d, d + 1
+
+  if (threadIdx.x == 0) {
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm->x_full[a], 1);
+      mbar_init(&sm->x_conv[a], 4 * n_ks);         // one arrival per converting warp
+      mbar_init(&sm->x_stage_free[a], 4 * n_ks);
+      mbar_init(&sm->acc_full[a], 1);
+      mbar_init(&sm->acc_empty[a], TS_WORKERS);
+      mbar_init(&sm->part_full[a], 12);
+      mbar_init(&sm->lab_ready[a], 4);
+    }
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&sm->b_full[s], 1);
+      mbar_init(&sm->b_empty[s], 1);
+    }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(&sm->tmem_base, TC_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- sample tiles
+    if (lane == 0) {
+      uint32_t t = 0;
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+        const uint32_t xs = t & 1, xu = t >> 1;
+        if (!ts_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag)) break;
+        mbar_expect_tx(&sm->x_full[xs], TC_ATOM_BYTES);
+        tma_load_2d(sm->xstage[xs], &map_x, 0, (int)(tile * TC_BM), &sm->x_full[xs]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- centroid stages
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        if (resident && it != 0) break;            // everything is in shared memory already
+        for (int i = 0; i < n_nt; ++i, ++it) {
+          const int nt = (nt0 + i) % n_nt;
+          const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
+          if (!ts_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&sm->b_full[s], 2 * TC_ATOM_BYTES);
+          tma_load_2d(sm->bhi[s], &map_chi, 0, nt * TC_BN, &sm->b_full[s]);
+          tma_load_2d(sm->blo[s], &map_clo, 0, nt * TC_BN, &sm->b_full[s]);
+        }
+      }
+    }
+  } else if (warp < TS_WORKER0) {
+    // ------------------------------------------------------------------------ MMA
+    const uint32_t mw = (uint32_t)warp - 2u;
+    const uint32_t ring = resident ? (uint32_t)n_nt : (uint32_t)TC_STAGES;
+    const uint32_t lap_flip = resident ? 0u : 1u;
+    uint32_t t = 0, g = 0, s = 0, lap = 0;
+    bool ok = true;
+    const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
+    const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
+    const uint32_t d_tmem = tmem_base + TC_ACC_COL + mw * TC_BN;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+      const uint32_t xs = t & 1, xu = t >> 1;
+      const uint32_t a_hi = tmem_base + xs * 64, a_lo = a_hi + 32;
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag))) break;
+      tc_fence_after();
+      for (int i = 0; i < n_nt && ok; ++i, ++g) {
+        if ((g & 1u) == mw) {
+          if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag)) ||
+              !__all_sync(0xffffffffu, ts_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          if (elect_one()) {
+#pragma unroll
+            for (int ks = 0; ks < TC_KC / 8; ++ks) {
+              if (ks < n_ks) {
+                const uint64_t adv = (uint64_t)(ks * 2);
+                umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, ks != 0);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
+              }
+            }
+            if (!resident) umma_commit(&sm->b_empty[s]);
+            umma_commit(&sm->acc_full[mw]);
+          }
+          __syncwarp();
+        }
+        if (++s == ring) {
+          s = 0;
+          lap ^= lap_flip;
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- workers
+    const int wk = warp - TS_WORKER0;
+    const int lq = warp & 3, cq = wk >> 2;
+    const int lane_base = lq * 32;
+    const int row = lane_base + lane;
+    const bool converts = cq < n_ks;
+    float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
+    uint32_t t = 0, g = 0, changed = 0;
+    bool ok = true;
+    // update geometry: G lanes (a power of two) of 16 bytes serve one row; a warp adds 8 rows
+    const int urow0 = wk * 8;
+    int G = 1;
+    while (G * 4 < p.d) G <<= 1;
+    const int rpi = 32 / G;                        // rows per warp instruction: 4 .. 32
+    const int sub = lane / G;
+    const int col = (lane % G) * 4;
+    const bool col_ok = col < p.d;
+    const int n_instr = (8 + rpi - 1) / rpi;       // 1 or 2
+
+    auto convert_tile = [&](uint32_t tt) -> bool {
+      const uint32_t xs = tt & 1, xu = tt >> 1;
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag))) return false;
+      uint32_t hi[8], lo[8];
+      const unsigned char* rowp = sm->xstage[xs] + row * 128;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        const int c = cq * 2 + c2;
+        float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+        if (c == fold_chunk) {
+          x.x = 1.f;
+          x.y = 1.f;
+        }
+        const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
+        const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
+        hi[4 * c2 + 0] = __float_as_uint(h0); lo[4 * c2 + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
+        hi[4 * c2 + 1] = __float_as_uint(h1); lo[4 * c2 + 1] = __float_as_uint(tf32_round_alu(x.y - h1));
+        hi[4 * c2 + 2] = __float_as_uint(h2); lo[4 * c2 + 2] = __float_as_uint(tf32_round_alu(x.z - h2));
+        hi[4 * c2 + 3] = __float_as_uint(h3); lo[4 * c2 + 3] = __float_as_uint(tf32_round_alu(x.w - h3));
+      }
+      const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + xs * 64 + cq * 8;
+      tmem_st8(lane_addr, hi);
+      tmem_st8(lane_addr + 32, lo);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sm->x_conv[xs]);
+        mbar_arrive(&sm->x_stage_free[xs]);
+      }
+      return true;
+    };
+
+    if (converts) ok = convert_tile(0);
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+      const int64_t m0 = tile * TC_BM;
+      const bool has_next = tile + gridDim.x < n_tiles;
+      const uint32_t buf = t & 1, ub = t >> 1;
+      float best = __int_as_float(0xff800000);
+      uint32_t bi = 0;
+      // the rows this warp will add into the centroid sums are fetched now, so that their
+      // latency hides behind the epilogues
+      const float* xbase = p.X + (m0 + urow0) * (int64_t)p.d + col;
+      float4 xpre[2];
+      auto pre_ok = [&](int j) -> bool {
+        const int r = j * rpi + sub;
+        return update && j < n_instr && r < 8 && col_ok && (m0 + urow0 + r < p.n);
+      };
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        xpre[j] = pre_ok(j) ? __ldg(reinterpret_cast<const float4*>(xbase + (int64_t)(j * rpi + sub) * p.d))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+      // the other tensor-memory slot was last read by the MMAs of tile t - 1, all of whose
+      // accumulators this warp has consumed: it is free for tile t + 1
+      if (converts && has_next && !convert_tile(t + 1)) break;
+      for (int i = 0; i < n_nt; ++i, ++g) {
+        const uint32_t ab = g & 1, ug = g >> 1;
+        const int cn = ((nt0 + i) % n_nt) * TC_BN + cq * 32;
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN + cq * 32, v);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+        float qa;
+        uint32_t ia;
+        const float4 unused[8] = {};
+        argmax32<true>(v, unused, (uint32_t)cn, qa, ia);
+        // centroid tiles arrive in rotated order: larger score wins, equal scores -> smaller index
+        if (qa > best || (qa == best && ia < bi)) {
+          best = qa;
+          bi = ia;
+        }
+      }
+      if (!ok) break;
+
+      if (cq != 0) {
+        sm->part_v[cq - 1][row] = best;
+        sm->part_i[cq - 1][row] = (uint16_t)bi;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->part_full[buf]);
+      } else {
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag))) break;
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          const float ov = sm->part_v[q][row];
+          const uint32_t oi = sm->part_i[q][row];
+          if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+          }
+        }
+        if (m0 + row < p.n) {
+          p.labels[m0 + row] = bi;
+          if (update) changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
+        }
+        sm->lab_s[buf][row] = (uint16_t)bi;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->lab_ready[buf]);
+      }
+      // Every warp waits for the merged labels (also when nothing is updated): part_* have one
+      // buffer, which quarter 0 has read before it arrives here, so no quarter can overwrite
+      // it a tile early.  lab_s[buf] is reused two tiles later; by then every warp has passed
+      // this point of tile t + 1, which it reaches only after finishing the update of tile t.
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag))) break;
+      if (!update) continue;
+
+      // ---- centroid update of rows urow0 .. urow0 + 7 of this tile
+      const int my = urow0 + (lane & 7);
+      const uint32_t ubi = sm->lab_s[buf][my];
+      const bool uvalid = m0 + my < p.n;
+      float uwi = 0.f;
+      if (uvalid) uwi = p.w ? p.w[m0 + my] : 1.f;
+      if (uvalid && lane < 8) atomicAdd(&acc_copy[(int64_t)p.k * p.d + ubi], uwi);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const bool okj = pre_ok(j);
+        const int src = okj ? j * rpi + sub : 0;
+        const uint32_t lab = __shfl_sync(0xffffffffu, ubi, src);
+        const float wr = __shfl_sync(0xffffffffu, uwi, src);
+        if (okj) {
+          float4 u;
+          u.x = xpre[j].x * wr; u.y = xpre[j].y * wr; u.z = xpre[j].z * wr; u.w = xpre[j].w * wr;
+          atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + col), u);
+        }
+      }
+    }
+    if (update && cq == 0) {
+      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
+      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TC_TMEM_COLS);
+  }
+}
+
+// Set KMB_TC_SMALL=0 in the environment to run short rows on the general kernel (A/B runs).
+static bool tc_small_disabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("KMB_TC_SMALL");
+    cached = (e != nullptr && e[0] == '0') ? 1 : 0;
+  }
+  return cached == 1;
+}
+
 // Centroids -> zero-padded hi / lo parts (both rounded to tf32) and +inf-padded half norms.
+// With `fold` the features d and d + 1 carry -h (see lloyd_tc_folds); padding centroids get a
+// NaN there, so that their scores are NaN and never win.
 __global__ void tc_split_centroids_kernel(const float* __restrict__ C, const float* __restrict__ h,
                                           float* __restrict__ chi, float* __restrict__ clo,
                                           float* __restrict__ h_pad, int k, int d, int k_pad,
-                                          int d_pad) {
+                                          int d_pad, int fold) {
   const int64_t total = (int64_t)k_pad * d_pad;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * blockDim.x) {
@@ -722,8 +1092,17 @@ __global__ void tc_split_centroids_kernel(const float* __restrict__ C, const flo
     float hi = 0.f, lo = 0.f;
     if (j < k && f < d) {
       const float c = C[(int64_t)j * d + f];
-      hi = tf32_round(c);
-      lo = tf32_round(c - hi);
+      hi = tf32_rna(c);
+      lo = tf32_rna(c - hi);
+    } else if (fold && (f == d || f == d + 1)) {
+      if (j < k) {
+        float fhi[2], flo[2];
+        lloyd_tc_fold_values(h[j], fhi, flo);
+        hi = fhi[f - d];
+        lo = flo[f - d];
+      } else if (f == d) {
+        hi = __int_as_float(0x7fc00000);
+      }
     }
     chi[e] = hi;
     clo[e] = lo;
@@ -807,12 +1186,14 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
     return KMB_ERR_WORKSPACE;
   }
   // The time-out flag in the control block is sticky: only kmb_lloyd_workspace_init clears it.
+  // The raw-product hook (dots) must see plain dot products, so it never folds.
+  const bool fold = lloyd_tc_folds(d) && dots == nullptr && h != nullptr;
   if (!operands_ready) {
     const int64_t total = (int64_t)k_pad * d_pad;
     int grid = (int)ceil_div(total, 256);
     if (grid > 1184) grid = 1184;
     tc_split_centroids_kernel<<<grid, 256, 0, stream>>>(C, h, ws.chi, ws.clo, ws.h_pad, k, d, k_pad,
-                                                        d_pad);
+                                                        d_pad, fold ? 1 : 0);
     KMB_CHECK_LAUNCH();
   }
   CUtensorMap map_x, map_chi, map_clo;
@@ -829,10 +1210,25 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
+  if (fold && d_pad == TC_KC && !tc_small_disabled()) {
+    // short rows: the kernel with sixteen epilogue warps
+    const size_t smem = sizeof(TsSmem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_small_kernel<<<(unsigned)grid, TS_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+    KMB_CHECK_LAUNCH();
+    return KMB_OK;
+  }
   const size_t smem = sizeof(TcSmem) + 1024;
-  KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem));
-  lloyd_tc_kernel<<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  if (fold) {
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_kernel<true><<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  } else {
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_kernel<false><<<(unsigned)grid, TC_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+  }
   KMB_CHECK_LAUNCH();
   return KMB_OK;
 }
