@@ -955,6 +955,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       return true;
     };
 
+    KMB_PROF(long long c_conv = 0, w_acc = 0, c_arg = 0, w_part = 0, w_lab = 0, c_upd = 0, t_all = clock64(), tw;)
     if (converts) ok = convert_tile(0);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
       const int64_t m0 = tile * TC_BM;
@@ -962,6 +963,9 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       const uint32_t buf = t & 1, ub = t >> 1;
       float best = __int_as_float(0xff800000);
       uint32_t bi = 0;
+      // previous label of this thread's row: fetched now, compared once the new one is known
+      uint32_t prev_lab = 0xffffffffu;
+      if (update && cq == 0 && p.prev != nullptr && m0 + row < p.n) prev_lab = __ldg(p.prev + m0 + row);
       // the rows this warp will add into the centroid sums are fetched now, so that their
       // latency hides behind the epilogues
       const float* xbase = p.X + (m0 + urow0) * (int64_t)p.d + col;
@@ -976,14 +980,18 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             : make_float4(0.f, 0.f, 0.f, 0.f);
       // the other tensor-memory slot was last read by the MMAs of tile t - 1, all of whose
       // accumulators this warp has consumed: it is free for tile t + 1
+      KMB_PROF(tw = clock64();)
       if (converts && has_next && !convert_tile(t + 1)) break;
+      KMB_PROF(c_conv += clock64() - tw;)
       for (int i = 0; i < n_nt; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
         const int cn = ((nt0 + i) % n_nt) * TC_BN + cq * 32;
+        KMB_PROF(tw = clock64();)
         if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
           ok = false;
           break;
         }
+        KMB_PROF(w_acc += clock64() - tw; tw = clock64();)
         tc_fence_after();
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN + cq * 32, v);
@@ -1000,6 +1008,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           best = qa;
           bi = ia;
         }
+        KMB_PROF(c_arg += clock64() - tw;)
       }
       if (!ok) break;
 
@@ -1009,7 +1018,9 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->part_full[buf]);
       } else {
+        KMB_PROF(tw = clock64();)
         if (!__all_sync(0xffffffffu, ts_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag))) break;
+        KMB_PROF(w_part += clock64() - tw;)
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
           const float ov = sm->part_v[q][row];
@@ -1019,20 +1030,23 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             bi = oi;
           }
         }
-        if (m0 + row < p.n) {
-          p.labels[m0 + row] = bi;
-          if (update) changed += (p.prev == nullptr) ? 1u : (p.prev[m0 + row] != bi ? 1u : 0u);
-        }
         sm->lab_s[buf][row] = (uint16_t)bi;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->lab_ready[buf]);
+        if (m0 + row < p.n) {
+          p.labels[m0 + row] = bi;
+          if (update) changed += (prev_lab != bi) ? 1u : 0u;
+        }
       }
       // Every warp waits for the merged labels (also when nothing is updated): part_* have one
       // buffer, which quarter 0 has read before it arrives here, so no quarter can overwrite
       // it a tile early.  lab_s[buf] is reused two tiles later; by then every warp has passed
       // this point of tile t + 1, which it reaches only after finishing the update of tile t.
+      KMB_PROF(tw = clock64();)
       if (!__all_sync(0xffffffffu, ts_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag))) break;
+      KMB_PROF(w_lab += clock64() - tw;)
       if (!update) continue;
+      KMB_PROF(tw = clock64();)
 
       // ---- centroid update of rows urow0 .. urow0 + 7 of this tile
       const int my = urow0 + (lane & 7);
@@ -1053,7 +1067,9 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           atomicAdd(reinterpret_cast<float4*>(acc_copy + (int64_t)lab * p.d + col), u);
         }
       }
+      KMB_PROF(c_upd += clock64() - tw;)
     }
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0 && (warp & 3) == 0) printf("[ts prof] worker warp %d (cq %d): total %lld cyc, convert %lld, wait acc_full %lld, ld+argmax %lld, wait part %lld, wait labels %lld, update %lld, tiles %u\n", warp, cq, clock64() - t_all, c_conv, w_acc, c_arg, w_part, w_lab, c_upd, t);)
     if (update && cq == 0) {
       for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
       if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);

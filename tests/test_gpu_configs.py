@@ -118,6 +118,29 @@ def _stress_rows(rng, n, d, blobs=512, outliers=0.1, box=50.0, std=0.1):
     return X.astype(np.float32)
 
 
+def _exact_labels(X, C, chunk=20_000):
+    """argmin of the float64 squared distances, lowest index on ties."""
+    X64, C64 = X.astype(np.float64), C.astype(np.float64)
+    cc = (C64 * C64).sum(axis=1)
+    out = np.empty(X.shape[0], dtype=np.int64)
+    for a in range(0, X.shape[0], chunk):
+        out[a:a + chunk] = np.argmin(cc[None, :] - 2.0 * (X64[a:a + chunk] @ C64.T), axis=1)
+    return out
+
+
+def _outside_tie_window(labels, exact, X, C, rtol):
+    """(count, worst ratio) of rows whose label differs from the float64 label by more than a
+    tie of `rtol` relative to max(d_a, d_b, |x|^2)."""
+    bad = np.nonzero(labels != exact)[0]
+    if bad.size == 0:
+        return 0, 0.0
+    X64, C64 = X[bad].astype(np.float64), C.astype(np.float64)
+    da = ((X64 - C64[labels[bad]]) ** 2).sum(axis=1)
+    db = ((X64 - C64[exact[bad]]) ** 2).sum(axis=1)
+    ratio = np.abs(da - db) / np.maximum(np.maximum(da, db), (X64 * X64).sum(axis=1))
+    return int((ratio > rtol).sum()), float(ratio.max())
+
+
 def test_relocation_stress_shape_on_the_tensor_core_step():
     """d = 64, k = 4096, 90 % of the rows in 512 tight blobs and 10 % uniform outliers, on the
     tensor-core step, with initial centres that contain duplicates so that clusters come out
@@ -141,8 +164,17 @@ def test_relocation_stress_shape_on_the_tensor_core_step():
     torch.cuda.synchronize()
     st.check_device_waits()
     labels = st.labels_new.cpu().numpy().astype(np.int64)
-    ok, n_bad, n_unexplained = ref.labels_agree(labels, ref_labels, X, init, rtol=1e-6)
-    assert ok, (n_bad, n_unexplained)
+    # This data is ill-conditioned for ANY float32 dot-product argmin: |x|^2 is ~5e4 while the
+    # centres inside a blob are ~1 apart, so the reference's own fp32 arithmetic (the C
+    # restatement) leaves the 1e-6 tie window against float64 labels on a few dozen rows of
+    # 400 000 (measured: 64 rows, worst 1.33e-6).  Both are therefore judged against the float64
+    # labels: the CUDA path may not leave the window more often, nor further, than the
+    # reference arithmetic does, and never by more than 2e-6.
+    exact = _exact_labels(X, init)
+    n_ref, worst_ref = _outside_tie_window(ref_labels.astype(np.int64), exact, X, init, 1e-6)
+    n_gpu, worst_gpu = _outside_tie_window(labels, exact, X, init, 1e-6)
+    assert n_gpu <= max(n_ref, 2), (n_gpu, n_ref)
+    assert worst_gpu <= max(worst_ref, 1e-6) * 1.05 and worst_gpu <= 2e-6, (worst_gpu, worst_ref)
 
     sums, sizes = ref.accumulate_centroids(X.astype(np.float64), w.astype(np.float64), labels, k)
     empty = np.nonzero(sizes == 0)[0]
