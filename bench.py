@@ -706,8 +706,11 @@ def run_rowscan_arm(args, cfg):
     Y = X[:kt].contiguous()
     Dt = torch.empty((kt, rows), dtype=dtype, device=device)
     Xr = X[:rows]
-    ms = timed(lambda: check(lib.kmb_euclidean_distances(code, ptr(Xr), ptr(Y), ptr(Dt), rows, d, kt, s)))
-    out["euclidean_distances"] = dict(line(ms, rows * d * esize + rows * kt * esize), rows=rows, k=kt)
+    ms = timed(lambda: check(lib.kmb_euclidean_distances(code, ptr(Xr), ptr(Y), ptr(Dt), rows, d, kt, rows, s)))
+    out["euclidean_distances"] = dict(line(ms, rows * d * esize + rows * kt * esize), rows=rows, k=kt,
+                                      fma_tflops=3.0 * rows * d * kt / ms / 1e9,
+                                      note="direct squared differences: 3 flops (subtract, multiply, add) "
+                                           "per sample x centroid x feature on the FMA pipe")
     print(json.dumps(out), flush=True)
 
 

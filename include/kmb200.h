@@ -161,11 +161,14 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C,
                 const uint32_t* labels, void* per_sample, void* total, int64_t n, int d,
                 int k, void* workspace, size_t workspace_bytes, void* stream);
 
-/* out_t[j*n + i] = sqrt(sum_f (Y[j,f] - X[i,f])^2): the (k, n) array whose transpose
- * the reference returns.  Replaces make_compute_euclidean_distances_fixed_window_kernel,
+/* out_t[j*ldo + i] = sqrt(sum_f (Y[j,f] - X[i,f])^2) for i < n, j < k: the (k, n) array whose
+ * transpose the reference returns.  ldo >= n is the pitch of out_t in elements, so that a block
+ * of rows can be written into a larger (k, n_total) array (pass out_t + first_row and
+ * ldo = n_total).  Squared differences are accumulated directly, as in the reference.
+ * Replaces make_compute_euclidean_distances_fixed_window_kernel,
  * kmeans/kernels/compute_euclidean_distances.py:16-161. */
 int kmb_euclidean_distances(int dtype, const void* X, const void* Y, void* out_t,
-                            int64_t n, int d, int k, void* stream);
+                            int64_t n, int d, int k, int64_t ldo, void* stream);
 
 /* Empty-cluster relocation on un-normalised sums: for i < n_reloc, j = empty_list[i],
  * q = far_idx[i]: sums[label_q] -= w_q x_q; sums[j] = w_q x_q; counts likewise;

@@ -58,7 +58,7 @@ _SIGNATURES = {
                                   c_size_t, _P]),
     "kmb_inertia": (c_int, [c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t,
                             _P]),
-    "kmb_euclidean_distances": (c_int, [c_int, _P, _P, _P, c_int64, c_int, c_int, _P]),
+    "kmb_euclidean_distances": (c_int, [c_int, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P]),
     "kmb_relocate_empty_clusters": (c_int, [c_int, _P, _P, _P, c_int64, _P, _P, c_int, _P, _P, c_int,
                                             c_int, _P]),
     "kmb_topk": (c_int, [c_int, _P, c_int, c_int64, c_int, _P, _P, _P, c_size_t, _P]),

@@ -132,31 +132,6 @@ __global__ void sum_partials_kernel(const double* __restrict__ partial, int coun
   }
 }
 
-// out_t[j*n + i] = sqrt(sum_f (Y[j,f] - X[i,f])^2).  One thread per (i, j-chunk): the
-// sample row sits in registers/L1, centroids of the chunk stream through shared memory.
-template <typename T>
-__global__ void __launch_bounds__(RS_THREADS)
-distances_kernel(const T* __restrict__ X, const T* __restrict__ Y, T* __restrict__ out_t,
-                 int64_t n, int d, int k, int jchunk) {
-  extern __shared__ __align__(16) unsigned char dyn_smem[];
-  T* Ys = reinterpret_cast<T*>(dyn_smem);  // jchunk x d
-  const int j0 = blockIdx.y * jchunk;
-  const int nj = (k - j0 < jchunk) ? (k - j0) : jchunk;
-  for (int e = threadIdx.x; e < nj * d; e += RS_THREADS) Ys[e] = Y[(int64_t)j0 * d + e];
-  __syncthreads();
-  const int64_t i = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x;
-  if (i >= n) return;
-  const T* x = X + i * (int64_t)d;
-  for (int j = 0; j < nj; ++j) {
-    T s = T(0);
-    for (int f = 0; f < d; ++f) {
-      const T diff = Ys[j * d + f] - x[f];
-      s = fma(diff, diff, s);
-    }
-    out_t[(int64_t)(j0 + j) * n + i] = sqrt(s);
-  }
-}
-
 // partial[b*d + f] = float64 sum over the block's rows of X[i, f].
 template <typename T>
 __global__ void __launch_bounds__(RS_THREADS)
@@ -347,27 +322,6 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
                                                (T*)total, nullptr);
       KMB_CHECK_LAUNCH();
     }
-  });
-  return KMB_OK;
-}
-
-int kmb_euclidean_distances(int dtype, const void* X, const void* Y, void* out_t, int64_t n, int d,
-                            int k, void* stream) {
-  KMB_REQUIRE(X && Y && out_t, "kmb_euclidean_distances: NULL argument");
-  KMB_REQUIRE(n >= 0 && d > 0 && k > 0, "kmb_euclidean_distances: bad sizes");
-  if (n == 0) return KMB_OK;
-  const size_t esize = dtype == KMB_F32 ? 4 : 8;
-  KMB_REQUIRE((size_t)d * esize <= 32 * 1024, "kmb_euclidean_distances: d too large (%d)", d);
-  int jchunk = (int)((32 * 1024) / ((size_t)d * esize));
-  if (jchunk > k) jchunk = k;
-  if (jchunk > 64) jchunk = 64;
-  const int64_t gy = ceil_div(k, jchunk);
-  KMB_REQUIRE(gy <= 65535, "kmb_euclidean_distances: too many centroid chunks");
-  KMB_DISPATCH_DTYPE(dtype, {
-    dim3 grid((unsigned)ceil_div(n, RS_THREADS), (unsigned)gy);
-    distances_kernel<T><<<grid, RS_THREADS, (size_t)jchunk * d * sizeof(T), (cudaStream_t)stream>>>(
-        (const T*)X, (const T*)Y, (T*)out_t, n, d, k, jchunk);
-    KMB_CHECK_LAUNCH();
   });
   return KMB_OK;
 }

@@ -550,17 +550,54 @@ def get_labels_inertia(X_t, centroids_t, sample_weight, with_inertia, algo="auto
     return labels, total.cpu().numpy()
 
 
+# Rows per launch of the distance kernel: bounds the grid and lets callers that cannot hold the
+# whole (n, k) result walk it block by block.
+DISTANCE_ROWS_PER_LAUNCH = 1 << 22
+
+
 def get_euclidean_distances(X_t, Y_t):
     """(n, k) euclidean distances, returned like the reference as the transposed view of a
-    (k, n) array (sklearn_numba_dpex/kmeans/drivers.py:702-732)."""
+    (k, n) array (sklearn_numba_dpex/kmeans/drivers.py:702-732).  The result holds n * k
+    elements (41 GB for 10 M samples and 1 024 centres in float32): when it does not fit the
+    free device memory a MemoryError says so and points at `iter_euclidean_distances`."""
     X = _rows(X_t)
     Y = _rows(Y_t, "Y_t")
     n, d = X.shape
     k = Y.shape[0]
+    need = n * k * X.element_size()
+    free, _ = torch.cuda.mem_get_info(X.device)
+    if need > free:
+        raise MemoryError(
+            f"the ({n}, {k}) distance matrix needs {need / 1e9:.1f} GB and {free / 1e9:.1f} GB of "
+            "device memory are free; walk it in row blocks with iter_euclidean_distances")
     out_t = torch.empty((k, n), dtype=X.dtype, device=X.device)
-    check(lib.kmb_euclidean_distances(dtype_code(X.dtype), ptr(X), ptr(Y), ptr(out_t), n, d, k,
-                                      stream_ptr(X.device)), "kmb_euclidean_distances")
+    for start in range(0, n, DISTANCE_ROWS_PER_LAUNCH):
+        stop = min(n, start + DISTANCE_ROWS_PER_LAUNCH)
+        check(lib.kmb_euclidean_distances(dtype_code(X.dtype), ptr(X[start:stop]), ptr(Y),
+                                          ptr(out_t[:, start:]), stop - start, d, k, n,
+                                          stream_ptr(X.device)), "kmb_euclidean_distances")
     return out_t.T
+
+
+def iter_euclidean_distances(X_t, Y_t, rows_per_block=None):
+    """Yields (start, stop, D) with D the (stop - start, k) distances of samples
+    [start, stop), block after block, for results too large to hold at once.  The block buffer
+    is reused: consume (or copy) D before asking for the next block."""
+    X = _rows(X_t)
+    Y = _rows(Y_t, "Y_t")
+    n, d = X.shape
+    k = Y.shape[0]
+    if rows_per_block is None:
+        budget = 1 << 30                           # about 1 GB of distances per block
+        rows_per_block = max(128, min(n, budget // (k * X.element_size())))
+    rows_per_block = int(rows_per_block)
+    buf = torch.empty((k, min(n, rows_per_block)), dtype=X.dtype, device=X.device)
+    for start in range(0, n, rows_per_block):
+        stop = min(n, start + rows_per_block)
+        check(lib.kmb_euclidean_distances(dtype_code(X.dtype), ptr(X[start:stop]), ptr(Y), ptr(buf),
+                                          stop - start, d, k, buf.shape[1], stream_ptr(X.device)),
+              "kmb_euclidean_distances")
+        yield start, stop, buf[:, : stop - start].T
 
 
 # ------------------------------------------------------------------------- k-means++
