@@ -120,13 +120,27 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test, but the hardware may keep the thread asleep for up to `hint_ns` nanoseconds
+// while the phase is incomplete: a waiting warp then costs no issue slots (a spinning one
+// competes with the epilogue warps for the integer pipe).
+__device__ __forceinline__ bool mbar_try_wait_sleep(void* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t TC_SLEEP_NS = 50000;
 // Bounded wait: false when the CTA is aborting or the time limit ran out.
 __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm, int* error_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_sleep(bar, parity, TC_SLEEP_NS)) return true;
     if (sm->abort_flag) return false;
     if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
       sm->abort_flag = 1;
@@ -260,11 +274,59 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return r;
 }
 
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Maximum of 32 scores with three-input maxima (NaNs are dropped; 32 NaNs give NaN).
+__device__ __forceinline__ float max32(const float (&q)[32]) {
+  float a[11];
+#pragma unroll
+  for (int j = 0; j < 10; ++j) a[j] = fmax3(q[3 * j], q[3 * j + 1], q[3 * j + 2]);
+  a[10] = fmaxf(q[30], q[31]);
+  const float b0 = fmax3(a[0], a[1], a[2]), b1 = fmax3(a[3], a[4], a[5]);
+  const float b2 = fmax3(a[6], a[7], a[8]), b3 = fmaxf(a[9], a[10]);
+  return fmaxf(fmax3(b0, b1, b2), b3);
+}
+
+// LOWEST index j with q[j] == m, m being the maximum of the 32 scores; (-inf, base) when m is
+// NaN.  The compare / select pairs of a plain scan run on the integer pipe, which issues at
+// half rate and is what bounds the epilogue; here the search runs on the FMA pipe instead:
+// e_j = (m - q[j]) * 2^126 + j is exactly j where q[j] == m and at least 2^12 elsewhere (the
+// difference of two distinct floats near m is at least |m| 2^-24), so the minimum of the e_j,
+// taken with three-input minima, IS the index.  The bound needs |m| >= 2^-90 and finite
+// scores; a warp in which any lane falls outside (or finds no index below 32) takes the exact
+// scan instead.
+__device__ __forceinline__ void index_of_max32(const float (&q)[32], float m, uint32_t base,
+                                               float& out_v, uint32_t& out_i) {
+  float e[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) e[j] = fmaf(m - q[j], 0x1p126f, (float)j);
+  float a[11];
+#pragma unroll
+  for (int j = 0; j < 10; ++j) a[j] = fmin3(e[3 * j], e[3 * j + 1], e[3 * j + 2]);
+  a[10] = fminf(e[30], e[31]);
+  const float b0 = fmin3(a[0], a[1], a[2]), b1 = fmin3(a[3], a[4], a[5]);
+  const float b2 = fmin3(a[6], a[7], a[8]), b3 = fminf(a[9], a[10]);
+  const float emin = fminf(fmin3(b0, b1, b2), b3);
+  uint32_t idx = (uint32_t)(int)emin;
+  const bool fast_ok = (emin < 32.f) && (fabsf(m) >= 0x1p-90f);
+  if (__any_sync(0xffffffffu, !fast_ok)) {
+    uint32_t ix = 0;
+#pragma unroll
+    for (int j = 31; j >= 1; --j) ix = (q[j] == m) ? (uint32_t)j : ix;
+    ix = (q[0] == m) ? 0u : ix;
+    idx = ix;
+  }
+  out_v = (m == m) ? m : __int_as_float(0xff800000);
+  out_i = base + idx;
+}
+
 // Maximum of the scores s[j] of 32 consecutive centroids and the LOWEST index that attains it.
 // The score is acc[j] - h[j] (the negated pseudo-inertia), or acc[j] itself when the half norms
-// were folded into the contraction.  A NaN score never wins (max drops it); 32 NaNs give
-// (-inf, base).  Values first with three-input maxima, then one equality scan from the top
-// index down, so that the lowest equal index is the last one written.
+// were folded into the contraction.  A NaN score never wins; 32 NaNs give (-inf, base).
 template <bool FOLD>
 __device__ __forceinline__ void argmax32(const uint32_t (&v)[32], const float4 (&h4)[8],
                                          uint32_t base, float& out_v, uint32_t& out_i) {
@@ -282,19 +344,7 @@ __device__ __forceinline__ void argmax32(const uint32_t (&v)[32], const float4 (
       q[4 * j4 + 3] = __uint_as_float(v[4 * j4 + 3]) - hv.w;
     }
   }
-  float a[11];
-#pragma unroll
-  for (int j = 0; j < 10; ++j) a[j] = fmax3(q[3 * j], q[3 * j + 1], q[3 * j + 2]);
-  a[10] = fmaxf(q[30], q[31]);
-  const float b0 = fmax3(a[0], a[1], a[2]), b1 = fmax3(a[3], a[4], a[5]);
-  const float b2 = fmax3(a[6], a[7], a[8]), b3 = fmaxf(a[9], a[10]);
-  float m = fmaxf(fmax3(b0, b1, b2), b3);
-  uint32_t idx = 0;
-#pragma unroll
-  for (int j = 31; j >= 1; --j) idx = (q[j] == m) ? (uint32_t)j : idx;
-  idx = (q[0] == m) ? 0u : idx;
-  out_v = (m == m) ? m : __int_as_float(0xff800000);
-  out_i = base + idx;
+  index_of_max32(q, max32(q), base, out_v, out_i);
 }
 
 template <bool FOLD>
@@ -773,8 +823,7 @@ __device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, 
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_sleep(bar, parity, TC_SLEEP_NS)) return true;
     if (sm->abort_flag) return false;
     if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
       sm->abort_flag = 1;

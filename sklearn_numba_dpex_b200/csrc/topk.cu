@@ -20,8 +20,11 @@ constexpr int TK_BINS = 1 << TK_RADIX_BITS;
 
 struct TkState {          // per row
   unsigned long long prefix_hi, prefix_lo;  // digits decided so far (right-aligned)
+  unsigned long long kth_hi, kth_lo;        // smallest key that is still among the k largest
   long long k_rem;                          // how many of the matching items are wanted
   unsigned long long cursor;                // gather cursor
+  unsigned int ticket;                      // CTAs of the current histogram pass that are done
+  int done;                                 // the threshold is final: later passes return at once
 };
 
 template <typename T>
@@ -52,18 +55,30 @@ __global__ void topk_init_kernel(TkState* st, unsigned int* hist, int n_rows, in
   if (e < (size_t)n_rows) {
     st[e].prefix_hi = 0ull;
     st[e].prefix_lo = 0ull;
+    st[e].kth_hi = 0ull;
+    st[e].kth_lo = 0ull;
     st[e].k_rem = k;
     st[e].cursor = 0ull;
+    st[e].ticket = 0u;
+    st[e].done = 0;
   }
 }
 
-// Histogram of the digit at `shift` over the items whose higher digits equal the prefix.
+// Histogram of the digit at `shift` over the items whose higher digits equal the prefix; the
+// CTA of a row that finishes last then walks the bins from the top until k_rem items are
+// covered and appends that digit to the prefix.  When the chosen bin holds exactly the number of
+// items still wanted, everything at or above it is the answer: the row is marked done and the
+// remaining passes return without reading it (the reference stops its passes the same way,
+// common/topk.py:1059-1061).  With continuous data that happens after two or three of the
+// eight (fp64: twelve) passes.
 template <typename T>
 __global__ void __launch_bounds__(TK_THREADS)
-topk_hist_kernel(const T* __restrict__ values, int64_t n_cols, const TkState* __restrict__ st,
+topk_hist_kernel(const T* __restrict__ values, int64_t n_cols, TkState* __restrict__ st,
                  unsigned int* __restrict__ hist, int shift, int first_pass) {
   __shared__ unsigned int sh[TK_BINS];
+  __shared__ int last_s;
   const int row = blockIdx.y;
+  if (*((volatile int*)&st[row].done)) return;
   const T* v = values + (int64_t)row * n_cols;
   sh[threadIdx.x] = 0u;
   __syncthreads();
@@ -75,31 +90,40 @@ topk_hist_kernel(const T* __restrict__ values, int64_t n_cols, const TkState* __
       atomicAdd(&sh[(unsigned)(key >> shift) & (TK_BINS - 1)], 1u);
   }
   __syncthreads();
+  unsigned int* h = hist + (size_t)row * TK_BINS;
   const unsigned int c = sh[threadIdx.x];
-  if (c) atomicAdd(&hist[(size_t)row * TK_BINS + threadIdx.x], c);
-}
+  if (c) atomicAdd(&h[threadIdx.x], c);
 
-// One warp per row: walk the bins from the top until k_rem items are covered.
-__global__ void topk_advance_kernel(TkState* __restrict__ st, const unsigned int* __restrict__ hist,
-                                    int n_rows) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= n_rows) return;
-  const unsigned int* h = hist + (size_t)row * TK_BINS;
-  long long k_rem = st[row].k_rem;
-  int digit = 0;
-  for (int b = TK_BINS - 1; b >= 0; --b) {
-    const long long c = (long long)h[b];
-    if (c >= k_rem) {
-      digit = b;
-      break;
+  // ---- the last CTA of the row advances the prefix
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = (atomicAdd(&st[row].ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  sh[threadIdx.x] = __ldcg(&h[threadIdx.x]);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long k_rem = st[row].k_rem;
+    int digit = 0;
+    for (int b = TK_BINS - 1; b >= 0; --b) {
+      const long long cb = (long long)sh[b];
+      if (cb >= k_rem) {
+        digit = b;
+        break;
+      }
+      k_rem -= cb;
     }
-    k_rem -= c;
+    const u128 np = (prefix << TK_RADIX_BITS) | (u128)digit;
+    const u128 kth = np << shift;
+    st[row].prefix_hi = (unsigned long long)(np >> 64);
+    st[row].prefix_lo = (unsigned long long)np;
+    st[row].kth_hi = (unsigned long long)(kth >> 64);
+    st[row].kth_lo = (unsigned long long)kth;
+    st[row].k_rem = k_rem;
+    st[row].ticket = 0u;
+    if ((long long)sh[digit] == k_rem || shift == 0) st[row].done = 1;
   }
-  u128 prefix = ((u128)st[row].prefix_hi << 64) | (u128)st[row].prefix_lo;
-  prefix = (prefix << TK_RADIX_BITS) | (u128)digit;
-  st[row].prefix_hi = (unsigned long long)(prefix >> 64);
-  st[row].prefix_lo = (unsigned long long)prefix;
-  st[row].k_rem = k_rem;
 }
 
 // Emit the items whose key is >= the k-th largest key (exactly k per row), unordered.
@@ -109,7 +133,7 @@ topk_gather_kernel(const T* __restrict__ values, int64_t n_cols, TkState* __rest
                    int64_t* __restrict__ tmp_idx) {
   const int row = blockIdx.y;
   const T* v = values + (int64_t)row * n_cols;
-  const u128 kth = ((u128)st[row].prefix_hi << 64) | (u128)st[row].prefix_lo;
+  const u128 kth = ((u128)st[row].kth_hi << 64) | (u128)st[row].kth_lo;
   for (int64_t i = (int64_t)blockIdx.x * TK_THREADS + threadIdx.x; i < n_cols;
        i += (int64_t)gridDim.x * TK_THREADS) {
     const u128 key = TkKey<T>::make(v[i], i);
@@ -120,24 +144,40 @@ topk_gather_kernel(const T* __restrict__ values, int64_t n_cols, TkState* __rest
   }
 }
 
-// Rank sort of the k winners of a row: position = number of winners with a larger key.
+// Rank sort of the k winners of a row: position = number of winners with a larger key.  The
+// keys are staged in shared memory when all k of them fit (`staged`), else read from global.
+constexpr int TK_SORT_SMEM_MAX_K = 4096;
+
 template <typename T>
 __global__ void __launch_bounds__(TK_THREADS)
 topk_sort_kernel(const T* __restrict__ values, int64_t n_cols, int k,
                  const int64_t* __restrict__ tmp_idx, T* __restrict__ out_values,
-                 int64_t* __restrict__ out_idx) {
+                 int64_t* __restrict__ out_idx, int staged) {
+  extern __shared__ __align__(16) unsigned char tk_dyn[];
+  u128* keys_s = reinterpret_cast<u128*>(tk_dyn);
   const int row = blockIdx.y;
   const int e = blockIdx.x * TK_THREADS + threadIdx.x;
-  if (e >= k) return;
   const T* v = values + (int64_t)row * n_cols;
   const int64_t* mine = tmp_idx + (int64_t)row * k;
+  if (staged) {
+    for (int o = threadIdx.x; o < k; o += TK_THREADS) {
+      const int64_t j = mine[o];
+      keys_s[o] = TkKey<T>::make(v[j], j);
+    }
+    __syncthreads();
+  }
+  if (e >= k) return;
   const int64_t i = mine[e];
   const T vi = v[i];
   const u128 key = TkKey<T>::make(vi, i);
   int rank = 0;
-  for (int o = 0; o < k; ++o) {
-    const int64_t j = mine[o];
-    rank += (TkKey<T>::make(v[j], j) > key) ? 1 : 0;
+  if (staged) {
+    for (int o = 0; o < k; ++o) rank += (keys_s[o] > key) ? 1 : 0;
+  } else {
+    for (int o = 0; o < k; ++o) {
+      const int64_t j = mine[o];
+      rank += (TkKey<T>::make(v[j], j) > key) ? 1 : 0;
+    }
   }
   if (out_values) out_values[(int64_t)row * k + rank] = vi;
   if (out_idx) out_idx[(int64_t)row * k + rank] = i;
@@ -169,13 +209,17 @@ int topk_run(const T* values, int n_rows, int64_t n_cols, int k, T* out_values, 
     unsigned int* h = hist + (size_t)p * n_rows * TK_BINS;
     topk_hist_kernel<T><<<grid, TK_THREADS, 0, s>>>(values, n_cols, st, h, shift, p == 0);
     KMB_CHECK_LAUNCH();
-    topk_advance_kernel<<<(unsigned)ceil_div(n_rows, 128), 128, 0, s>>>(st, h, n_rows);
-    KMB_CHECK_LAUNCH();
   }
   topk_gather_kernel<T><<<grid, TK_THREADS, 0, s>>>(values, n_cols, st, k, tmp_idx);
   KMB_CHECK_LAUNCH();
   dim3 sgrid((unsigned)ceil_div(k, TK_THREADS), (unsigned)n_rows);
-  topk_sort_kernel<T><<<sgrid, TK_THREADS, 0, s>>>(values, n_cols, k, tmp_idx, out_values, out_idx);
+  const int staged = k <= TK_SORT_SMEM_MAX_K ? 1 : 0;
+  const size_t sort_smem = staged ? (size_t)k * sizeof(u128) : 0;
+  if (sort_smem > 48 * 1024)
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(topk_sort_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)(TK_SORT_SMEM_MAX_K * sizeof(u128))));
+  topk_sort_kernel<T><<<sgrid, TK_THREADS, sort_smem, s>>>(values, n_cols, k, tmp_idx, out_values,
+                                                          out_idx, staged);
   KMB_CHECK_LAUNCH();
   return KMB_OK;
 }
