@@ -394,26 +394,24 @@ def run_gpu_arm(args, cfg):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
-    step_idx = {"i": 0}
+    def around_fused_kernel(kind, it):
+        # events around the fused kernel of every timed iteration (iterations that the
+        # pipelined loop enqueues ahead and never uses fall outside the list)
+        i = it - it0
+        if 0 <= i < args.steps:
+            kev[i][0 if kind == "pre" else 1].record()
 
-    def timed_launch_step():
-        # LloydState.launch_step with events around the fused kernel
-        a, b = kev[step_idx["i"]]
-        a.record()
-        state.launch_fused_step()
-        b.record()
-        state.launch_reduce_finalize()
-        step_idx["i"] += 1
-
-    state.launch_step = timed_launch_step
+    it0 = state.it
+    state.event_hook = around_fused_kernel
     t_begin = time.time()
     ev0.record()
-    for _ in range(args.steps):
-        state.step()
+    out = state.run(args.steps, -1.0, pipelined=not args.no_pipeline, stop_on_strict=False)
     ev1.record()
     barrier()
     t_end = time.time()
-    del state.launch_step
+    state.event_hook = None
+    steps_run = out["n_iter"]
+    assert steps_run == args.steps, (steps_run, args.steps)
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     elapsed_ms = ev0.elapsed_time(ev1)
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
@@ -422,7 +420,7 @@ def run_gpu_arm(args, cfg):
     if world > 1:
         tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
     elapsed_ms, kernel_ms = float(t[0]), float(t[1])
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = elapsed_ms / steps_run
     value = 1e3 / ms_per_step
 
     # ---- end to end through the plugin: host buffers in, host results out
@@ -434,7 +432,7 @@ def run_gpu_arm(args, cfg):
         Ch = C0.cpu().pin_memory()
         # scaling cross-check, outside every timed region: the counts of the last step add up to
         # n and every rank holds the same total shift
-        counts_total = float(state.packed[k * state.d: k * state.d + k].double().sum())
+        counts_total = float(state.packed_last[k * state.d: k * state.d + k].double().sum())
         shift_bits = torch.tensor([state.status_host.numpy().view(np.float64)[1]], dtype=torch.float64,
                                   device=device)
         if world > 1:
@@ -556,7 +554,7 @@ def run_gpu_arm(args, cfg):
                             "fp_tflops_achieved": tf_achieved, "fma_peak_tflops": fma_peak}
         roofline["kernel_ms"] = kernel_ms
         line = {"metric": "Lloyd iterations/s", "value": value, "unit": "iterations/s",
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "n_gpus": world, "steps": steps_run, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
                 "config": {"workload": cfg["desc"], "n": n, "d": d, "k": k, "algo": algo_name,
@@ -730,6 +728,8 @@ def main():
     ap.add_argument("--mode", default="step", choices=["step", "fit", "rowscan"],
                     help="step: the headline per-iteration benchmark; fit: k-means++ + Lloyd; "
                          "rowscan: the k-means++ pass and the inertia kernel alone (1 GPU)")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="read every iteration's status before enqueuing the next one")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()

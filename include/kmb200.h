@@ -47,7 +47,8 @@ typedef enum {
   KMB_ALGO_TF32X3 = 2     /* tcgen05 kind::tf32, 3 products per pair (fp32 only)     */
 } kmb_algo;
 
-/* Record written by kmb_lloyd_finalize (device memory, 32 bytes). */
+/* Record written by kmb_lloyd_finalize (32 bytes of device memory, or of page-locked host
+ * memory through its device address, see kmb_host_device_pointer). */
 typedef struct {
   int32_t n_empty;     /* clusters whose weight sum is exactly 0                      */
   int32_t changed;     /* 1 if any label differs from the previous labels, else 0     */
@@ -78,6 +79,13 @@ const char* kmb_last_error(void);
 int kmb_version(void);
 /* SM count and compute capability of `device` (host outputs). */
 int kmb_device_info(int device, int* sm_count, int* cc_major, int* cc_minor);
+
+/* Device address of page-locked host memory (`host` must be pinned, e.g. cudaHostAlloc), so
+ * that a kernel can write a small result record straight into host memory: *device receives
+ * the pointer to hand to e.g. kmb_lloyd_finalize as `status`.  No counterpart in the reference,
+ * which reads its per-iteration scalars with blocking device-to-host copies
+ * (kmeans/drivers.py:238, 329, 341). */
+int kmb_host_device_pointer(void* host, void** device);
 
 /* Bytes of scratch that is enough for ANY call below on these sizes. */
 size_t kmb_workspace_bytes(int64_t n, int d, int k);

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "kmb_last_error": (c_char_p, []),
     "kmb_version": (c_int, []),
     "kmb_device_info": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "kmb_host_device_pointer": (c_int, [_P, POINTER(c_void_p)]),
     "kmb_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "kmb_lloyd_acc_len": (c_int64, [c_int, c_int]),
     "kmb_lloyd_acc_copies": (c_int, [c_int, c_int, c_int64, c_int, c_int]),
@@ -176,6 +177,16 @@ def lloyd_workspace(device, n, d, k, own=False):
     check(lib.kmb_lloyd_workspace_init(ptr(buf), buf.numel(), stream_ptr(device)),
           "kmb_lloyd_workspace_init")
     return buf, buf.numel()
+
+
+def host_device_pointer(pinned_tensor):
+    """Device address of a page-locked host tensor (for records a kernel writes directly)."""
+    if pinned_tensor.is_cuda or not pinned_tensor.is_pinned():
+        raise ValueError("host_device_pointer needs a page-locked host tensor")
+    out = c_void_p()
+    check(lib.kmb_host_device_pointer(ptr(pinned_tensor), ctypes.byref(out)),
+          "kmb_host_device_pointer")
+    return out
 
 
 def check_wait_error(ws, device):

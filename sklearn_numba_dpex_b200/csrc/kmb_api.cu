@@ -26,6 +26,12 @@ int kmb_device_info(int device, int* sm_count, int* cc_major, int* cc_minor) {
   return KMB_OK;
 }
 
+int kmb_host_device_pointer(void* host, void** device) {
+  KMB_REQUIRE(host && device, "kmb_host_device_pointer: NULL argument");
+  KMB_CHECK_CUDA(cudaHostGetDevicePointer(device, host, 0));
+  return KMB_OK;
+}
+
 size_t kmb_workspace_bytes(int64_t n, int d, int k) {
   // Fixed-order reductions use <= 4096 float64 partials per reduced quantity and at most
   // max(d, 64) quantities; the tensor-core step keeps hi/lo copies of the centroids.

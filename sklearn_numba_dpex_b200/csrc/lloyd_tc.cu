@@ -92,6 +92,7 @@ struct TcParams {
   int d_pad;
   int k;
   int k_pad;
+  uint32_t sleep_ns;        // > 0: barrier waits may sleep this long between polls (see mbar_try_wait_sleep)
 };
 
 // ---------------------------------------------------------------------------- PTX
@@ -134,13 +135,19 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(void* bar, uint32_t parity, 
       : "memory");
   return ok != 0;
 }
-constexpr uint32_t TC_SLEEP_NS = 50000;
+
 // Bounded wait: false when the CTA is aborting or the time limit ran out.
-__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm, int* error_flag) {
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm, int* error_flag,
+                                          uint32_t sleep_ns = 0u) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait_sleep(bar, parity, TC_SLEEP_NS)) return true;
+    if (sleep_ns != 0u) {
+      if (mbar_try_wait_sleep(bar, parity, sleep_ns)) return true;
+    } else {
+      for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    }
     if (sm->abort_flag) return false;
     if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
       sm->abort_flag = 1;
@@ -274,12 +281,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return r;
 }
 
-__device__ __forceinline__ float fmin3(float a, float b, float c) {
-  float r;
-  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-
 // Maximum of 32 scores with three-input maxima (NaNs are dropped; 32 NaNs give NaN).
 __device__ __forceinline__ float max32(const float (&q)[32]) {
   float a[11];
@@ -292,34 +293,16 @@ __device__ __forceinline__ float max32(const float (&q)[32]) {
 }
 
 // LOWEST index j with q[j] == m, m being the maximum of the 32 scores; (-inf, base) when m is
-// NaN.  The compare / select pairs of a plain scan run on the integer pipe, which issues at
-// half rate and is what bounds the epilogue; here the search runs on the FMA pipe instead:
-// e_j = (m - q[j]) * 2^126 + j is exactly j where q[j] == m and at least 2^12 elsewhere (the
-// difference of two distinct floats near m is at least |m| 2^-24), so the minimum of the e_j,
-// taken with three-input minima, IS the index.  The bound needs |m| >= 2^-90 and finite
-// scores; a warp in which any lane falls outside (or finds no index below 32) takes the exact
-// scan instead.
+// NaN: one equality scan from the top index down, so that the lowest equal index is written
+// last.  (A variant that searched on the FMA pipe, e_j = (m - q[j]) * 2^126 + j reduced with
+// three-input minima, executed 25 % more instructions and measured 6 % slower on short rows:
+// the epilogue is bound by issue slots, not by the integer pipe.)
 __device__ __forceinline__ void index_of_max32(const float (&q)[32], float m, uint32_t base,
                                                float& out_v, uint32_t& out_i) {
-  float e[32];
+  uint32_t idx = 0;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) e[j] = fmaf(m - q[j], 0x1p126f, (float)j);
-  float a[11];
-#pragma unroll
-  for (int j = 0; j < 10; ++j) a[j] = fmin3(e[3 * j], e[3 * j + 1], e[3 * j + 2]);
-  a[10] = fminf(e[30], e[31]);
-  const float b0 = fmin3(a[0], a[1], a[2]), b1 = fmin3(a[3], a[4], a[5]);
-  const float b2 = fmin3(a[6], a[7], a[8]), b3 = fminf(a[9], a[10]);
-  const float emin = fminf(fmin3(b0, b1, b2), b3);
-  uint32_t idx = (uint32_t)(int)emin;
-  const bool fast_ok = (emin < 32.f) && (fabsf(m) >= 0x1p-90f);
-  if (__any_sync(0xffffffffu, !fast_ok)) {
-    uint32_t ix = 0;
-#pragma unroll
-    for (int j = 31; j >= 1; --j) ix = (q[j] == m) ? (uint32_t)j : ix;
-    ix = (q[0] == m) ? 0u : ix;
-    idx = ix;
-  }
+  for (int j = 31; j >= 1; --j) idx = (q[j] == m) ? (uint32_t)j : idx;
+  idx = (q[0] == m) ? 0u : idx;
   out_v = (m == m) ? m : __int_as_float(0xff800000);
   out_i = base + idx;
 }
@@ -408,7 +391,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
         const uint32_t xs = two_tiles ? (t & 1) : 0, xu = two_tiles ? (t >> 1) : t;
-        if (!mbar_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag)) break;
+        if (!mbar_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) break;
         mbar_expect_tx(&sm->x_full[xs], (uint32_t)n_kc * TC_ATOM_BYTES);
         for (int kc = 0; kc < n_kc; ++kc)
           tma_load_2d(sm->xstage[xs * 2 + kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full[xs]);
@@ -422,11 +405,11 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         if (resident && it != 0) break;     // everything is in shared memory already
         for (int i = 0; i < n_nt && ok; ++i) {
-          const int nt = (nt0 + i) % n_nt;
+          const int nt = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
           for (int j = 0; j < n_kc; ++j, ++it) {
             const int kc = (kc0 + j) % n_kc;
             const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
-            if (!mbar_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
+            if (!mbar_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) {
               ok = false;
               break;
             }
@@ -458,7 +441,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const uint32_t a_hi0 = tmem_base + (two_tiles ? xs * 128 : TC_A_HI_COL);
       const uint32_t a_lo0 = tmem_base + (two_tiles ? xs * 128 + 64 : TC_A_LO_COL);
       KMB_PROF(tw = clock64();)
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag, p.sleep_ns))) break;
       KMB_PROF(w_conv += clock64() - tw;)
       tc_fence_after();
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
@@ -471,7 +454,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           continue;
         }
         KMB_PROF(tw = clock64();)
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag, p.sleep_ns))) {
           ok = false;
           break;
         }
@@ -480,7 +463,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         int kc = kc0;
         for (int j = 0; j < n_kc; ++j) {
           KMB_PROF(tw = clock64();)
-          if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full[s], lap, sm, p.error_flag, p.sleep_ns))) {
             ok = false;
             break;
           }
@@ -546,7 +529,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const uint32_t xs = two_tiles ? (tt & 1) : 0, xu = two_tiles ? (tt >> 1) : tt;
       const uint32_t hi_col = two_tiles ? xs * 128 : TC_A_HI_COL;
       const uint32_t lo_col = two_tiles ? xs * 128 + 64 : TC_A_LO_COL;
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag))) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag, p.sleep_ns))) return false;
       for (int kc = 0; kc < n_kc; ++kc) {
         if (n_kc > 1 && (kc & 1) != grp) continue;     // the other group's chunk
         uint32_t hi[32], lo[32];
@@ -610,9 +593,10 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       KMB_PROF(c_conv += clock64() - tw;)
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
-        const int cn = ((nt0 + i) % n_nt) * TC_BN + grp * 64;   // first centroid of this half
+        const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;   // nt0, i < n_nt: no division
+        const int cn = nt_w * TC_BN + grp * 64;   // first centroid of this half
         KMB_PROF(tw = clock64();)
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag, p.sleep_ns))) {
           ok = false;
           break;
         }
@@ -678,7 +662,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) mbar_arrive(&sm->part_full[buf]);
       } else {
         KMB_PROF(tw = clock64();)
-        if (!__all_sync(0xffffffffu, mbar_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag))) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag, p.sleep_ns))) break;
         KMB_PROF(w_part += clock64() - tw;)
         const float ov = sm->part_v[row];
         const uint32_t oi = sm->part_i[row];
@@ -700,7 +684,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       // warp has passed this point of tile t + 1, which it reaches only after finishing the
       // update of tile t.
       KMB_PROF(tw = clock64();)
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag, p.sleep_ns))) break;
       KMB_PROF(w_lab += clock64() - tw;)
       if (!update) continue;
       KMB_PROF(tw = clock64();)
@@ -819,11 +803,17 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8])
 }
 
 // Bounded wait on a barrier of the short-row kernel (same rule as mbar_wait).
-__device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, int* error_flag) {
+__device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, int* error_flag,
+                                        uint32_t sleep_ns = 0u) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait_sleep(bar, parity, TC_SLEEP_NS)) return true;
+    if (sleep_ns != 0u) {
+      if (mbar_try_wait_sleep(bar, parity, sleep_ns)) return true;
+    } else {
+      for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    }
     if (sm->abort_flag) return false;
     if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
       sm->abort_flag = 1;
@@ -880,7 +870,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
         const uint32_t xs = t & 1, xu = t >> 1;
-        if (!ts_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag)) break;
+        if (!ts_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) break;
         mbar_expect_tx(&sm->x_full[xs], TC_ATOM_BYTES);
         tma_load_2d(sm->xstage[xs], &map_x, 0, (int)(tile * TC_BM), &sm->x_full[xs]);
       }
@@ -893,9 +883,9 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         if (resident && it != 0) break;            // everything is in shared memory already
         for (int i = 0; i < n_nt; ++i, ++it) {
-          const int nt = (nt0 + i) % n_nt;
+          const int nt = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
           const uint32_t s = it % TC_STAGES, u = it / TC_STAGES;
-          if (!ts_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag)) {
+          if (!ts_wait(&sm->b_empty[s], (u & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) {
             ok = false;
             break;
           }
@@ -918,12 +908,12 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
       const uint32_t xs = t & 1, xu = t >> 1;
       const uint32_t a_hi = tmem_base + xs * 64, a_lo = a_hi + 32;
-      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_conv[xs], xu & 1, sm, p.error_flag, p.sleep_ns))) break;
       tc_fence_after();
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
         if ((g & 1u) == mw) {
-          if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag)) ||
-              !__all_sync(0xffffffffu, ts_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+          if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_empty[mw], ((g >> 1) & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) ||
+              !__all_sync(0xffffffffu, ts_wait(&sm->b_full[s], lap, sm, p.error_flag, p.sleep_ns))) {
             ok = false;
             break;
           }
@@ -973,7 +963,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     auto convert_tile = [&](uint32_t tt) -> bool {
       const uint32_t xs = tt & 1, xu = tt >> 1;
-      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag))) return false;
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->x_full[xs], xu & 1, sm, p.error_flag, p.sleep_ns))) return false;
       uint32_t hi[8], lo[8];
       const unsigned char* rowp = sm->xstage[xs] + row * 128;
 #pragma unroll
@@ -1034,9 +1024,10 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       KMB_PROF(c_conv += clock64() - tw;)
       for (int i = 0; i < n_nt; ++i, ++g) {
         const uint32_t ab = g & 1, ug = g >> 1;
-        const int cn = ((nt0 + i) % n_nt) * TC_BN + cq * 32;
+        const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;   // nt0, i < n_nt: no division
+        const int cn = nt_w * TC_BN + cq * 32;
         KMB_PROF(tw = clock64();)
-        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag))) {
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->acc_full[ab], ug & 1, sm, p.error_flag, p.sleep_ns))) {
           ok = false;
           break;
         }
@@ -1068,7 +1059,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         if (lane == 0) mbar_arrive(&sm->part_full[buf]);
       } else {
         KMB_PROF(tw = clock64();)
-        if (!__all_sync(0xffffffffu, ts_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag))) break;
+        if (!__all_sync(0xffffffffu, ts_wait(&sm->part_full[buf], ub & 1, sm, p.error_flag, p.sleep_ns))) break;
         KMB_PROF(w_part += clock64() - tw;)
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
@@ -1092,7 +1083,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       // it a tile early.  lab_s[buf] is reused two tiles later; by then every warp has passed
       // this point of tile t + 1, which it reaches only after finishing the update of tile t.
       KMB_PROF(tw = clock64();)
-      if (!__all_sync(0xffffffffu, ts_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, ts_wait(&sm->lab_ready[buf], ub & 1, sm, p.error_flag, p.sleep_ns))) break;
       KMB_PROF(w_lab += clock64() - tw;)
       if (!update) continue;
       KMB_PROF(tw = clock64();)
@@ -1131,6 +1122,18 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     tc_fence_after();
     tmem_dealloc(tmem_base, TC_TMEM_COLS);
   }
+}
+
+// KMB_TC_SLEEP_NS=<n> in the environment makes the barrier waits sleep up to n ns between
+// polls (A/B runs); the default polls without sleeping.
+static uint32_t tc_sleep_ns() {
+  static long cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("KMB_TC_SLEEP_NS");
+    cached = (e != nullptr) ? atol(e) : 0;
+    if (cached < 0) cached = 0;
+  }
+  return (uint32_t)cached;
 }
 
 // Set KMB_TC_SMALL=0 in the environment to run short rows on the general kernel (A/B runs).
@@ -1271,6 +1274,7 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.X = X; p.w = w; p.h_pad = ws.h_pad; p.prev = prev; p.labels = labels; p.acc = acc;
   p.dots = dots; p.error_flag = &ws.ctl->wait_error; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
+  p.sleep_ns = tc_sleep_ns();
 
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();

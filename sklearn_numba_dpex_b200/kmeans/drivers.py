@@ -18,7 +18,8 @@ import torch
 from .. import dist
 from .._cabi import (ALGO_AUTO, ALGO_NAMES, FIN_CLEAR_ACC, FIN_MERGE, FIN_PREPARE_TF32X3,
                      STATUS_DTYPE, STEP_ACC_CLEARED, STEP_OPERANDS_READY, KmbError, c_void_p, check,
-                     check_wait_error, dtype_code, lib, lloyd_workspace, ptr, stream_ptr,
+                     check_wait_error, dtype_code, host_device_pointer, lib, lloyd_workspace, ptr,
+                     stream_ptr,
                      workspace_for)
 
 
@@ -55,19 +56,16 @@ def _weights_or_none(sample_weight, use_uniform_weights):
     return sample_weight
 
 
-def _read_status(status_dev, status_host):
-    status_host.copy_(status_dev, non_blocking=True)
-    torch.cuda.current_stream(status_dev.device).synchronize()
-    rec = status_host.numpy().view(STATUS_DTYPE)[0]
-    if int(rec["wait_error"]) != 0:
-        raise KmbError("a bounded wait inside the tcgen05 Lloyd kernel ran out; the results of "
-                       "this iteration are invalid")
-    return int(rec["n_empty"]), int(rec["changed"]), float(rec["shift_total"])
-
-
 class LloydState:
-    """Buffers and one-iteration step of the Lloyd loop (kmeans/drivers.py:146-343 of the
-    reference allocates the same set once per call).  `step()` is what the benchmark times."""
+    """Buffers and iterations of the Lloyd loop (kmeans/drivers.py:146-343 of the reference
+    allocates the same set once per call).
+
+    Iteration `it` reads the centroids in slot it % 3 and the labels of iteration it - 1, and
+    writes the labels, the merged sums, the empty list and the status record of slot it % 2 and
+    the centroids of slot (it + 1) % 3.  The extra slots let `run()` enqueue iteration it + 1
+    before the status of iteration `it` has been read: when that status asks for a relocation
+    (or ends the loop) everything iteration `it` produced is still in place.  `C`, `labels`,
+    `packed`, ... name the slots of the current iteration `self.it`."""
 
     def __init__(self, X, sample_weight, centers, algo=ALGO_AUTO):
         n, d = X.shape
@@ -96,22 +94,25 @@ class LloydState:
         self.n, self.d, self.k = n, d, k
         self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, want, n_policy, d, k),
                           "kmb_lloyd_resolve_algo")
+        self.is_tc = self.algo == ALGO_NAMES["tf32x3"]
         self.acc_len = lib.kmb_lloyd_acc_len(d, k)
         self.n_copies = check(lib.kmb_lloyd_acc_copies(self.dtype, self.algo, n, d, k))
-        self.C = centers.contiguous().clone()
-        self.C_new = torch.empty_like(self.C)
-        self.h = torch.empty(k, dtype=dt, device=dev)
-        self.h_new = torch.empty(k, dtype=dt, device=dev)
+        self.it = 0                              # iterations completed so far
+        self._Cs = [centers.contiguous().clone()] + [torch.empty((k, d), dtype=dt, device=dev)
+                                                     for _ in range(2)]
+        self._hs = [torch.empty(k, dtype=dt, device=dev) for _ in range(3)]
+        self._labs = [torch.empty(n, dtype=torch.int32, device=dev) for _ in range(2)]
+        self._packs = [torch.empty(self.acc_len, dtype=dt, device=dev) for _ in range(2)]
+        self._empties = [torch.empty(k, dtype=torch.int32, device=dev) for _ in range(2)]
         self.shifts = torch.empty(k, dtype=dt, device=dev)
-        self.labels = torch.empty(n, dtype=torch.int32, device=dev)
-        self.labels_new = torch.empty(n, dtype=torch.int32, device=dev)
         # The copies start at zero and every finalize (or merge) clears them again once read,
         # so no step has to clear them.
         self.acc = torch.zeros((self.n_copies, self.acc_len), dtype=dt, device=dev)
-        self.packed = torch.empty(self.acc_len, dtype=dt, device=dev)
-        self.empty_list = torch.empty(k, dtype=torch.int32, device=dev)
-        self.status_dev = torch.empty(32, dtype=torch.uint8, device=dev)
-        self.status_host = torch.empty(32, dtype=torch.uint8).pin_memory()
+        # Status records: page-locked host memory that the finalize kernel writes directly (no
+        # copy to enqueue), one record per slot, each followed on the stream by an event.
+        self._status = torch.zeros((2, 32), dtype=torch.uint8).pin_memory()
+        self._status_ptrs = [host_device_pointer(self._status[i]) for i in range(2)]
+        self._events = [torch.cuda.Event() for _ in range(2)]
         # A workspace of this state's own: the tensor-core operands that a finalize writes for
         # the next step, and the sticky time-out flag, live there between calls.  The row-scan
         # calls of this state (inertia, top-k) use the shared scratch buffer instead.
@@ -119,54 +120,104 @@ class LloydState:
         self.scratch, self.scratch_bytes = workspace_for(dev, n, d, k)
         self.sq_dist = None
         self.have_prev = False
-        self.operands_ready = False
+        self._operands_slot = None               # centroid slot whose split operands sit in ws
         self.kernel_launches = 0
-        self.is_tc = self.algo == ALGO_NAMES["tf32x3"]
+        self.event_hook = None                   # callable(kind, it) around the fused kernel
         check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
               "kmb_half_l2_norm")
         self.kernel_launches += 1
 
+    # -- the slots of the current iteration -------------------------------------------
+    C = property(lambda self: self._Cs[self.it % 3])
+    C_new = property(lambda self: self._Cs[(self.it + 1) % 3])
+    h = property(lambda self: self._hs[self.it % 3])
+    h_new = property(lambda self: self._hs[(self.it + 1) % 3])
+    labels = property(lambda self: self._labs[(self.it + 1) % 2])       # of iteration it - 1
+    labels_new = property(lambda self: self._labs[self.it % 2])
+    packed = property(lambda self: self._packs[self.it % 2])
+    empty_list = property(lambda self: self._empties[self.it % 2])
+    status_dev = property(lambda self: self._status[self.it % 2])
+    status_host = property(lambda self: self._status[(self.it + 1) % 2])   # last finished iteration
+    packed_last = property(lambda self: self._packs[(self.it + 1) % 2])    # last finished iteration
+
+    @property
+    def operands_ready(self):
+        return self.is_tc and self._operands_slot == self.it % 3
+
+    @operands_ready.setter
+    def operands_ready(self, value):
+        self._operands_slot = (self.it % 3) if value else None
+
     # -- pieces -----------------------------------------------------------------------
-    def _finalize(self, merge, clear):
+    def _finalize(self, it, merge, clear):
         """One kernel: (merge of the copies,) division, shifts, next half norms, operands of
-        the next tensor-core step, empty list, status record."""
+        the next tensor-core step, empty list, status record of iteration `it`."""
         flags = (FIN_MERGE if merge else 0) | (FIN_CLEAR_ACC if clear else 0) | \
             (FIN_PREPARE_TF32X3 if self.is_tc else 0)
-        check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.acc), self.n_copies, ptr(self.packed),
-                                     flags, ptr(self.C), ptr(self.C_new), ptr(self.h_new),
-                                     ptr(self.shifts), ptr(self.empty_list), ptr(self.status_dev),
-                                     self.k, self.d, ptr(self.ws), self.ws_bytes,
-                                     stream_ptr(self.X.device)), "kmb_lloyd_finalize")
+        dev = self.X.device
+        check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.acc), self.n_copies,
+                                     ptr(self._packs[it % 2]), flags, ptr(self._Cs[it % 3]),
+                                     ptr(self._Cs[(it + 1) % 3]), ptr(self._hs[(it + 1) % 3]),
+                                     ptr(self.shifts), ptr(self._empties[it % 2]),
+                                     self._status_ptrs[it % 2], self.k, self.d, ptr(self.ws),
+                                     self.ws_bytes, stream_ptr(dev)), "kmb_lloyd_finalize")
+        self._events[it % 2].record(torch.cuda.current_stream(dev))
         self.kernel_launches += 1
+        self._operands_slot = (it + 1) % 3 if self.is_tc else None
 
-    def launch_fused_step(self):
-        """The fused kernel alone: labels of the new assignment and the accumulator copies."""
-        flags = STEP_ACC_CLEARED | (STEP_OPERANDS_READY if self.operands_ready else 0)
-        check(lib.kmb_lloyd_step(self.dtype, self.algo, ptr(self.X), ptr(self.w), ptr(self.C),
-                                 ptr(self.h), ptr(self.labels) if self.have_prev else None,
-                                 ptr(self.labels_new), ptr(self.acc), self.n_copies, self.n,
+    def _launch_fused(self, it):
+        """The fused kernel of iteration `it`: its labels and the accumulator copies."""
+        ready = self.is_tc and self._operands_slot == it % 3
+        flags = STEP_ACC_CLEARED | (STEP_OPERANDS_READY if ready else 0)
+        prev = self._labs[(it + 1) % 2] if (self.have_prev or it > 0) else None
+        if self.event_hook is not None:
+            self.event_hook("pre", it)
+        check(lib.kmb_lloyd_step(self.dtype, self.algo, ptr(self.X), ptr(self.w),
+                                 ptr(self._Cs[it % 3]), ptr(self._hs[it % 3]), ptr(prev),
+                                 ptr(self._labs[it % 2]), ptr(self.acc), self.n_copies, self.n,
                                  self.d, self.k, flags, ptr(self.ws), self.ws_bytes,
                                  stream_ptr(self.X.device)), "kmb_lloyd_step")
-        self.kernel_launches += 1 + (1 if self.is_tc and not self.operands_ready else 0)
+        if self.event_hook is not None:
+            self.event_hook("post", it)
+        self.kernel_launches += 1 + (1 if self.is_tc and not ready else 0)
 
-    def launch_reduce_finalize(self):
-        """Everything of an iteration after the fused kernel, enqueued without a host read:
+    def _launch_reduce_finalize(self, it):
+        """Everything of iteration `it` after the fused kernel, enqueued without a host read:
         one kernel on one GPU; merge, all-reduce, finalize over row shards."""
         if dist.active():
             check(lib.kmb_lloyd_merge_copies(self.dtype, ptr(self.acc), self.n_copies,
-                                             self.acc_len, ptr(self.packed), 1,
+                                             self.acc_len, ptr(self._packs[it % 2]), 1,
                                              stream_ptr(self.X.device)), "kmb_lloyd_merge_copies")
             self.kernel_launches += 1
-            dist.all_reduce_sum_(self.packed)
-            self._finalize(merge=False, clear=False)
+            dist.all_reduce_sum_(self._packs[it % 2])
+            self._finalize(it, merge=False, clear=False)
         else:
-            self._finalize(merge=True, clear=True)
-        self.operands_ready = self.is_tc
+            self._finalize(it, merge=True, clear=True)
+
+    def _launch(self, it):
+        self._launch_fused(it)
+        self._launch_reduce_finalize(it)
+
+    def launch_fused_step(self):
+        self._launch_fused(self.it)
+
+    def launch_reduce_finalize(self):
+        self._launch_reduce_finalize(self.it)
 
     def launch_step(self):
-        """E-step + accumulation + reduction + finalize, all enqueued (no host read)."""
-        self.launch_fused_step()
-        self.launch_reduce_finalize()
+        """E-step + accumulation + reduction + finalize of the current iteration, all enqueued
+        (no host read)."""
+        self._launch(self.it)
+
+    def _wait_status(self, it):
+        """Waits for the status record of iteration `it`: (n_empty, changed, shift_total)."""
+        self._events[it % 2].synchronize()
+        rec = self._status[it % 2].numpy().view(STATUS_DTYPE)[0]
+        if int(rec["wait_error"]) != 0:
+            self._operands_slot = None
+            raise KmbError("a bounded wait inside the tcgen05 Lloyd kernel ran out; the results "
+                           "of this iteration are invalid")
+        return int(rec["n_empty"]), int(rec["changed"]), float(rec["shift_total"])
 
     def _relocate(self, n_empty):
         """kmeans/drivers.py:238-272 and 396-433 of the reference.  The distances that rank
@@ -192,7 +243,7 @@ class LloydState:
                                               ptr(self.packed), self.d, self.k, stream_ptr(dev)),
               "kmb_relocate_empty_clusters")
         self.kernel_launches += 2
-        self._finalize(merge=False, clear=False)
+        self._finalize(self.it, merge=False, clear=False)
 
     def inertia_against_sums(self):
         """What the reference prints per iteration when verbose: the weighted inertia of the
@@ -209,40 +260,84 @@ class LloydState:
         return float(total[0])
 
     def step(self, before_relocation=None):
-        """One Lloyd iteration.  Returns (n_empty_before_relocation, changed, shift_total).
-        `before_relocation`, when given, is called once the merged sums and the new labels
-        exist and before empty clusters are relocated."""
-        self.launch_step()
-        try:
-            n_empty, changed, shift = _read_status(self.status_dev, self.status_host)
-        except KmbError:
-            self.operands_ready = False     # the buffers were not swapped: C_new's operands are not C's
-            raise
+        """One Lloyd iteration, start to finish.  Returns (n_empty_before_relocation, changed,
+        shift_total).  `before_relocation`, when given, is called once the merged sums and the
+        new labels exist and before empty clusters are relocated."""
+        self._launch(self.it)
+        n_empty, changed, shift = self._wait_status(self.it)
         if before_relocation is not None:
             before_relocation(self)
         if n_empty > 0:
             self._relocate(n_empty)
-            _, _, shift = _read_status(self.status_dev, self.status_host)
-        self.C, self.C_new = self.C_new, self.C
-        self.h, self.h_new = self.h_new, self.h
-        self.labels, self.labels_new = self.labels_new, self.labels
-        self.have_prev = True
+            _, _, shift = self._wait_status(self.it)
+        self.it += 1
         return n_empty, changed, shift
+
+    def run(self, max_iter, tol=0.0, before_relocation=None, pipelined=True, stop_on_strict=True):
+        """The loop of `lloyd` (kmeans/drivers.py:188-343 of the reference) from the current
+        state: iterates until max_iter, a total shift <= tol, or strict convergence (labels
+        unchanged, armed after the second iteration as in the reference).  Returns a dict with
+        n_iter, strict, shift, n_relocation_events, n_empty_max.
+
+        Pipelined: iteration i + 1 is enqueued BEFORE the status of iteration i is read, so the
+        GPU never idles while the host decides; it is run again only when iteration i had to
+        relocate empty clusters, and simply ignored when iteration i ended the loop.  With a
+        callback (verbose mode) the loop runs unpipelined.  `stop_on_strict=False` keeps iterating
+        after the labels have stopped changing (the benchmark times a fixed number of steps)."""
+        T = np.float32 if self.X.dtype == torch.float32 else np.float64
+        pipelined = bool(pipelined) and before_relocation is None
+        n_iter, shift, armed, strict = 0, np.inf, False, False
+        events, n_empty_max = 0, 0
+        launched = False                          # iteration self.it is already in flight
+        while n_iter < max_iter and shift > tol:
+            if not launched:
+                self._launch(self.it)
+            launched = False
+            speculate = pipelined and n_iter + 1 < max_iter
+            if speculate:
+                self._launch(self.it + 1)
+            n_empty, changed, shift_total = self._wait_status(self.it)
+            if before_relocation is not None:
+                before_relocation(self)
+            if n_empty > 0:
+                # (the speculative iteration ran from centroids that are about to change)
+                self._relocate(n_empty)
+                _, _, shift_total = self._wait_status(self.it)
+                speculate = False
+            events += int(n_empty > 0)
+            n_empty_max = max(n_empty_max, n_empty)
+            self.it += 1
+            launched = speculate
+            n_iter += 1
+            if n_iter > 1:
+                if armed and changed == 0 and stop_on_strict:
+                    strict = True
+                    break
+                armed = True
+            shift = T(shift_total)
+        if launched:
+            # an iteration in flight that the loop did not need: let it finish (it wrote only
+            # slots of its own and the operands of centroids nobody will use) and forget it
+            self._events[self.it % 2].synchronize()
+            self._operands_slot = None
+        return dict(n_iter=n_iter, strict=strict, shift=shift, n_relocation_events=events,
+                    n_empty_max=n_empty_max)
 
     def final_labels_inertia(self):
         dev = self.X.device
+        labels = self._labs[self.it % 2]          # free: the next iteration would write it
         check(lib.kmb_assign_labels(self.dtype, self.algo, ptr(self.X), ptr(self.C), ptr(self.h),
-                                    ptr(self.labels), self.n, self.d, self.k, ptr(self.ws),
+                                    ptr(labels), self.n, self.d, self.k, ptr(self.ws),
                                     self.ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
-        self.operands_ready = False
+        self._operands_slot = (self.it % 3) if self.is_tc else None
         total = torch.empty(1, dtype=self.X.dtype, device=dev)
-        check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.C), ptr(self.labels),
+        check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.C), ptr(labels),
                               None, ptr(total), self.n, self.d, self.k, ptr(self.scratch),
                               self.scratch_bytes, stream_ptr(dev)), "kmb_inertia")
         self.kernel_launches += 3 + (1 if self.is_tc else 0)
         dist.all_reduce_sum_(total)
         self.check_device_waits()
-        return self.labels, total
+        return labels, total
 
     def centers(self):
         """Current centroids (k, d) without the padding features, contiguous."""
@@ -312,26 +407,16 @@ def lloyd(X_t, sample_weight, centroids_t, use_uniform_weights, max_iter=300, ve
         dist.check_same_across_ranks(d=state.d, k=state.k, dtype=str(X.dtype),
                                      max_iter=int(max_iter), tol=float(tol))
 
-    n_iteration = 0
-    shift = np.inf
-    armed = False
-    strict = False
     verbose = bool(verbose)
-    n_reloc_events, n_empty_max = 0, 0
-    while n_iteration < max_iter and shift > tol:
-        def report(st, it=n_iteration):
-            print(f"Iteration {it}, inertia {st.inertia_against_sums():5.3e}")
+    counter = {"it": 0}
 
-        n_empty, changed, shift_total = state.step(report if verbose else None)
-        n_reloc_events += int(n_empty > 0)
-        n_empty_max = max(n_empty_max, n_empty)
-        n_iteration += 1
-        if n_iteration > 1:
-            if armed and changed == 0:
-                strict = True
-                break
-            armed = True
-        shift = T(shift_total)
+    def report(st):
+        print(f"Iteration {counter['it']}, inertia {st.inertia_against_sums():5.3e}")
+        counter["it"] += 1
+
+    out = state.run(int(max_iter), tol, before_relocation=report if verbose else None)
+    n_iteration, strict, shift = out["n_iter"], out["strict"], out["shift"]
+    n_reloc_events, n_empty_max = out["n_relocation_events"], out["n_empty_max"]
 
     if verbose:
         converged_at = n_iteration - 1

@@ -399,3 +399,56 @@ def test_wait_error_flag_is_sticky_and_reaches_the_status_record():
     st.check_device_waits()
     st.step()                                     # usable again
     check_wait_error(st.ws, st.X.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(3000, 5, 12), (40_000, 16, 130)], ids=lambda s: "n%d_d%d_k%d" % s)
+def test_pipelined_loop_equals_step_by_step(dtype, shape):
+    """`LloydState.run` enqueues iteration i + 1 before it has read the status of iteration i.
+    On data whose first iterations relocate empty clusters (duplicated initial centres) and
+    that then converges strictly, the pipelined loop must take the same decisions and end in
+    the same state as the loop that reads every status first, and as the CPU oracle."""
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    n, d, k = shape
+    rng = np.random.default_rng(n + k)
+    X, _ = _blobs(rng, n, d, k, dtype, std=0.3)
+    C = X[rng.choice(n, size=k, replace=False)].copy()
+    C[1] = C[0]
+    C[k - 1] = C[2]                       # two clusters start empty -> relocation in iteration 1
+    w = np.ones(n, dtype=dtype)
+    results = []
+    for pipelined in (True, False):
+        st = LloydState(_dev(X), None, _dev(C), "auto")
+        out = st.run(40, 0.0, pipelined=pipelined)
+        labels, total = st.final_labels_inertia()
+        results.append((out, labels.cpu().numpy(), st.centers().cpu().numpy(), float(total[0]), st.it))
+    (o1, l1, c1, i1, it1), (o2, l2, c2, i2, it2) = results
+    assert o1["n_relocation_events"] >= 1 and o1["n_empty_max"] >= 2
+    assert (o1["n_iter"], o1["strict"], o1["n_relocation_events"]) == \
+        (o2["n_iter"], o2["strict"], o2["n_relocation_events"])
+    assert it1 == it2 == o1["n_iter"]
+    assert o1["strict"] and 3 <= o1["n_iter"] < 40
+    assert_array_equal(l1, l2)
+    assert_allclose(c1, c2, rtol=RTOL[dtype] * 10, atol=RTOL[dtype] * 10)
+    assert_allclose(i1, i2, rtol=RTOL[dtype] * 10)
+    o_labels, o_inertia, o_C, o_iter = ref.lloyd(X, w, C, True, 40, False, 0.0)
+    assert o_iter == o1["n_iter"]
+    ok, n_bad, n_unexplained = ref.labels_agree(l1, o_labels, X, o_C)
+    assert ok, (n_bad, n_unexplained)
+    assert_allclose(i1, float(o_inertia), rtol=1e-4 if dtype == np.float32 else 1e-9)
+
+
+def test_run_can_ignore_strict_convergence_and_counts_steps():
+    from sklearn_numba_dpex_b200.kmeans.drivers import LloydState
+
+    rng = np.random.default_rng(2)
+    X, _ = _blobs(rng, 2000, 4, 5, np.float32, std=0.2)
+    st = LloydState(_dev(X), None, _dev(X[:5].copy()), "auto")
+    out = st.run(25, -1.0, stop_on_strict=False)
+    assert out["n_iter"] == 25 and st.it == 25 and not out["strict"]
+    seen = []
+    st.event_hook = lambda kind, it: seen.append((kind, it))
+    st.run(3, -1.0, stop_on_strict=False)
+    st.event_hook = None
+    assert seen == [("pre", 25), ("post", 25), ("pre", 26), ("post", 26), ("pre", 27), ("post", 27)]
