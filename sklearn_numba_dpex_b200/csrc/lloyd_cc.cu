@@ -321,10 +321,21 @@ int launch_lloyd_cc(const CcArgs<T>& args_in, cudaStream_t stream) {
   return KMB_OK;
 }
 
+// float64 on the double-precision MMA path (lloyd_f64.cu)
+bool lloyd_f64_mma_enabled();
+int lloyd_f64_step(const double* X, const double* w, const double* C, const double* h,
+                   const uint32_t* prev, uint32_t* labels, double* acc, int n_copies,
+                   int64_t acc_len, int64_t n, int d, int k, cudaStream_t stream);
+int lloyd_f64_assign(const double* X, const double* C, const double* h, uint32_t* labels, int64_t n,
+                     int d, int k, cudaStream_t stream);
+
 // Entry points used by lloyd_api.cu
 int lloyd_cc_step(int dtype, const void* X, const void* w, const void* C, const void* h,
                   const uint32_t* prev, uint32_t* labels, void* acc, int n_copies,
                   int64_t acc_len, int64_t n, int d, int k, cudaStream_t stream) {
+  if (dtype == KMB_F64 && lloyd_f64_mma_enabled())
+    return lloyd_f64_step((const double*)X, (const double*)w, (const double*)C, (const double*)h, prev,
+                          labels, (double*)acc, n_copies, acc_len, n, d, k, stream);
   KMB_DISPATCH_DTYPE(dtype, {
     CcArgs<T> a{(const T*)X, (const T*)w, (const T*)C, (const T*)h, prev, labels, (T*)acc,
                 n_copies, acc_len, n, d, k, 0, 0, 1, 1};
@@ -334,6 +345,9 @@ int lloyd_cc_step(int dtype, const void* X, const void* w, const void* C, const 
 
 int lloyd_cc_assign(int dtype, const void* X, const void* C, const void* h, uint32_t* labels,
                     int64_t n, int d, int k, cudaStream_t stream) {
+  if (dtype == KMB_F64 && lloyd_f64_mma_enabled())
+    return lloyd_f64_assign((const double*)X, (const double*)C, (const double*)h, labels, n, d, k,
+                            stream);
   KMB_DISPATCH_DTYPE(dtype, {
     CcArgs<T> a{(const T*)X, nullptr, (const T*)C, (const T*)h, nullptr, labels, nullptr,
                 1, 0, n, d, k, 0, 0, 1, 1};
