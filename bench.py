@@ -394,22 +394,20 @@ def run_gpu_arm(args, cfg):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
-    def around_fused_kernel(kind, it):
-        # events around the fused kernel of every timed iteration (iterations that the
-        # pipelined loop enqueues ahead and never uses fall outside the list)
-        i = it - it0
-        if 0 <= i < args.steps:
-            kev[i][0 if kind == "pre" else 1].record()
-
+    # events around the fused kernel of every timed iteration (created ahead: the launch call
+    # records them by handle)
     it0 = state.it
-    state.event_hook = around_fused_kernel
+    for a, b in kev:
+        a.record()
+        b.record()
+    state.step_events = {it0 + i: kev[i] for i in range(args.steps)}
     t_begin = time.time()
     ev0.record()
     out = state.run(args.steps, -1.0, pipelined=not args.no_pipeline, stop_on_strict=False)
     ev1.record()
     barrier()
     t_end = time.time()
-    state.event_hook = None
+    state.step_events = {}
     steps_run = out["n_iter"]
     assert steps_run == args.steps, (steps_run, args.steps)
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None

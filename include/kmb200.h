@@ -154,6 +154,41 @@ int kmb_lloyd_finalize(int dtype, void* acc, int n_copies, void* merged, int fla
                        uint32_t* empty_list, kmb_lloyd_status* status, int k, int d,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* One whole single-GPU iteration in one call, for hosts whose per-call overhead matters (a
+ * Python loop on a 30 us kernel): the buffers of the loop are described ONCE in a plan, and
+ * kmb_lloyd_plan_launch(plan, it, ...) enqueues iteration `it` on them: kmb_lloyd_step reading
+ * centroids C[it % 3], half norms h[it % 3] and previous labels labels[(it + 1) % 2], writing
+ * labels[it % 2]; then kmb_lloyd_finalize (merge + clear + operands of the next step) writing
+ * merged[it % 2], C[(it + 1) % 3], h[(it + 1) % 3], empty_list[it % 2] and status[it % 2].
+ * The three-deep centroid ring lets a caller enqueue iteration it + 1 before it has read the
+ * status of iteration it and still find everything iteration it produced.  `acc` must be zero
+ * before the first launch (every launch leaves it zero again).  flags: KMB_PLAN_HAVE_PREV when
+ * labels[(it + 1) % 2] hold previous labels, KMB_PLAN_OPERANDS_READY as KMB_STEP_OPERANDS_READY.
+ * The three events (cudaEvent_t as void*, each may be NULL) are recorded before the fused
+ * kernel, after it, and after the finalize kernel.  The caller owns the plan's memory; the
+ * library keeps no reference to it after the call returns.  No counterpart in the reference,
+ * whose loop issues one Python call per kernel (kmeans/drivers.py:188-343). */
+typedef struct {
+  int32_t dtype, algo;              /* algo resolved: KMB_ALGO_CUDA_CORE or KMB_ALGO_TF32X3 */
+  int32_t d, k, n_copies, reserved;
+  int64_t n;
+  const void* X;
+  const void* w;                    /* may be NULL */
+  void* C[3];
+  void* h[3];
+  uint32_t* labels[2];
+  void* acc;
+  void* merged[2];
+  void* shifts;
+  uint32_t* empty_list[2];
+  kmb_lloyd_status* status[2];
+  void* workspace;
+  size_t workspace_bytes;
+} kmb_lloyd_plan;
+enum { KMB_PLAN_HAVE_PREV = 1, KMB_PLAN_OPERANDS_READY = 2 };
+int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, void* event_before_step,
+                          void* event_after_step, void* event_done, void* stream);
+
 /* labels only.  Replaces make_label_assignment_fixed_window_kernel,
  * sklearn_numba_dpex/kmeans/kernels/compute_labels.py:19-185. */
 int kmb_assign_labels(int dtype, int algo, const void* X, const void* C,

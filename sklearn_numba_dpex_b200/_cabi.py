@@ -86,6 +86,19 @@ _SIGNATURES = {
     "kmb_matmul_nt": (c_int, [c_int, c_int, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t, _P]),
 }
 
+class LloydPlan(ctypes.Structure):
+    """kmb_lloyd_plan of include/kmb200.h."""
+    _fields_ = [("dtype", c_int32), ("algo", c_int32), ("d", c_int32), ("k", c_int32),
+                ("n_copies", c_int32), ("reserved", c_int32), ("n", c_int64),
+                ("X", c_void_p), ("w", c_void_p), ("C", c_void_p * 3), ("h", c_void_p * 3),
+                ("labels", c_void_p * 2), ("acc", c_void_p), ("merged", c_void_p * 2),
+                ("shifts", c_void_p), ("empty_list", c_void_p * 2), ("status", c_void_p * 2),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+
+
+_SIGNATURES["kmb_lloyd_plan_launch"] = (c_int, [POINTER(LloydPlan), c_int64, c_int, _P, _P, _P, _P])
+PLAN_HAVE_PREV, PLAN_OPERANDS_READY = 1, 2
+
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
 for _name, (_res, _args) in _SIGNATURES.items():

@@ -119,4 +119,52 @@ int cc_vec_width(const void* base, int d) {
   return 1;
 }
 
+// ---- atomics-free centroid update through owner groups ------------------------------------
+// The clusters are dealt out to NG groups of G lanes (cluster j belongs to group j % NG); every
+// row of the tile is on the list of the group that owns its label, and a group adds its rows
+// into its own clusters' sums: no two groups ever touch the same sum, so plain shared-memory
+// loads and stores do.  A lane serves 4 consecutive features; rows are taken two at a time so
+// that the global loads of both are in flight together (the loads are the latency of the loop).
+constexpr int CC_MAX_GROUPS = 64;
+
+__host__ __device__ inline int owner_group_lanes(int d) {
+  int G = 4;
+  while (G * 4 < d && G < 32) G <<= 1;
+  return G;
+}
+
+template <typename T>
+__device__ __forceinline__ void owner_group_update(T* __restrict__ ssum, const T* __restrict__ xt,
+                                                   const T* __restrict__ wt,
+                                                   const uint32_t* __restrict__ lab_s,
+                                                   const unsigned char* __restrict__ rows, int cnt,
+                                                   int d, int k, int G, int gl) {
+  for (int i = 0; i < cnt; i += 2) {
+    const bool two = i + 1 < cnt;
+    const int r0 = rows[i], r1 = two ? rows[i + 1] : r0;
+    const uint32_t l0 = lab_s[r0], l1 = lab_s[r1];
+    const T w0 = wt ? wt[r0] : T(1), w1 = wt ? wt[r1] : T(1);
+    for (int f = gl * 4; f < d; f += G * 4) {
+      T x0[4], x1[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x0[e] = (f + e < d) ? xt[(int64_t)r0 * d + f + e] : T(0);
+        x1[e] = (two && f + e < d) ? xt[(int64_t)r1 * d + f + e] : T(0);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (f + e < d) ssum[l0 * d + f + e] += x0[e] * w0;
+      if (two) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (f + e < d) ssum[l1 * d + f + e] += x1[e] * w1;
+      }
+    }
+    if (gl == 0) {
+      ssum[k * d + l0] += w0;
+      if (two) ssum[k * d + l1] += w1;
+    }
+  }
+}
+
 }  // namespace kmb

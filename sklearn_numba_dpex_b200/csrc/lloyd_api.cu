@@ -93,6 +93,34 @@ int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void
                        d, k, (cudaStream_t)stream);
 }
 
+int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, void* event_before_step,
+                          void* event_after_step, void* event_done, void* stream) {
+  KMB_REQUIRE(plan != nullptr && it >= 0, "kmb_lloyd_plan_launch: bad arguments");
+  KMB_REQUIRE((flags & ~(KMB_PLAN_HAVE_PREV | KMB_PLAN_OPERANDS_READY)) == 0,
+              "kmb_lloyd_plan_launch: unknown flag bits %d", flags);
+  KMB_REQUIRE(plan->algo == KMB_ALGO_CUDA_CORE || plan->algo == KMB_ALGO_TF32X3,
+              "kmb_lloyd_plan_launch: the plan must hold a resolved algo");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int c = (int)(it % 3), cn = (int)((it + 1) % 3), l = (int)(it % 2), lp = (int)((it + 1) % 2);
+  const bool tc = plan->algo == KMB_ALGO_TF32X3;
+  if (event_before_step) KMB_CHECK_CUDA(cudaEventRecord((cudaEvent_t)event_before_step, s));
+  int rc = kmb_lloyd_step(plan->dtype, plan->algo, plan->X, plan->w, plan->C[c], plan->h[c],
+                          (flags & KMB_PLAN_HAVE_PREV) ? plan->labels[lp] : nullptr, plan->labels[l],
+                          plan->acc, plan->n_copies, plan->n, plan->d, plan->k,
+                          KMB_STEP_ACC_CLEARED | ((flags & KMB_PLAN_OPERANDS_READY) ? KMB_STEP_OPERANDS_READY : 0),
+                          plan->workspace, plan->workspace_bytes, stream);
+  if (rc != KMB_OK) return rc;
+  if (event_after_step) KMB_CHECK_CUDA(cudaEventRecord((cudaEvent_t)event_after_step, s));
+  rc = kmb_lloyd_finalize(plan->dtype, plan->acc, plan->n_copies, plan->merged[l],
+                          KMB_FIN_MERGE | KMB_FIN_CLEAR_ACC | (tc ? KMB_FIN_PREPARE_TF32X3 : 0),
+                          plan->C[c], plan->C[cn], plan->h[cn], plan->shifts, plan->empty_list[l],
+                          plan->status[l], plan->k, plan->d, plan->workspace, plan->workspace_bytes,
+                          stream);
+  if (rc != KMB_OK) return rc;
+  if (event_done) KMB_CHECK_CUDA(cudaEventRecord((cudaEvent_t)event_done, s));
+  return KMB_OK;
+}
+
 int kmb_assign_labels(int dtype, int algo, const void* X, const void* C, const void* half_norms,
                       uint32_t* labels, int64_t n, int d, int k, void* workspace,
                       size_t workspace_bytes, void* stream) {

@@ -32,7 +32,6 @@ namespace kmb {
 constexpr size_t CC_PRIV_SMEM_MAX = 64 * 1024;
 // Largest centroid set (bytes, padded to whole tiles and chunks) kept resident in shared memory.
 constexpr size_t CC_RES_SMEM_MAX = 32 * 1024;
-constexpr int CC_MAX_GROUPS = 64;      // owner groups of the update: 8 warps x at most 8 per warp
 
 template <typename T>
 struct CcArgs {
@@ -108,8 +107,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_cc_kernel(CcArgs<T> a) {
   unsigned my_changed = 0;
 
   // update geometry: groups of G lanes, group og owns the clusters j with j % NG == og
-  int G = 4;
-  while (G < d && G < 32) G <<= 1;
+  const int G = owner_group_lanes(d);
   const int NG = (CC_THREADS / 32) * (32 / G);
   const int og = (tid >> 5) * (32 / G) + (tid & 31) / G;
   const int gl = (tid & 31) % G;
@@ -240,15 +238,8 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_cc_kernel(CcArgs<T> a) {
     if (UPDATE && a.smem_priv) {
       __syncthreads();
       // each owner group adds its rows into its own clusters: no other group touches them
-      const int cnt = grp_cnt[og];
-      const T* xt = a.X + m0 * (int64_t)d;
-      for (int i = 0; i < cnt; ++i) {
-        const int row = grp_rows[og * BM + i];
-        const uint32_t lab = lab_s[row];
-        const T wi = a.w ? a.w[m0 + row] : T(1);
-        for (int f = gl; f < d; f += G) ssum[lab * d + f] += xt[(int64_t)row * d + f] * wi;
-        if (gl == 0) ssum[k * d + lab] += wi;
-      }
+      owner_group_update<T>(ssum, a.X + m0 * (int64_t)d, a.w ? a.w + m0 : nullptr, lab_s,
+                            grp_rows + og * BM, grp_cnt[og], d, k, G, gl);
       __syncwarp();
       if (gl == 0) grp_cnt[og] = 0;     // next written after the barriers of the next tile
     } else if (UPDATE) {

@@ -32,7 +32,7 @@ namespace kmb {
 constexpr int F64_BM = 128, F64_BN = 64, F64_BK = 16, F64_LD = F64_BK + 4;
 constexpr size_t F64_PRIV_SMEM_MAX = 64 * 1024;
 constexpr size_t F64_RES_SMEM_MAX = 48 * 1024;
-constexpr int F64_MAX_GROUPS = 64;
+constexpr int F64_MAX_GROUPS = CC_MAX_GROUPS;
 
 struct F64Args {
   const double* X;
@@ -126,8 +126,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
   unsigned my_changed = 0;
 
   // update geometry: groups of G lanes, group og owns the clusters j with j % NG == og
-  int G = 4;
-  while (G < d && G < 32) G <<= 1;
+  const int G = owner_group_lanes(d);
   const int NG = (CC_THREADS / 32) * (32 / G);
   const int og = warp * (32 / G) + lane / G;
   const int gl = lane % G;
@@ -261,15 +260,8 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
     }
     if (UPDATE && a.smem_priv) {
       __syncthreads();
-      const int cnt = grp_cnt[og];
-      const double* xt = a.X + m0 * (int64_t)d;
-      for (int i = 0; i < cnt; ++i) {
-        const int row = grp_rows[og * BM + i];
-        const uint32_t lab = lab_s[row];
-        const double wi = a.w ? a.w[m0 + row] : 1.0;
-        for (int f = gl; f < d; f += G) ssum[lab * d + f] += xt[(int64_t)row * d + f] * wi;
-        if (gl == 0) ssum[k * d + lab] += wi;
-      }
+      owner_group_update<double>(ssum, a.X + m0 * (int64_t)d, a.w ? a.w + m0 : nullptr, lab_s,
+                                 grp_rows + og * BM, grp_cnt[og], d, k, G, gl);
       __syncwarp();
       if (gl == 0) grp_cnt[og] = 0;
     } else if (UPDATE) {

@@ -93,6 +93,7 @@ struct TcParams {
   int k;
   int k_pad;
   uint32_t sleep_ns;        // > 0: barrier waits may sleep this long between polls (see mbar_try_wait_sleep)
+  int round_lo;             // general kernel: round the low parts of the sample split (else truncated)
 };
 
 // ---------------------------------------------------------------------------- PTX
@@ -545,10 +546,15 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           // instead of letting it be truncated
           const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
           const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
-          hi[4 * c + 0] = __float_as_uint(h0); lo[4 * c + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
-          hi[4 * c + 1] = __float_as_uint(h1); lo[4 * c + 1] = __float_as_uint(tf32_round_alu(x.y - h1));
-          hi[4 * c + 2] = __float_as_uint(h2); lo[4 * c + 2] = __float_as_uint(tf32_round_alu(x.z - h2));
-          hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(tf32_round_alu(x.w - h3));
+          float l0 = x.x - h0, l1 = x.y - h1, l2 = x.z - h2, l3 = x.w - h3;
+          if (p.round_lo) {
+            l0 = tf32_round_alu(l0); l1 = tf32_round_alu(l1);
+            l2 = tf32_round_alu(l2); l3 = tf32_round_alu(l3);
+          }
+          hi[4 * c + 0] = __float_as_uint(h0); lo[4 * c + 0] = __float_as_uint(l0);
+          hi[4 * c + 1] = __float_as_uint(h1); lo[4 * c + 1] = __float_as_uint(l1);
+          hi[4 * c + 2] = __float_as_uint(h2); lo[4 * c + 2] = __float_as_uint(l2);
+          hi[4 * c + 3] = __float_as_uint(h3); lo[4 * c + 3] = __float_as_uint(l3);
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16) + kc * TC_KC;
         tmem_st32(lane_addr + hi_col, hi);
@@ -1124,6 +1130,17 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   }
 }
 
+}  // namespace kmb
+
+#include "lloyd_tc_teams.cuh"
+
+namespace kmb {
+
+static int tc_env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e != nullptr ? atoi(e) : dflt;
+}
+
 // KMB_TC_SLEEP_NS=<n> in the environment makes the barrier waits sleep up to n ns between
 // polls (A/B runs); the default polls without sleeping.
 static uint32_t tc_sleep_ns() {
@@ -1136,14 +1153,15 @@ static uint32_t tc_sleep_ns() {
   return (uint32_t)cached;
 }
 
-// Set KMB_TC_SMALL=0 in the environment to run short rows on the general kernel (A/B runs).
-static bool tc_small_disabled() {
+// Which kernel takes short rows: KMB_TC_SMALL=0 the general kernel, 1 the sixteen-worker kernel,
+// anything else (default) the two-team kernel (A/B runs).
+static int tc_small_mode() {
   static int cached = -1;
   if (cached < 0) {
     const char* e = getenv("KMB_TC_SMALL");
-    cached = (e != nullptr && e[0] == '0') ? 1 : 0;
+    cached = (e != nullptr && e[0] == '0') ? 0 : ((e != nullptr && e[0] == '1') ? 1 : 2);
   }
-  return cached == 1;
+  return cached;
 }
 
 // Centroids -> zero-padded hi / lo parts (both rounded to tf32) and +inf-padded half norms.
@@ -1275,12 +1293,22 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.dots = dots; p.error_flag = &ws.ctl->wait_error; p.acc_len = acc_len; p.n = n; p.ldd = ldd;
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
   p.sleep_ns = tc_sleep_ns();
+  p.round_lo = tc_env_int("KMB_TC_ROUND_LO", 1);
 
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
-  if (fold && d_pad == TC_KC && !tc_small_disabled()) {
-    // short rows: the kernel with sixteen epilogue warps
+  if (fold && d_pad == TC_KC && tc_small_mode() == 2) {
+    // short rows: two teams of eight epilogue warps, alternate sample tiles
+    const size_t smem = sizeof(TtSmem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_teams_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_teams_kernel<<<(unsigned)grid, TT_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+    KMB_CHECK_LAUNCH();
+    return KMB_OK;
+  }
+  if (fold && d_pad == TC_KC && tc_small_mode() == 1) {
+    // short rows: the kernel with sixteen epilogue warps on every tile
     const size_t smem = sizeof(TsSmem) + 1024;
     KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));

@@ -16,7 +16,8 @@ import numpy as np
 import torch
 
 from .. import dist
-from .._cabi import (ALGO_AUTO, ALGO_NAMES, FIN_CLEAR_ACC, FIN_MERGE, FIN_PREPARE_TF32X3,
+from .._cabi import (ALGO_AUTO, ALGO_NAMES, FIN_CLEAR_ACC, FIN_MERGE, FIN_PREPARE_TF32X3, PLAN_HAVE_PREV,
+                     PLAN_OPERANDS_READY, LloydPlan,
                      STATUS_DTYPE, STEP_ACC_CLEARED, STEP_OPERANDS_READY, KmbError, c_void_p, check,
                      check_wait_error, dtype_code, host_device_pointer, lib, lloyd_workspace, ptr,
                      stream_ptr,
@@ -113,6 +114,11 @@ class LloydState:
         self._status = torch.zeros((2, 32), dtype=torch.uint8).pin_memory()
         self._status_ptrs = [host_device_pointer(self._status[i]) for i in range(2)]
         self._events = [torch.cuda.Event() for _ in range(2)]
+        for ev in self._events:
+            ev.record(torch.cuda.current_stream(dev))       # creates the handle
+        self._event_handles = [c_void_p(ev.cuda_event) for ev in self._events]
+        # iterations -> (event before, event after) the fused kernel, for callers that time it
+        self.step_events = {}
         # A workspace of this state's own: the tensor-core operands that a finalize writes for
         # the next step, and the sticky time-out flag, live there between calls.  The row-scan
         # calls of this state (inertia, top-k) use the shared scratch buffer instead.
@@ -126,6 +132,25 @@ class LloydState:
         check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
               "kmb_half_l2_norm")
         self.kernel_launches += 1
+        # The whole ring described once, so that a single-GPU iteration is ONE call into the
+        # library (kmb_lloyd_plan_launch) instead of one per kernel.
+        plan = LloydPlan()
+        plan.dtype, plan.algo, plan.d, plan.k = self.dtype, self.algo, d, k
+        plan.n_copies, plan.n = self.n_copies, n
+        plan.X = X.data_ptr()
+        plan.w = sample_weight.data_ptr() if sample_weight is not None else None
+        for i in range(3):
+            plan.C[i] = self._Cs[i].data_ptr()
+            plan.h[i] = self._hs[i].data_ptr()
+        for i in range(2):
+            plan.labels[i] = self._labs[i].data_ptr()
+            plan.merged[i] = self._packs[i].data_ptr()
+            plan.empty_list[i] = self._empties[i].data_ptr()
+            plan.status[i] = self._status_ptrs[i].value
+        plan.acc, plan.shifts = self.acc.data_ptr(), self.shifts.data_ptr()
+        plan.workspace, plan.workspace_bytes = self.ws.data_ptr(), self.ws_bytes
+        self._plan = plan
+        self._plan_ref = ctypes.byref(plan)
 
     # -- the slots of the current iteration -------------------------------------------
     C = property(lambda self: self._Cs[self.it % 3])
@@ -195,8 +220,22 @@ class LloydState:
             self._finalize(it, merge=True, clear=True)
 
     def _launch(self, it):
-        self._launch_fused(it)
-        self._launch_reduce_finalize(it)
+        """Enqueues iteration `it`: fused kernel, reduction, finalize."""
+        if dist.active() or self.event_hook is not None:
+            self._launch_fused(it)
+            self._launch_reduce_finalize(it)
+            return
+        ready = self.is_tc and self._operands_slot == it % 3
+        flags = (PLAN_HAVE_PREV if (self.have_prev or it > 0) else 0) | \
+            (PLAN_OPERANDS_READY if ready else 0)
+        ev = self.step_events.get(it)
+        stream = c_void_p(torch.cuda.current_stream(self.X.device).cuda_stream)
+        check(lib.kmb_lloyd_plan_launch(self._plan_ref, it, flags,
+                                        c_void_p(ev[0].cuda_event) if ev else None,
+                                        c_void_p(ev[1].cuda_event) if ev else None,
+                                        self._event_handles[it % 2], stream), "kmb_lloyd_plan_launch")
+        self.kernel_launches += 2 + (1 if self.is_tc and not ready else 0)
+        self._operands_slot = (it + 1) % 3 if self.is_tc else None
 
     def launch_fused_step(self):
         self._launch_fused(self.it)
