@@ -122,6 +122,9 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_cc_kernel(CcArgs<T> a) {
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const int64_t m0 = tile * BM;
     const int rows = (int)((n - m0 < BM) ? (n - m0) : BM);
+    // previous label of the row this thread will write: fetched now, compared after the argmin
+    uint32_t prev_lab = 0xffffffffu;
+    if (UPDATE && a.prev != nullptr && tid < rows) prev_lab = __ldg(a.prev + m0 + tid);
     const bool has_next = tile + gridDim.x < n_tiles;
     T best[TM];
     uint32_t bi[TM];
@@ -223,7 +226,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_cc_kernel(CcArgs<T> a) {
       const uint32_t lab = lab_s[tid];
       a.labels[m0 + tid] = lab;
       if (UPDATE) {
-        my_changed += (a.prev == nullptr) ? 1u : (a.prev[m0 + tid] != lab ? 1u : 0u);
+        my_changed += (prev_lab != lab) ? 1u : 0u;
         if (a.smem_priv) {
           // hand the row to the group that owns its cluster
           const int owner = (int)(lab % (uint32_t)NG);

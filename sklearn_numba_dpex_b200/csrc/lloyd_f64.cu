@@ -141,6 +141,9 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const int64_t m0 = tile * BM;
     const int rows = (int)((n - m0 < BM) ? (n - m0) : BM);
+    // previous label of the row this thread will write: fetched now, compared after the argmin
+    uint32_t prev_lab = 0xffffffffu;
+    if (UPDATE && a.prev != nullptr && tid < rows) prev_lab = __ldg(a.prev + m0 + tid);
     double best[4];
     uint32_t bi[4];
 #pragma unroll
@@ -247,7 +250,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
       const uint32_t lab = lab_s[tid];
       a.labels[m0 + tid] = lab;
       if (UPDATE) {
-        my_changed += (a.prev == nullptr) ? 1u : (a.prev[m0 + tid] != lab ? 1u : 0u);
+        my_changed += (prev_lab != lab) ? 1u : 0u;
         if (a.smem_priv) {
           const int owner = (int)(lab % (uint32_t)NG);
           const int pos = atomicAdd(&grp_cnt[owner], 1);

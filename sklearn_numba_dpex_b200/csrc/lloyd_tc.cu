@@ -1153,13 +1153,14 @@ static uint32_t tc_sleep_ns() {
   return (uint32_t)cached;
 }
 
-// Which kernel takes short rows: KMB_TC_SMALL=0 the general kernel, 1 the sixteen-worker kernel,
-// anything else (default) the two-team kernel (A/B runs).
+// Which kernel takes short rows: the sixteen-worker kernel (default, KMB_TC_SMALL=1); 0 selects
+// the general kernel, 2 the two-team kernel (A/B runs: on n = 5 M, d = 14, k = 256 the three
+// measured 0.56 ms, 0.77 ms and 0.62 ms per step).
 static int tc_small_mode() {
   static int cached = -1;
   if (cached < 0) {
     const char* e = getenv("KMB_TC_SMALL");
-    cached = (e != nullptr && e[0] == '0') ? 0 : ((e != nullptr && e[0] == '1') ? 1 : 2);
+    cached = (e != nullptr && e[0] == '0') ? 0 : ((e != nullptr && e[0] == '2') ? 2 : 1);
   }
   return cached;
 }
