@@ -123,9 +123,9 @@ int cc_vec_width(const void* base, int d) {
 // The clusters are dealt out to NG groups of G lanes (cluster j belongs to group j % NG); every
 // row of the tile is on the list of the group that owns its label, and a group adds its rows
 // into its own clusters' sums: no two groups ever touch the same sum, so plain shared-memory
-// loads and stores do.  A lane serves 4 features (strided by the group width); rows are taken
-// four at a time so that their global loads are in flight together (the loads are the latency
-// of the loop).
+// loads and stores do.  A lane serves 4 consecutive features; rows are taken two at a time so
+// that the global loads of both are in flight together (the loads are the latency of the loop;
+// four rows at a time with strided lanes measured 6 - 13 % slower).
 constexpr int CC_MAX_GROUPS = 64;
 
 __host__ __device__ inline int owner_group_lanes(int d) {
@@ -140,42 +140,30 @@ __device__ __forceinline__ void owner_group_update(T* __restrict__ ssum, const T
                                                    const uint32_t* __restrict__ lab_s,
                                                    const unsigned char* __restrict__ rows, int cnt,
                                                    int d, int k, int G, int gl) {
-  // lane gl serves features gl, gl + G, gl + 2 G, gl + 3 G of a block of 4 G features:
-  // consecutive lanes touch consecutive addresses (coalesced loads, conflict-free banks)
-  for (int i = 0; i < cnt; i += 4) {
-    int r[4];
-    uint32_t l[4];
-    T w[4];
+  for (int i = 0; i < cnt; i += 2) {
+    const bool two = i + 1 < cnt;
+    const int r0 = rows[i], r1 = two ? rows[i + 1] : r0;
+    const uint32_t l0 = lab_s[r0], l1 = lab_s[r1];
+    const T w0 = wt ? wt[r0] : T(1), w1 = wt ? wt[r1] : T(1);
+    for (int f = gl * 4; f < d; f += G * 4) {
+      T x0[4], x1[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      r[u] = rows[(i + u < cnt) ? i + u : i];
-      l[u] = lab_s[r[u]];
-      w[u] = wt ? wt[r[u]] : T(1);
-    }
-    for (int f0 = 0; f0 < d; f0 += G * 4) {
-      T x[4][4];
+      for (int e = 0; e < 4; ++e) {
+        x0[e] = (f + e < d) ? xt[(int64_t)r0 * d + f + e] : T(0);
+        x1[e] = (two && f + e < d) ? xt[(int64_t)r1 * d + f + e] : T(0);
+      }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int e = 0; e < 4; ++e)
+        if (f + e < d) ssum[l0 * d + f + e] += x0[e] * w0;
+      if (two) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int f = f0 + gl + e * G;
-          x[u][e] = (i + u < cnt && f < d) ? xt[(int64_t)r[u] * d + f] : T(0);
-        }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (i + u < cnt) {            // in list order: two rows of one cluster add one after the other
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int f = f0 + gl + e * G;
-            if (f < d) ssum[l[u] * d + f] += x[u][e] * w[u];
-          }
-        }
+        for (int e = 0; e < 4; ++e)
+          if (f + e < d) ssum[l1 * d + f + e] += x1[e] * w1;
       }
     }
     if (gl == 0) {
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i + u < cnt) ssum[k * d + l[u]] += w[u];
+      ssum[k * d + l0] += w0;
+      if (two) ssum[k * d + l1] += w1;
     }
   }
 }

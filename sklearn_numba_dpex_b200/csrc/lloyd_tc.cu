@@ -1133,6 +1133,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 }  // namespace kmb
 
 #include "lloyd_tc_teams.cuh"
+#include "lloyd_tc_quads.cuh"
 
 namespace kmb {
 
@@ -1160,7 +1161,7 @@ static int tc_small_mode() {
   static int cached = -1;
   if (cached < 0) {
     const char* e = getenv("KMB_TC_SMALL");
-    cached = (e != nullptr && e[0] == '0') ? 0 : ((e != nullptr && e[0] == '2') ? 2 : 1);
+    cached = (e == nullptr) ? 3 : ((e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3);
   }
   return cached;
 }
@@ -1299,6 +1300,15 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
+  if (fold && d_pad == TC_KC && tc_small_mode() == 3) {
+    // short rows: four quads, each owning whole sample tiles
+    const size_t smem = sizeof(TqSmem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_quads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_quads_kernel<<<(unsigned)grid, TQ_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+    KMB_CHECK_LAUNCH();
+    return KMB_OK;
+  }
   if (fold && d_pad == TC_KC && tc_small_mode() == 2) {
     // short rows: two teams of eight epilogue warps, alternate sample tiles
     const size_t smem = sizeof(TtSmem) + 1024;

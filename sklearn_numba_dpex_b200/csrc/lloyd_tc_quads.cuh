@@ -1,0 +1,321 @@
+// Short-row form of the tensor-core Lloyd step in which every sample tile belongs to ONE quad of
+// warps from start to finish.  Included by lloyd_tc.cu (PTX wrappers, TcParams, argmax32).
+//
+// Rows of at most 28 features (one 32-feature chunk including the two fold features, see
+// lloyd_tc_folds).  At this size the step is bound by the instructions of the epilogue warps, and
+// two thirds of those are per-tile bookkeeping that EVERY warp touching a tile repeats (barrier
+// waits, tensor-memory loads, label exchange, update addressing).  Here only four warps touch a
+// tile, and they never talk to each other:
+//   warp 0        TMA producer of the sample tiles (one slot per quad)
+//   warp 1        TMA producer of the centroid stages (resident when all of them fit)
+//   warps 2, 3    issue the MMAs in tile order, one accumulator buffer each
+//   warps 4 + 4 Q .. 7 + 4 Q   quad Q (Q = 0..3) owns the CTA's tiles t with t mod 4 = Q.  Warp lq of a
+//                 quad owns TMEM lanes 32 lq .. 32 lq + 31, i.e. ONE THREAD OWNS ONE SAMPLE ROW of
+//                 the tile: it splits the row into hi / lo parts in the quad's tensor-memory slot,
+//                 reduces ALL columns of every accumulator of the tile (32 at a time) to its
+//                 (score, index), writes the label, and adds its own row into the centroid sums
+//                 with 16-byte vector reductions.  No partial results, no label exchange.
+// Four tiles are in flight, one per quad, each at a different stage (split, MMA, argmax, update),
+// so the quads hide each other's latencies and spread the argmax bursts over time.
+// Tensor memory: sample slot of quad Q: hi at columns 64 Q, lo at 64 Q + 32 (256 columns);
+// accumulators at 256 and 384, used in turn by the global sequence of (tile, centroid tile).
+#pragma once
+
+namespace kmb {
+
+constexpr int TQ_WARPS = 20;
+constexpr int TQ_THREADS = TQ_WARPS * 32;
+constexpr int TQ_WORKER0 = 4;
+constexpr int TQ_STAGES = 4;        // centroid stages (hi + lo = 32 KB each)
+
+struct TqSmem {
+  unsigned char xstage[4][TC_ATOM_BYTES];          // [quad]
+  unsigned char bhi[TQ_STAGES][TC_ATOM_BYTES];
+  unsigned char blo[TQ_STAGES][TC_ATOM_BYTES];
+  unsigned long long x_full[4], x_conv[4], x_stage_free[4];   // [quad]
+  unsigned long long acc_full[4][2];               // [quad][buffer]: an accumulator of the quad's tile is complete
+  unsigned long long acc_empty[2];                 // [buffer]: its four readers have it in registers
+  unsigned long long b_full[TQ_STAGES], b_empty[TQ_STAGES];
+  unsigned int tmem_base;
+  volatile int abort_flag;
+};
+static_assert(sizeof(TqSmem) + 1024 <= 232448, "TqSmem exceeds the 227 KB a CTA may use");
+
+// Bounded wait on a barrier of this kernel (same rule as mbar_wait).
+__device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, int* error_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm->abort_flag) return false;
+    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+      sm->abort_flag = 1;
+      atomicExch(error_flag, 1);
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TQ_THREADS, 1)
+lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
+                      const __grid_constant__ CUtensorMap map_clo, TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  TqSmem* sm = reinterpret_cast<TqSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_nt = p.k_pad / TC_BN;
+  // n < 2^31 - 128 (checked by the host), so tile and row indices fit 32 bits
+  const int n_tiles = (int)((p.n + TC_BM - 1) / TC_BM);
+  const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const bool update = p.acc != nullptr;
+  const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
+  const bool resident = n_nt <= TQ_STAGES;
+  const int d_eff = p.d + 2;                       // data features + the two fold features
+  const int n_ks = (d_eff + 7) / 8;                // k-steps / 8-feature slices that hold data: 1..4
+  const int fold_chunk = p.d / 4;                  // 16-byte chunk of a row holding features d, d + 1
+
+  if (threadIdx.x == 0) {
+    for (int a = 0; a < 4; ++a) {
+      mbar_init(&sm->x_full[a], 1);
+      mbar_init(&sm->x_conv[a], 4);
+      mbar_init(&sm->x_stage_free[a], 4);
+      mbar_init(&sm->acc_full[a][0], 1);
+      mbar_init(&sm->acc_full[a][1], 1);
+    }
+    for (int a = 0; a < 2; ++a) mbar_init(&sm->acc_empty[a], 4);
+    for (int s = 0; s < TQ_STAGES; ++s) {
+      mbar_init(&sm->b_full[s], 1);
+      mbar_init(&sm->b_empty[s], 1);
+    }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(&sm->tmem_base, TC_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  // CTA-local tile t (global tile blockIdx.x + t * gridDim.x) belongs to quad t & 3 and is the
+  // (t >> 2)-th tile of that quad.
+  if (warp == 0) {
+    // ---------------------------------------------------------------- sample tiles
+    if (lane == 0) {
+      for (int t = 0; t < my_tiles; ++t) {
+        const int q = t & 3;
+        if (!tq_wait(&sm->x_stage_free[q], ((uint32_t)(t >> 2) & 1u) ^ 1u, sm, p.error_flag)) break;
+        mbar_expect_tx(&sm->x_full[q], TC_ATOM_BYTES);
+        tma_load_2d(sm->xstage[q], &map_x, 0, ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM, &sm->x_full[q]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- centroid stages
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        if (resident && t != 0) break;             // everything is in shared memory already
+        for (int i = 0; i < n_nt; ++i, ++it) {
+          const int nt = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
+          const uint32_t s = it % TQ_STAGES, u = it / TQ_STAGES;
+          if (!tq_wait(&sm->b_empty[s], (u & 1u) ^ 1u, sm, p.error_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&sm->b_full[s], 2 * TC_ATOM_BYTES);
+          tma_load_2d(sm->bhi[s], &map_chi, 0, nt * TC_BN, &sm->b_full[s]);
+          tma_load_2d(sm->blo[s], &map_clo, 0, nt * TC_BN, &sm->b_full[s]);
+        }
+      }
+    }
+  } else if (warp < TQ_WORKER0) {
+    // ------------------------------------------------------------------------ MMA
+    // Both warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i with
+    // g & 1 == mw into buffer mw and commits each to the (quad, buffer) barrier of the tile's owner.
+    const uint32_t mw = (uint32_t)warp - 2u;
+    const uint32_t ring = resident ? (uint32_t)n_nt : (uint32_t)TQ_STAGES;
+    const uint32_t lap_flip = resident ? 0u : 1u;
+    uint32_t g = 0, s = 0, lap = 0, ga = 0;
+    bool ok = true;
+    const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
+    const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
+    const uint32_t d_tmem = tmem_base + TC_ACC_COL + mw * TC_BN;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const uint32_t q = (uint32_t)t & 3u;
+      const uint32_t a_hi = tmem_base + q * 64u, a_lo = a_hi + 32u;
+      if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], ((uint32_t)t >> 2) & 1u, sm, p.error_flag))) break;
+      tc_fence_after();
+      for (int i = 0; i < n_nt && ok; ++i, ++g) {
+        if ((g & 1u) == mw) {
+          if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_empty[mw], (ga & 1u) ^ 1u, sm, p.error_flag)) ||
+              !__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
+          if (elect_one()) {
+#pragma unroll
+            for (int ks = 0; ks < TC_KC / 8; ++ks) {
+              if (ks < n_ks) {
+                const uint64_t adv = (uint64_t)(ks * 2);
+                umma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + adv, TC_IDESC, ks != 0);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + adv, TC_IDESC, 1);
+                umma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + adv, TC_IDESC, 1);
+              }
+            }
+            if (!resident) umma_commit(&sm->b_empty[s]);
+            umma_commit(&sm->acc_full[q][mw]);
+          }
+          __syncwarp();
+          ++ga;
+        }
+        if (++s == ring) {
+          s = 0;
+          lap ^= lap_flip;
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- workers
+    const int wk = warp - TQ_WORKER0;
+    const int quad = wk >> 2, lq = warp & 3;
+    const int lane_base = lq * 32;
+    const int row = lane_base + lane;              // this thread's row of every tile of the quad
+    float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
+    uint32_t uq0 = 0u, uq1 = 0u;                   // accumulators of this quad seen in buffer 0 / 1
+    uint32_t changed = 0;
+    bool ok = true;
+    const int n_chunks = p.d / 4;                  // 16-byte chunks of a data row (d is a multiple of 4)
+    const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 64u;
+    const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / 4 + 1 : 0;
+
+    for (int jt = 0; jt < my_count && ok; ++jt) {
+      const int t = quad + 4 * jt;
+      const int m0 = ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM;   // first row of the tile
+      const bool valid = m0 + row < (int)p.n;
+      // previous label of this row: fetched now, compared once the new one is known
+      uint32_t prev_lab = 0xffffffffu;
+      if (update && p.prev != nullptr && valid) prev_lab = __ldg(p.prev + m0 + row);
+
+      // ---- split this thread's row into hi / lo parts in the quad's tensor-memory slot
+      if (!__all_sync(0xffffffffu, tq_wait(&sm->x_full[quad], (uint32_t)jt & 1u, sm, p.error_flag))) break;
+      {
+        const unsigned char* rowp = sm->xstage[quad] + row * 128;
+#pragma unroll 1
+        for (int sl = 0; sl < n_ks; ++sl) {        // 8 features per slice
+          uint32_t hi[8], lo[8];
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            const int c = sl * 2 + c2;
+            float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
+            if (c == fold_chunk) {
+              x.x = 1.f;
+              x.y = 1.f;
+            }
+            const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
+            const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
+            hi[4 * c2 + 0] = __float_as_uint(h0); lo[4 * c2 + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
+            hi[4 * c2 + 1] = __float_as_uint(h1); lo[4 * c2 + 1] = __float_as_uint(tf32_round_alu(x.y - h1));
+            hi[4 * c2 + 2] = __float_as_uint(h2); lo[4 * c2 + 2] = __float_as_uint(tf32_round_alu(x.z - h2));
+            hi[4 * c2 + 3] = __float_as_uint(h3); lo[4 * c2 + 3] = __float_as_uint(tf32_round_alu(x.w - h3));
+          }
+          tmem_st8(slot_addr + sl * 8, hi);
+          tmem_st8(slot_addr + 32 + sl * 8, lo);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&sm->x_conv[quad]);          // the MMAs of this tile may start
+          mbar_arrive(&sm->x_stage_free[quad]);    // the staging buffer may take the quad's next tile
+        }
+      }
+
+      // ---- reduce every accumulator of the tile to this row's (score, index)
+      float best = __int_as_float(0xff800000);
+      uint32_t bi = 0;
+      const uint32_t g0 = (uint32_t)t * (uint32_t)n_nt;
+      for (int i = 0; i < n_nt; ++i) {
+        const uint32_t ab = (g0 + (uint32_t)i) & 1u;
+        const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
+        const int cn = nt_w * TC_BN;
+        if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_full[quad][ab], (ab ? uq1 : uq0) & 1u, sm, p.error_flag))) {
+          ok = false;
+          break;
+        }
+        if (ab) ++uq1; else ++uq0;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN;
+        const float4 unused[8] = {};
+        float qa = __int_as_float(0xff800000);
+        uint32_t ia = 0;
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c4 * 32, v);
+          tmem_ld_wait();
+          if (c4 == 3) {
+            // the whole accumulator has been read: hand the buffer back before the last argmax
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+          }
+          float qv;
+          uint32_t iv;
+          argmax32<true>(v, unused, (uint32_t)(cn + c4 * 32), qv, iv);
+          if (qv > qa) { qa = qv; ia = iv; }       // ascending inside the centroid tile: strict '>'
+        }
+        // centroid tiles arrive in rotated order: larger score wins, equal scores -> smaller index
+        if (qa > best || (qa == best && ia < bi)) {
+          best = qa;
+          bi = ia;
+        }
+      }
+      if (!ok) break;
+
+      // ---- label and update of this thread's own row
+      if (valid) {
+        p.labels[m0 + row] = bi;
+        if (update) {
+          changed += (prev_lab != bi) ? 1u : 0u;
+          const float wr = p.w ? p.w[m0 + row] : 1.f;
+          const float4* xrow = reinterpret_cast<const float4*>(p.X + (int64_t)(m0 + row) * p.d);
+          float* dst = acc_copy + (int64_t)bi * p.d;
+          atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wr);
+          for (int c0 = 0; c0 < n_chunks; c0 += 4) {
+            float4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              x[u] = (c0 + u < n_chunks) ? __ldg(xrow + c0 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (c0 + u < n_chunks) {
+                float4 a4;
+                a4.x = x[u].x * wr; a4.y = x[u].y * wr; a4.z = x[u].z * wr; a4.w = x[u].w * wr;
+                atomicAdd(reinterpret_cast<float4*>(dst + 4 * (c0 + u)), a4);
+              }
+            }
+          }
+        }
+      }
+    }
+    if (update) {
+      for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
+      if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TC_TMEM_COLS);
+  }
+}
+
+}  // namespace kmb
