@@ -445,8 +445,19 @@ def run_gpu_arm(args, cfg):
         e2e_iters = args.steps
         X_np, C_np = Xh.numpy(), Ch.numpy()      # page-locked numpy views: what a user hands in
 
-        def engine_fit(copy_x):
+        phases = {}
+
+        def engine_fit(copy_x, breakdown=False):
             from sklearn_numba_dpex_b200.kmeans import KMeans, KMeansEngine
+
+            def mark(name, t_prev):
+                # only in the (untimed) breakdown pass: wait for the device, note the phase
+                if not breakdown:
+                    return t_prev
+                torch.cuda.synchronize()
+                now = time.perf_counter()
+                phases[name] = (now - t_prev) * 1e3
+                return now
 
             KMeansEngine._CONFIG.update(device=local_rank, algo=args.algo)
             try:
@@ -456,13 +467,16 @@ def run_gpu_arm(args, cfg):
                 t0 = time.perf_counter()
                 engine = KMeansEngine(est)
                 Xp, _, sw = engine.prepare_fit(X_np, sample_weight=None)
+                tp = mark("validate_upload_centre_ms", t0)
                 centers_init = engine.init_centroids(Xp, sw)
                 labels, inertia, centers, n_iter = engine.kmeans_single(Xp, sw, centers_init)
+                tp = mark("lloyd_loop_and_final_pass_ms", tp)
                 engine.unshift_centers(Xp, centers)
                 labels_h = labels.cpu()
                 centres_h = centers.contiguous().cpu()
                 torch.cuda.synchronize()
                 dt_fit = time.perf_counter() - t0
+                mark("unshift_and_read_back_ms", tp)
             finally:
                 KMeansEngine._CONFIG.clear()
             # tol = 0 leaves strict convergence (labels unchanged) as the only early stop; well
@@ -494,6 +508,7 @@ def run_gpu_arm(args, cfg):
         dt_copy, n_lab, n_cen, it_copy = engine_fit(True)
         dt_inplace, _, _, it_inplace = engine_fit(False)
         dt_drivers, it_drivers = drivers_fit()
+        engine_fit(True, breakdown=True)          # untimed: the same call with a device wait per phase
         h2d = (Xh.numel() + Ch.numel()) * esize * world
         d2h = n_lab * 4 * world + n_cen * esize + esize
         e2e = {"value": it_copy / dt_copy, "unit": "iterations/s",
@@ -503,6 +518,7 @@ def run_gpu_arm(args, cfg):
                        f"(max_iter={e2e_iters}, tol=0) -> unshift_centers on a page-locked numpy X "
                        "(validation, upload, centring, tolerance scaling, Lloyd loop, final assignment "
                        "and inertia), labels and centres copied back; copy_x=True",
+               "breakdown_ms": {key: round(val, 3) for key, val in phases.items()},
                "copy_x_false": {"value": it_inplace / dt_inplace, "unit": "iterations/s"},
                "drivers_lloyd": {"value": it_drivers / dt_drivers, "unit": "iterations/s",
                                  "what": "one drivers.lloyd() call on tensors uploaded from pinned "

@@ -32,20 +32,20 @@ __device__ __forceinline__ void load_vec(T* dst, const T* src) {
 
 // Registers that hold one thread's share of a (ROWS x BK) chunk.  A row of the chunk is BK / 4
 // quads of 4 consecutive features; thread t takes quad t % QPR of rows t / QPR, t / QPR + RSTEP, ...
-template <typename T, int ROWS, int BK>
+template <typename T, int ROWS, int BK, int THREADS = CC_THREADS>
 struct ChunkRegs {
   static constexpr int QPR = BK / 4;
-  static constexpr int RSTEP = CC_THREADS / QPR;
+  static constexpr int RSTEP = THREADS / QPR;
   static constexpr int N = (ROWS + RSTEP - 1) / RSTEP;
   T v[N][4];
 };
 
 // Fetches the chunk [row0, row0 + ROWS) x [k0, k0 + BK) of the row-major matrix M (n_rows x d)
 // into registers, zero beyond the matrix.  `vec` is the widest aligned vector width.
-template <typename T, int ROWS, int BK>
-__device__ __forceinline__ void fetch_chunk(ChunkRegs<T, ROWS, BK>& r, const T* __restrict__ M,
+template <typename T, int ROWS, int BK, int THREADS = CC_THREADS>
+__device__ __forceinline__ void fetch_chunk(ChunkRegs<T, ROWS, BK, THREADS>& r, const T* __restrict__ M,
                                             int64_t row0, int64_t n_rows, int d, int k0, int vec) {
-  using R = ChunkRegs<T, ROWS, BK>;
+  using R = ChunkRegs<T, ROWS, BK, THREADS>;
   const int q = threadIdx.x % R::QPR;
   const int f0 = k0 + q * 4;
 #pragma unroll
@@ -95,9 +95,9 @@ __device__ __forceinline__ void fetch_chunk(ChunkRegs<T, ROWS, BK>& r, const T* 
 }
 
 // Stores the fetched chunk feature-major: S[kk][m], row pitch `ld`.
-template <typename T, int ROWS, int BK>
-__device__ __forceinline__ void store_chunk(const ChunkRegs<T, ROWS, BK>& r, T* __restrict__ S, int ld) {
-  using R = ChunkRegs<T, ROWS, BK>;
+template <typename T, int ROWS, int BK, int THREADS = CC_THREADS>
+__device__ __forceinline__ void store_chunk(const ChunkRegs<T, ROWS, BK, THREADS>& r, T* __restrict__ S, int ld) {
+  using R = ChunkRegs<T, ROWS, BK, THREADS>;
   const int q = threadIdx.x % R::QPR;
 #pragma unroll
   for (int i = 0; i < R::N; ++i) {

@@ -29,7 +29,7 @@
 
 namespace kmb {
 
-constexpr int F64_BM = 128, F64_BN = 64, F64_BK = 16, F64_LD = F64_BK + 4;
+constexpr int F64_BN = 64, F64_BK = 16, F64_LD = F64_BK + 4;
 constexpr size_t F64_PRIV_SMEM_MAX = 64 * 1024;
 constexpr size_t F64_RES_SMEM_MAX = 48 * 1024;
 constexpr int F64_MAX_GROUPS = CC_MAX_GROUPS;
@@ -61,10 +61,10 @@ __device__ __forceinline__ void dmma884(double (&c)[2], double a, double b) {
 
 // Stores a fetched (ROWS x 16) chunk row-major with pitch `ld` doubles: each thread holds quads
 // of 4 consecutive features, written as two 16-byte stores.
-template <int ROWS>
-__device__ __forceinline__ void store_chunk_rows(const ChunkRegs<double, ROWS, F64_BK>& r,
+template <int ROWS, int THREADS>
+__device__ __forceinline__ void store_chunk_rows(const ChunkRegs<double, ROWS, F64_BK, THREADS>& r,
                                                  double* __restrict__ S, int ld) {
-  using R = ChunkRegs<double, ROWS, F64_BK>;
+  using R = ChunkRegs<double, ROWS, F64_BK, THREADS>;
   const int q = threadIdx.x % R::QPR;
 #pragma unroll
   for (int i = 0; i < R::N; ++i) {
@@ -77,9 +77,12 @@ __device__ __forceinline__ void store_chunk_rows(const ChunkRegs<double, ROWS, F
   }
 }
 
-template <bool UPDATE, bool RESIDENT>
-__global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
-  constexpr int BM = F64_BM, BN = F64_BN, BK = F64_BK, LD = F64_LD;
+// WM = warps along the sample dimension: the CTA is WM x 2 warps on a (32 WM) x 64 score tile.
+// WM = 2 (128 threads, 64 samples) lets four CTAs share an SM, so that the serial phases of a
+// tile (argmin merge, label write, update) of one CTA overlap the contractions of three others.
+template <bool UPDATE, bool RESIDENT, int WM>
+__global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
+  constexpr int BM = 32 * WM, THREADS = 64 * WM, BN = F64_BN, BK = F64_BK, LD = F64_LD;
   __shared__ __align__(16) double Xs[BM * LD];
   __shared__ __align__(16) double Cs[BN * LD];
   __shared__ double hs[BN];
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = warp & 3, wn = warp >> 2;         // rows 32 wm .., columns 32 wn ..
+  const int wm = warp % WM, wn = warp / WM;        // rows 32 wm .., columns 32 wn ..
   const int gid = lane >> 2, tig = lane & 3;       // fragment coordinates inside an 8x8x4 MMA
   const int d = a.d, k = a.k;
   const int64_t n = a.n;
@@ -109,17 +112,17 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
   double* hres = Cres + (size_t)n_ctiles * n_kchunks * BN * LD;
 
   if (UPDATE && a.smem_priv) {
-    for (int e = tid; e < priv_len; e += CC_THREADS) ssum[e] = 0.0;
+    for (int e = tid; e < priv_len; e += THREADS) ssum[e] = 0.0;
   }
   if (tid < F64_MAX_GROUPS) grp_cnt[tid] = 0;
   if (RESIDENT) {
     for (int ct = 0; ct < n_ctiles; ++ct) {
       for (int kc = 0; kc < n_kchunks; ++kc) {
-        ChunkRegs<double, BN, BK> cr;
-        fetch_chunk<double, BN, BK>(cr, a.C, (int64_t)ct * BN, k, d, kc * BK, a.cvec);
-        store_chunk_rows<BN>(cr, Cres + (size_t)(ct * n_kchunks + kc) * BN * LD, LD);
+        ChunkRegs<double, BN, BK, THREADS> cr;
+        fetch_chunk<double, BN, BK, THREADS>(cr, a.C, (int64_t)ct * BN, k, d, kc * BK, a.cvec);
+        store_chunk_rows<BN, THREADS>(cr, Cres + (size_t)(ct * n_kchunks + kc) * BN * LD, LD);
       }
-      for (int j = tid; j < BN; j += CC_THREADS)
+      for (int j = tid; j < BN; j += THREADS)
         hres[ct * BN + j] = (ct * BN + j < k) ? a.h[ct * BN + j] : inf_value<double>();
     }
   }
@@ -127,15 +130,15 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
 
   // update geometry: groups of G lanes, group og owns the clusters j with j % NG == og
   const int G = owner_group_lanes(d);
-  const int NG = (CC_THREADS / 32) * (32 / G);
+  const int NG = (THREADS / 32) * (32 / G);
   const int og = warp * (32 / G) + lane / G;
   const int gl = lane % G;
 
-  ChunkRegs<double, BM, BK> xr;
-  ChunkRegs<double, BN, BK> cr;
+  ChunkRegs<double, BM, BK, THREADS> xr;
+  ChunkRegs<double, BN, BK, THREADS> cr;
   if (blockIdx.x < n_tiles) {
-    fetch_chunk<double, BM, BK>(xr, a.X, (int64_t)blockIdx.x * BM, n, d, 0, a.xvec);
-    if (!RESIDENT) fetch_chunk<double, BN, BK>(cr, a.C, 0, k, d, 0, a.cvec);
+    fetch_chunk<double, BM, BK, THREADS>(xr, a.X, (int64_t)blockIdx.x * BM, n, d, 0, a.xvec);
+    if (!RESIDENT) fetch_chunk<double, BN, BK, THREADS>(cr, a.C, 0, k, d, 0, a.cvec);
   }
 
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -163,9 +166,9 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
       for (int kc = 0; kc < n_kchunks; ++kc) {
         const bool stage_x = !(n_kchunks == 1 && ct > 0);
         __syncthreads();
-        if (stage_x) store_chunk_rows<BM>(xr, Xs, LD);
+        if (stage_x) store_chunk_rows<BM, THREADS>(xr, Xs, LD);
         if (!RESIDENT) {
-          store_chunk_rows<BN>(cr, Cs, LD);
+          store_chunk_rows<BN, THREADS>(cr, Cs, LD);
           if (kc == 0 && tid < BN) hs[tid] = (cn + tid < k) ? a.h[cn + tid] : inf_value<double>();
         }
         __syncthreads();
@@ -181,8 +184,8 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
           }
           const bool more = ntile < n_tiles;
           const bool next_stage_x = !(n_kchunks == 1 && nct > 0);
-          if (more && next_stage_x) fetch_chunk<double, BM, BK>(xr, a.X, ntile * BM, n, d, nkc * BK, a.xvec);
-          if (more && !RESIDENT) fetch_chunk<double, BN, BK>(cr, a.C, (int64_t)nct * BN, k, d, nkc * BK, a.cvec);
+          if (more && next_stage_x) fetch_chunk<double, BM, BK, THREADS>(xr, a.X, ntile * BM, n, d, nkc * BK, a.xvec);
+          if (more && !RESIDENT) fetch_chunk<double, BN, BK, THREADS>(cr, a.C, (int64_t)nct * BN, k, d, nkc * BK, a.cvec);
         }
         const double* Cc = RESIDENT ? Cres + (size_t)(ct * n_kchunks + kc) * BN * LD : Cs;
         const double* xa = Xs + (size_t)(wm * 32 + gid) * LD + tig;
@@ -270,9 +273,9 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
     } else if (UPDATE) {
       const int total = rows * d;
       const double* xt = a.X + m0 * (int64_t)d;
-      const int upd_drow = CC_THREADS / d, upd_df = CC_THREADS - upd_drow * d;
+      const int upd_drow = THREADS / d, upd_df = THREADS - upd_drow * d;
       int row = tid / d, f = tid - row * d;
-      for (int e = tid; e < total; e += CC_THREADS) {
+      for (int e = tid; e < total; e += THREADS) {
         const double wi = a.w ? a.w[m0 + row] : 1.0;
         atomicAdd(&acc_copy[(int64_t)lab_s[row] * d + f], xt[e] * wi);
         row += upd_drow;
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(CC_THREADS, 2) lloyd_f64_kernel(F64Args a) {
   if (UPDATE) {
     __syncthreads();
     if (a.smem_priv) {
-      for (int e = tid; e < priv_len; e += CC_THREADS) {
+      for (int e = tid; e < priv_len; e += THREADS) {
         const double v = ssum[e];
         if (v != 0.0) atomicAdd(&acc_copy[e], v);
       }
@@ -303,9 +306,21 @@ static size_t f64_resident_bytes(int d, int k) {
   return (n_ctiles * n_kchunks * F64_BN * F64_LD + n_ctiles * F64_BN) * sizeof(double);
 }
 
-template <bool UPDATE>
-static int launch_lloyd_f64(F64Args args, cudaStream_t stream) {
-  const int64_t n_tiles = ceil_div(args.n, F64_BM);
+// KMB_F64_WM=4 in the environment selects the 256-thread, 128-sample CTA (A/B runs); the
+// default is the 128-thread, 64-sample CTA, four to an SM.
+static int f64_wm() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("KMB_F64_WM");
+    cached = (e != nullptr && e[0] == '4') ? 4 : 2;
+  }
+  return cached;
+}
+
+template <bool UPDATE, int WM>
+static int launch_lloyd_f64_wm(F64Args args, cudaStream_t stream) {
+  constexpr int BM = 32 * WM, THREADS = 64 * WM;
+  const int64_t n_tiles = ceil_div(args.n, BM);
   if (n_tiles == 0) return KMB_OK;
   const size_t priv = (size_t)((int64_t)args.k * args.d + args.k) * sizeof(double);
   args.smem_priv = (UPDATE && priv <= F64_PRIV_SMEM_MAX) ? 1 : 0;
@@ -315,14 +330,20 @@ static int launch_lloyd_f64(F64Args args, cudaStream_t stream) {
   args.cvec = cc_vec_width<double>(args.C, args.d);
   size_t dyn = args.smem_priv ? (priv + 15) / 16 * 16 : 0;
   if (args.resident) dyn += res_bytes;
-  auto kern = args.resident ? lloyd_f64_kernel<UPDATE, true> : lloyd_f64_kernel<UPDATE, false>;
+  auto kern = args.resident ? lloyd_f64_kernel<UPDATE, true, WM> : lloyd_f64_kernel<UPDATE, false, WM>;
   KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)(F64_PRIV_SMEM_MAX + F64_RES_SMEM_MAX + 16)));
-  int64_t grid = (int64_t)sm_count() * 2;
+  int64_t grid = (int64_t)sm_count() * (8 / WM);
   if (grid > n_tiles) grid = n_tiles;
-  kern<<<(unsigned)grid, CC_THREADS, dyn, stream>>>(args);
+  kern<<<(unsigned)grid, THREADS, dyn, stream>>>(args);
   KMB_CHECK_LAUNCH();
   return KMB_OK;
+}
+
+template <bool UPDATE>
+static int launch_lloyd_f64(F64Args args, cudaStream_t stream) {
+  return f64_wm() == 4 ? launch_lloyd_f64_wm<UPDATE, 4>(args, stream)
+                       : launch_lloyd_f64_wm<UPDATE, 2>(args, stream);
 }
 
 // KMB_F64_MMA=0 in the environment sends float64 back to the DFMA kernel (A/B runs).
