@@ -46,7 +46,11 @@ CONFIGS = {
 CHUNK = 1 << 20
 # DRAM bytes (read + written) per sample row of one fused-step launch, from the ncu captures
 # summarised under profiles/ (taken at a smaller n; the traffic grows in proportion to n).
-DRAM_BYTES_PER_ROW = {("tf32x3", 128): 540.4}
+DRAM_BYTES_PER_ROW = {
+    ("tf32x3", 128): 540.4,     # lloyd_tc_kernel, n = 1 M, d = 128, k = 1024
+    ("tf32x3", 14): 71.8,       # lloyd_tc_quads_kernel, n = 3 M, d = 14 padded to 16, k = 256
+    ("cuda_core", 32): 266.5,   # lloyd_f64_kernel, n = 1 M, d = 32, k = 64, float64
+}
 
 
 def algorithmic_flops(n, d, k):
@@ -554,16 +558,19 @@ def run_gpu_arm(args, cfg):
             fma_peak, fma_clock = measure_fma_peak(torch, device, cfg["dtype"])
             hbm_ms = abytes / peaks["hbm_gbs"] / 1e6
             fma_ms = flops / (fma_peak * 1e9) if fma_peak else None
+            traffic = None
+            if cfg["dtype"] == "f64":
+                traffic = DRAM_BYTES_PER_ROW.get(("cuda_core", d), 0) * n_local or None
             if fma_peak and fma_ms >= hbm_ms:
                 roofline = {"bound": "fma_pipe", "achieved": tf_achieved, "peak": fma_peak,
-                            "unit": "TFLOP/s", "frac": tf_achieved / fma_peak, "traffic": None,
+                            "unit": "TFLOP/s", "frac": tf_achieved / fma_peak, "traffic": traffic,
                             "peak_source": f"live {'FP32' if cfg['dtype'] == 'f32' else 'FP64'} FMA rate of "
                                            "a register-resident kernel (kmb_measure_fma_peak), best of 10",
                             "hbm_frac": gb_achieved / peaks["hbm_gbs"],
                             "ideal_ms": {"fma_pipe": fma_ms, "hbm": hbm_ms}}
             else:
                 roofline = {"bound": "hbm", "achieved": gb_achieved, "peak": peaks["hbm_gbs"],
-                            "unit": "GB/s", "frac": gb_achieved / peaks["hbm_gbs"], "traffic": None,
+                            "unit": "GB/s", "frac": gb_achieved / peaks["hbm_gbs"], "traffic": traffic,
                             "peak_source": peaks["source"] + " hbm_gbs",
                             "fp_tflops_achieved": tf_achieved, "fma_peak_tflops": fma_peak}
         roofline["kernel_ms"] = kernel_ms

@@ -29,9 +29,11 @@
 // moment; the argmin stays "lowest index wins ties" by merging per-tile minima
 // lexicographically.
 //
-// Every wait on an mbarrier is bounded: on time-out the CTA raises a flag in global memory,
-// all roles leave their loops, tensor memory is released and the kernel returns; the host
-// reads the flag with kmb_lloyd_tc_error.
+// Every wait on an mbarrier is bounded: on time-out the CTA raises a flag in global memory and
+// all roles leave their loops.  On the way out the producers wait (again bounded) for the bulk
+// copies they still have in flight and the MMA warps for their last MMAs, then tensor memory is
+// released and the kernel returns; the flag is sticky and reaches the host through the status
+// record and kmb_lloyd_wait_error.
 //
 // Stands for fused_lloyd_single_step / assignment of the reference
 // (sklearn_numba_dpex/kmeans/kernels/lloyd_single_step.py:149-414,
@@ -69,6 +71,8 @@ struct TcSmem {
   unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
   unsigned long long acc_full[2], acc_empty[2];
   unsigned long long part_full[2], lab_ready[2];
+  unsigned long long drain[2];      // [MMA warp]: its last MMAs have completed (aborting CTA only)
+  long long timeout_cycles;
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -94,6 +98,10 @@ struct TcParams {
   int k_pad;
   uint32_t sleep_ns;        // > 0: barrier waits may sleep this long between polls (see mbar_try_wait_sleep)
   int round_lo;             // general kernel: round the low parts of the sample split (else truncated)
+  int acc_bufs;             // quads kernel: accumulators to use when three fit (2 or 3)
+  float fone;               // 1.0f, opaque to the compiler (see take_if_equal)
+  long long timeout_cycles; // limit of every barrier wait
+  int test_stall;           // test hook: the sample-tile producer stops after its first tile
 };
 
 // ---------------------------------------------------------------------------- PTX
@@ -150,11 +158,29 @@ __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, TcSmem* sm
         if (mbar_try_wait(bar, parity)) return true;
     }
     if (sm->abort_flag) return false;
-    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+    if (clock64() - t0 > sm->timeout_cycles) {
       sm->abort_flag = 1;
       atomicExch(error_flag, 1);
       return false;
     }
+  }
+}
+
+// Leaving an aborting CTA: wait, for about a millisecond at most, until phase `parity` of a
+// barrier has completed.
+__device__ __forceinline__ void drain_wait(void* bar, uint32_t parity) {
+  for (int i = 0; i < 4096; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    __nanosleep(256);
+  }
+}
+// A producer that armed the `full` barriers of a ring of n_slots slots for items 0 .. issued - 1
+// (item i -> slot i mod n_slots, phase (i / n_slots) & 1) waits for the last copy into every slot,
+// so that no bulk copy is still writing this CTA's shared memory when the CTA exits.
+__device__ __forceinline__ void drain_ring(unsigned long long* bars, uint32_t n_slots, uint32_t issued) {
+  for (uint32_t s = 0; s < n_slots && s < issued; ++s) {
+    const uint32_t last = s + ((issued - 1u - s) / n_slots) * n_slots;
+    drain_wait(&bars[s], (last / n_slots) & 1u);
   }
 }
 __device__ __forceinline__ void fence_barrier_init() {
@@ -250,6 +276,15 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+// Aborting CTA: the elected lane of an MMA warp commits once more, to a barrier nobody else uses,
+// and waits (bounded) for it: all MMAs it issued have then completed.
+__device__ __forceinline__ void mma_drain(void* bar) {
+  if (elect_one()) {
+    umma_commit(bar);
+    drain_wait(bar, 0u);
+  }
+  __syncwarp();
+}
 
 // Shared-memory matrix descriptor of a K-major, 128B-swizzled tile whose rows are 128 bytes
 // apart and whose 8-row groups are 1024 bytes apart.
@@ -331,6 +366,66 @@ __device__ __forceinline__ void argmax32(const uint32_t (&v)[32], const float4 (
   index_of_max32(q, max32(q), base, out_v, out_i);
 }
 
+// acc = (qj == m) ? one * J + basef : acc with the select done by a PREDICATED FMA: the comparison
+// runs on the integer pipe, the conditional write on the FMA pipe.  `one` is 1.0f passed at run
+// time, so that the compiler cannot turn the FMA back into a move or a select; J is an immediate
+// (HEX = its float32 bit pattern) and basef changes with every group of 32 scores, so that
+// nothing of it can be computed ahead of the loop and kept in registers.
+#define KMB_TAKE_IF_EQUAL(acc, qj, HEX)                                                        \
+  asm("{\n\t.reg .pred p;\n\tsetp.eq.f32 p, %1, %2;\n\t@p fma.rn.f32 %0, %3, 0f" HEX ", %4;\n\t}" \
+      : "+f"(acc)                                                                                       \
+      : "f"(qj), "f"(m), "f"(one), "f"(basef))
+
+// argmax32 for folded half norms with the index carried as a float (exact: indices < 2^24) and
+// the index search split between the pipes: per score one comparison on the integer pipe (half
+// rate) and one predicated multiply on the FMA pipe, instead of a comparison and a select both on
+// the integer pipe.  Two independent chains (scores 0..15 and 16..31) walk down from the top
+// index so that the lowest equal index is written last; 32 NaNs give (-inf, some index), which
+// never wins a strict comparison.
+__device__ __forceinline__ void argmax32_fidx(const uint32_t (&v)[32], float basef, float one,
+                                              float& out_v, float& out_if) {
+  float q[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) q[j] = __uint_as_float(v[j]);
+  const float m = max32(q);
+  float lo = 3.0e38f, hi = 3.0e38f;
+  KMB_TAKE_IF_EQUAL(hi, q[31], "41F80000");
+  KMB_TAKE_IF_EQUAL(lo, q[15], "41700000");
+  KMB_TAKE_IF_EQUAL(hi, q[30], "41F00000");
+  KMB_TAKE_IF_EQUAL(lo, q[14], "41600000");
+  KMB_TAKE_IF_EQUAL(hi, q[29], "41E80000");
+  KMB_TAKE_IF_EQUAL(lo, q[13], "41500000");
+  KMB_TAKE_IF_EQUAL(hi, q[28], "41E00000");
+  KMB_TAKE_IF_EQUAL(lo, q[12], "41400000");
+  KMB_TAKE_IF_EQUAL(hi, q[27], "41D80000");
+  KMB_TAKE_IF_EQUAL(lo, q[11], "41300000");
+  KMB_TAKE_IF_EQUAL(hi, q[26], "41D00000");
+  KMB_TAKE_IF_EQUAL(lo, q[10], "41200000");
+  KMB_TAKE_IF_EQUAL(hi, q[25], "41C80000");
+  KMB_TAKE_IF_EQUAL(lo, q[9], "41100000");
+  KMB_TAKE_IF_EQUAL(hi, q[24], "41C00000");
+  KMB_TAKE_IF_EQUAL(lo, q[8], "41000000");
+  KMB_TAKE_IF_EQUAL(hi, q[23], "41B80000");
+  KMB_TAKE_IF_EQUAL(lo, q[7], "40E00000");
+  KMB_TAKE_IF_EQUAL(hi, q[22], "41B00000");
+  KMB_TAKE_IF_EQUAL(lo, q[6], "40C00000");
+  KMB_TAKE_IF_EQUAL(hi, q[21], "41A80000");
+  KMB_TAKE_IF_EQUAL(lo, q[5], "40A00000");
+  KMB_TAKE_IF_EQUAL(hi, q[20], "41A00000");
+  KMB_TAKE_IF_EQUAL(lo, q[4], "40800000");
+  KMB_TAKE_IF_EQUAL(hi, q[19], "41980000");
+  KMB_TAKE_IF_EQUAL(lo, q[3], "40400000");
+  KMB_TAKE_IF_EQUAL(hi, q[18], "41900000");
+  KMB_TAKE_IF_EQUAL(lo, q[2], "40000000");
+  KMB_TAKE_IF_EQUAL(hi, q[17], "41880000");
+  KMB_TAKE_IF_EQUAL(lo, q[1], "3F800000");
+  KMB_TAKE_IF_EQUAL(hi, q[16], "41800000");
+  KMB_TAKE_IF_EQUAL(lo, q[0], "00000000");
+  out_v = (m == m) ? m : __int_as_float(0xff800000);
+  out_if = fminf(lo, hi);
+}
+#undef KMB_TAKE_IF_EQUAL
+
 template <bool FOLD>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
@@ -373,7 +468,9 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       mbar_init(&sm->acc_empty[a], 8);
       mbar_init(&sm->part_full[a], 4);
       mbar_init(&sm->lab_ready[a], 4);
+      mbar_init(&sm->drain[a], 1);
     }
+    sm->timeout_cycles = p.timeout_cycles;
     sm->abort_flag = 0;
     fence_barrier_init();
   }
@@ -392,11 +489,13 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
         const uint32_t xs = two_tiles ? (t & 1) : 0, xu = two_tiles ? (t >> 1) : t;
+        if (p.test_stall != 0 && t >= 1) break;    // test hook: a sample tile that never arrives
         if (!mbar_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) break;
         mbar_expect_tx(&sm->x_full[xs], (uint32_t)n_kc * TC_ATOM_BYTES);
         for (int kc = 0; kc < n_kc; ++kc)
           tma_load_2d(sm->xstage[xs * 2 + kc], &map_x, kc * TC_KC, (int)(tile * TC_BM), &sm->x_full[xs]);
       }
+      if (sm->abort_flag) drain_ring(sm->x_full, two_tiles ? 2u : 1u, t);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- centroid stages
@@ -420,6 +519,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           }
         }
       }
+      if (sm->abort_flag) drain_ring(sm->b_full, (uint32_t)TC_STAGES, it);
     }
   } else if (warp < TC_EPI_WARP0) {
     // ------------------------------------------------------------------------ MMA
@@ -498,6 +598,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
       }
     }
+    if (sm->abort_flag) mma_drain(&sm->drain[mw]);
     KMB_PROF(if (blockIdx.x == 0 && lane == 0) printf("[tc prof] mma warp %d: total %lld cyc, wait x_conv %lld, acc_empty %lld, b_full %lld, tiles %u\n", warp, clock64() - t_all, w_conv, w_acc, w_b, t);)
   } else {
     // ------------------------------------- workers: split into TMEM, argmin, centroid update
@@ -796,6 +897,8 @@ struct TsSmem {
   unsigned long long b_full[TC_STAGES], b_empty[TC_STAGES];
   unsigned long long acc_full[2], acc_empty[2];
   unsigned long long part_full[2], lab_ready[2];
+  unsigned long long drain[2];      // [MMA warp]: its last MMAs have completed (aborting CTA only)
+  long long timeout_cycles;
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -821,7 +924,7 @@ __device__ __forceinline__ bool ts_wait(void* bar, uint32_t parity, TsSmem* sm, 
         if (mbar_try_wait(bar, parity)) return true;
     }
     if (sm->abort_flag) return false;
-    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+    if (clock64() - t0 > sm->timeout_cycles) {
       sm->abort_flag = 1;
       atomicExch(error_flag, 1);
       return false;
@@ -853,7 +956,9 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       mbar_init(&sm->acc_empty[a], TS_WORKERS);
       mbar_init(&sm->part_full[a], 12);
       mbar_init(&sm->lab_ready[a], 4);
+      mbar_init(&sm->drain[a], 1);
     }
+    sm->timeout_cycles = p.timeout_cycles;
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
       mbar_init(&sm->b_empty[s], 1);
@@ -876,10 +981,12 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       uint32_t t = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
         const uint32_t xs = t & 1, xu = t >> 1;
+        if (p.test_stall != 0 && t >= 1) break;    // test hook: a sample tile that never arrives
         if (!ts_wait(&sm->x_stage_free[xs], (xu & 1) ^ 1, sm, p.error_flag, p.sleep_ns)) break;
         mbar_expect_tx(&sm->x_full[xs], TC_ATOM_BYTES);
         tma_load_2d(sm->xstage[xs], &map_x, 0, (int)(tile * TC_BM), &sm->x_full[xs]);
       }
+      if (sm->abort_flag) drain_ring(sm->x_full, 2u, t);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- centroid stages
@@ -900,6 +1007,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           tma_load_2d(sm->blo[s], &map_clo, 0, nt * TC_BN, &sm->b_full[s]);
         }
       }
+      if (sm->abort_flag) drain_ring(sm->b_full, (uint32_t)TC_STAGES, it);
     }
   } else if (warp < TS_WORKER0) {
     // ------------------------------------------------------------------------ MMA
@@ -947,6 +1055,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
       }
     }
+    if (sm->abort_flag) mma_drain(&sm->drain[mw]);
   } else {
     // -------------------------------------------------------------------- workers
     const int wk = warp - TS_WORKER0;
@@ -1132,7 +1241,6 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
 }  // namespace kmb
 
-#include "lloyd_tc_teams.cuh"
 #include "lloyd_tc_quads.cuh"
 
 namespace kmb {
@@ -1154,14 +1262,14 @@ static uint32_t tc_sleep_ns() {
   return (uint32_t)cached;
 }
 
-// Which kernel takes short rows: the sixteen-worker kernel (default, KMB_TC_SMALL=1); 0 selects
-// the general kernel, 2 the two-team kernel (A/B runs: on n = 5 M, d = 14, k = 256 the three
-// measured 0.56 ms, 0.77 ms and 0.62 ms per step).
+// Which kernel takes short rows: the four-quad kernel (default, KMB_TC_SMALL=3); 0 selects the
+// general kernel, 1 the sixteen-worker kernel (A/B runs: on n = 5 M, d = 14, k = 256 they
+// measured 0.37 ms, 0.77 ms and 0.56 ms per step).
 static int tc_small_mode() {
   static int cached = -1;
   if (cached < 0) {
     const char* e = getenv("KMB_TC_SMALL");
-    cached = (e == nullptr) ? 3 : ((e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3);
+    cached = (e == nullptr) ? 3 : ((e[0] == '0' || e[0] == '1') ? e[0] - '0' : 3);
   }
   return cached;
 }
@@ -1296,6 +1404,14 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.n_copies = n_copies; p.d = d; p.d_pad = d_pad; p.k = k; p.k_pad = k_pad;
   p.sleep_ns = tc_sleep_ns();
   p.round_lo = tc_env_int("KMB_TC_ROUND_LO", 1);
+  p.acc_bufs = tc_env_int("KMB_TQ_ACC", 3);
+  p.fone = 1.0f;
+  // KMB_TC_TIMEOUT_MS: limit of every barrier wait (default 2 s at 2 GHz); KMB_TC_TEST_STALL=1
+  // makes every CTA's sample-tile producer stop after its first tile, which is how the tests make
+  // a wait run out without faulting anything.
+  const int timeout_ms = tc_env_int("KMB_TC_TIMEOUT_MS", 0);
+  p.timeout_cycles = timeout_ms > 0 ? (long long)timeout_ms * 2000000LL : TC_TIMEOUT_CYCLES;
+  p.test_stall = tc_env_int("KMB_TC_TEST_STALL", 0);
 
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
@@ -1303,18 +1419,10 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   if (fold && d_pad == TC_KC && tc_small_mode() == 3) {
     // short rows: four quads, each owning whole sample tiles
     const size_t smem = sizeof(TqSmem) + 1024;
-    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_quads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-    lloyd_tc_quads_kernel<<<(unsigned)grid, TQ_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
-    KMB_CHECK_LAUNCH();
-    return KMB_OK;
-  }
-  if (fold && d_pad == TC_KC && tc_small_mode() == 2) {
-    // short rows: two teams of eight epilogue warps, alternate sample tiles
-    const size_t smem = sizeof(TtSmem) + 1024;
-    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_teams_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-    lloyd_tc_teams_kernel<<<(unsigned)grid, TT_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
+    // KMB_TQ_FIDX=0 keeps the whole index search on the integer pipe (A/B runs)
+    auto kern = tc_env_int("KMB_TQ_FIDX", 1) ? lloyd_tc_quads_kernel<true> : lloyd_tc_quads_kernel<false>;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)grid, TQ_THREADS, smem, stream>>>(map_x, map_chi, map_clo, p);
     KMB_CHECK_LAUNCH();
     return KMB_OK;
   }

@@ -8,7 +8,8 @@
 // tile, and they never talk to each other:
 //   warp 0        TMA producer of the sample tiles (one slot per quad)
 //   warp 1        TMA producer of the centroid stages (resident when all of them fit)
-//   warps 2, 3    issue the MMAs in tile order, one accumulator buffer each
+//   warps 2, 3    issue the MMAs in tile order: one accumulator buffer each when there are two
+//                 buffers, warp 2 alone when there are three (a buffer must be filled in order)
 //   warps 4 + 4 Q .. 7 + 4 Q   quad Q (Q = 0..3) owns the CTA's tiles t with t mod 4 = Q.  Warp lq of a
 //                 quad owns TMEM lanes 32 lq .. 32 lq + 31, i.e. ONE THREAD OWNS ONE SAMPLE ROW of
 //                 the tile: it splits the row into hi / lo parts in the quad's tensor-memory slot,
@@ -17,8 +18,11 @@
 //                 with 16-byte vector reductions.  No partial results, no label exchange.
 // Four tiles are in flight, one per quad, each at a different stage (split, MMA, argmax, update),
 // so the quads hide each other's latencies and spread the argmax bursts over time.
-// Tensor memory: sample slot of quad Q: hi at columns 64 Q, lo at 64 Q + 32 (256 columns);
-// accumulators at 256 and 384, used in turn by the global sequence of (tile, centroid tile).
+// Tensor memory (512 columns): the sample slot of quad Q holds the hi part and then the lo part
+// of its tile, 8 columns per k-step each.  Rows of at most 16 features (two k-steps) need 32
+// columns per quad, which leaves room for THREE 128-column accumulators behind the slots; longer
+// rows take 64 columns per quad and two accumulators.  The accumulators are used in turn by the
+// CTA-wide sequence g = 0, 1, 2, ... of (tile, centroid tile) pairs: buffer g mod n_acc.
 #pragma once
 
 namespace kmb {
@@ -33,9 +37,14 @@ struct TqSmem {
   unsigned char bhi[TQ_STAGES][TC_ATOM_BYTES];
   unsigned char blo[TQ_STAGES][TC_ATOM_BYTES];
   unsigned long long x_full[4], x_conv[4], x_stage_free[4];   // [quad]
-  unsigned long long acc_full[4][2];               // [quad][buffer]: an accumulator of the quad's tile is complete
-  unsigned long long acc_empty[2];                 // [buffer]: its four readers have it in registers
+  // [quad][buffer]: an accumulator of the quad's tile is complete.  One barrier per quad AND buffer:
+  // a waiter may be at most one phase ahead of its barrier, which holds for the accumulators of
+  // one quad (consumed in order) but not for a barrier shared by quads working on different tiles.
+  unsigned long long acc_full[4][3];
+  unsigned long long acc_empty[3];                 // [buffer]: its four readers have it in registers
   unsigned long long b_full[TQ_STAGES], b_empty[TQ_STAGES];
+  unsigned long long drain[2];                     // [MMA warp]: its last MMAs have completed (aborting CTA only)
+  long long timeout_cycles;
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -49,7 +58,7 @@ __device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, 
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (sm->abort_flag) return false;
-    if (clock64() - t0 > TC_TIMEOUT_CYCLES) {
+    if (clock64() - t0 > sm->timeout_cycles) {
       sm->abort_flag = 1;
       atomicExch(error_flag, 1);
       return false;
@@ -57,6 +66,8 @@ __device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, 
   }
 }
 
+// FIDX: search the index of the maximum on the FMA pipe (see argmax32_fidx).
+template <bool FIDX>
 __global__ void __launch_bounds__(TQ_THREADS, 1)
 lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                       const __grid_constant__ CUtensorMap map_clo, TcParams p) {
@@ -73,20 +84,28 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   const int d_eff = p.d + 2;                       // data features + the two fold features
   const int n_ks = (d_eff + 7) / 8;                // k-steps / 8-feature slices that hold data: 1..4
   const int fold_chunk = p.d / 4;                  // 16-byte chunk of a row holding features d, d + 1
+  // tensor-memory layout (see the head of this file)
+  const uint32_t half_cols = (n_ks <= 2) ? 16u : 32u;          // columns of the hi (or lo) part of a slot
+  const uint32_t n_acc = (n_ks <= 2 && p.acc_bufs >= 3) ? 3u : 2u;
+  const uint32_t acc_col0 = 8u * half_cols;                    // four slots of 2 * half_cols columns
 
   if (threadIdx.x == 0) {
     for (int a = 0; a < 4; ++a) {
       mbar_init(&sm->x_full[a], 1);
       mbar_init(&sm->x_conv[a], 4);
       mbar_init(&sm->x_stage_free[a], 4);
-      mbar_init(&sm->acc_full[a][0], 1);
-      mbar_init(&sm->acc_full[a][1], 1);
     }
-    for (int a = 0; a < 2; ++a) mbar_init(&sm->acc_empty[a], 4);
+    for (int a = 0; a < 3; ++a) {
+      for (int q = 0; q < 4; ++q) mbar_init(&sm->acc_full[q][a], 1);
+      mbar_init(&sm->acc_empty[a], 4);
+    }
     for (int s = 0; s < TQ_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
       mbar_init(&sm->b_empty[s], 1);
     }
+    mbar_init(&sm->drain[0], 1);
+    mbar_init(&sm->drain[1], 1);
+    sm->timeout_cycles = p.timeout_cycles;
     sm->abort_flag = 0;
     fence_barrier_init();
   }
@@ -104,12 +123,15 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   if (warp == 0) {
     // ---------------------------------------------------------------- sample tiles
     if (lane == 0) {
-      for (int t = 0; t < my_tiles; ++t) {
+      int t = 0;
+      for (; t < my_tiles; ++t) {
         const int q = t & 3;
+        if (p.test_stall != 0 && t >= 1) break;    // test hook: a sample tile that never arrives
         if (!tq_wait(&sm->x_stage_free[q], ((uint32_t)(t >> 2) & 1u) ^ 1u, sm, p.error_flag)) break;
         mbar_expect_tx(&sm->x_full[q], TC_ATOM_BYTES);
         tma_load_2d(sm->xstage[q], &map_x, 0, ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM, &sm->x_full[q]);
       }
+      if (sm->abort_flag) drain_ring(sm->x_full, 4u, (uint32_t)t);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- centroid stages
@@ -130,27 +152,32 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           tma_load_2d(sm->blo[s], &map_clo, 0, nt * TC_BN, &sm->b_full[s]);
         }
       }
+      if (sm->abort_flag) drain_ring(sm->b_full, (uint32_t)TQ_STAGES, it);
     }
   } else if (warp < TQ_WORKER0) {
     // ------------------------------------------------------------------------ MMA
-    // Both warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i with
-    // g & 1 == mw into buffer mw and commits each to the (quad, buffer) barrier of the tile's owner.
+    // The issuing warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i
+    // with g mod n_mma == mw into buffer g mod n_acc and commits each to the (quad, buffer)
+    // barrier of the tile's owner.  Two buffers: two warps, each the only user of its buffer.
+    // Three buffers: one warp, so that every buffer is filled and handed back in order of g.
     const uint32_t mw = (uint32_t)warp - 2u;
+    const uint32_t n_mma = (n_acc == 2u) ? 2u : 1u;
     const uint32_t ring = resident ? (uint32_t)n_nt : (uint32_t)TQ_STAGES;
     const uint32_t lap_flip = resident ? 0u : 1u;
-    uint32_t g = 0, s = 0, lap = 0, ga = 0;
+    uint32_t g = 0, s = 0, lap = 0;
     bool ok = true;
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
-    const uint32_t d_tmem = tmem_base + TC_ACC_COL + mw * TC_BN;
-    for (int t = 0; t < my_tiles && ok; ++t) {
+    for (int t = 0; t < my_tiles && ok && mw < n_mma; ++t) {
       const uint32_t q = (uint32_t)t & 3u;
-      const uint32_t a_hi = tmem_base + q * 64u, a_lo = a_hi + 32u;
+      const uint32_t a_hi = tmem_base + q * 2u * half_cols, a_lo = a_hi + half_cols;
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], ((uint32_t)t >> 2) & 1u, sm, p.error_flag))) break;
       tc_fence_after();
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
-        if ((g & 1u) == mw) {
-          if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_empty[mw], (ga & 1u) ^ 1u, sm, p.error_flag)) ||
+        if (g % n_mma == mw) {
+          const uint32_t ab = g % n_acc, au = g / n_acc;       // buffer and how often it was used before
+          const uint32_t d_tmem = tmem_base + acc_col0 + ab * TC_BN;
+          if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_empty[ab], (au & 1u) ^ 1u, sm, p.error_flag)) ||
               !__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
             ok = false;
             break;
@@ -169,10 +196,9 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               }
             }
             if (!resident) umma_commit(&sm->b_empty[s]);
-            umma_commit(&sm->acc_full[q][mw]);
+            umma_commit(&sm->acc_full[q][ab]);
           }
           __syncwarp();
-          ++ga;
         }
         if (++s == ring) {
           s = 0;
@@ -180,6 +206,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
       }
     }
+    if (sm->abort_flag) mma_drain(&sm->drain[mw]);
   } else {
     // -------------------------------------------------------------------- workers
     const int wk = warp - TQ_WORKER0;
@@ -187,20 +214,24 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int lane_base = lq * 32;
     const int row = lane_base + lane;              // this thread's row of every tile of the quad
     float* acc_copy = update ? p.acc + (int64_t)(blockIdx.x % p.n_copies) * p.acc_len : nullptr;
-    uint32_t uq0 = 0u, uq1 = 0u;                   // accumulators of this quad seen in buffer 0 / 1
     uint32_t changed = 0;
+    uint32_t seen = 0u;                            // bit b: parity of this quad's next accumulator in buffer b
     bool ok = true;
     const int n_chunks = p.d / 4;                  // 16-byte chunks of a data row (d is a multiple of 4)
-    const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 64u;
+    const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 2u * half_cols;
     const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / 4 + 1 : 0;
 
     for (int jt = 0; jt < my_count && ok; ++jt) {
       const int t = quad + 4 * jt;
       const int m0 = ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM;   // first row of the tile
       const bool valid = m0 + row < (int)p.n;
-      // previous label of this row: fetched now, compared once the new one is known
+      // previous label and weight of this row: fetched now, used once the new label is known
       uint32_t prev_lab = 0xffffffffu;
-      if (update && p.prev != nullptr && valid) prev_lab = __ldg(p.prev + m0 + row);
+      float wr = 1.f;
+      if (update && valid) {
+        if (p.prev != nullptr) prev_lab = __ldg(p.prev + m0 + row);
+        if (p.w != nullptr) wr = __ldg(p.w + m0 + row);
+      }
 
       // ---- split this thread's row into hi / lo parts in the quad's tensor-memory slot
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_full[quad], (uint32_t)jt & 1u, sm, p.error_flag))) break;
@@ -225,7 +256,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             hi[4 * c2 + 3] = __float_as_uint(h3); lo[4 * c2 + 3] = __float_as_uint(tf32_round_alu(x.w - h3));
           }
           tmem_st8(slot_addr + sl * 8, hi);
-          tmem_st8(slot_addr + 32 + sl * 8, lo);
+          tmem_st8(slot_addr + half_cols + sl * 8, lo);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -239,21 +270,24 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       // ---- reduce every accumulator of the tile to this row's (score, index)
       float best = __int_as_float(0xff800000);
       uint32_t bi = 0;
+      float bif = 0.f;                             // FIDX: the index is carried as a float
       const uint32_t g0 = (uint32_t)t * (uint32_t)n_nt;
       for (int i = 0; i < n_nt; ++i) {
-        const uint32_t ab = (g0 + (uint32_t)i) & 1u;
+        const uint32_t g = g0 + (uint32_t)i;
+        const uint32_t ab = g % n_acc;
         const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
         const int cn = nt_w * TC_BN;
-        if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_full[quad][ab], (ab ? uq1 : uq0) & 1u, sm, p.error_flag))) {
+        if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_full[quad][ab], (seen >> ab) & 1u, sm, p.error_flag))) {
           ok = false;
           break;
         }
-        if (ab) ++uq1; else ++uq0;
+        seen ^= 1u << ab;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + TC_ACC_COL + ab * TC_BN;
+        const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + acc_col0 + ab * TC_BN;
         const float4 unused[8] = {};
         float qa = __int_as_float(0xff800000);
         uint32_t ia = 0;
+        float iaf = 0.f;
 #pragma unroll 1
         for (int c4 = 0; c4 < 4; ++c4) {
           uint32_t v[32];
@@ -266,16 +300,28 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
           }
           float qv;
-          uint32_t iv;
-          argmax32<true>(v, unused, (uint32_t)(cn + c4 * 32), qv, iv);
-          if (qv > qa) { qa = qv; ia = iv; }       // ascending inside the centroid tile: strict '>'
+          if (FIDX) {
+            float ivf;
+            argmax32_fidx(v, (float)(cn + c4 * 32), p.fone, qv, ivf);
+            if (qv > qa) { qa = qv; iaf = ivf; }   // ascending inside the centroid tile: strict '>'
+          } else {
+            uint32_t iv;
+            argmax32<true>(v, unused, (uint32_t)(cn + c4 * 32), qv, iv);
+            if (qv > qa) { qa = qv; ia = iv; }
+          }
         }
         // centroid tiles arrive in rotated order: larger score wins, equal scores -> smaller index
-        if (qa > best || (qa == best && ia < bi)) {
+        if (FIDX) {
+          if (qa > best || (qa == best && iaf < bif)) {
+            best = qa;
+            bif = iaf;
+          }
+        } else if (qa > best || (qa == best && ia < bi)) {
           best = qa;
           bi = ia;
         }
       }
+      if (FIDX) bi = (uint32_t)bif;
       if (!ok) break;
 
       // ---- label and update of this thread's own row
@@ -283,7 +329,6 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         p.labels[m0 + row] = bi;
         if (update) {
           changed += (prev_lab != bi) ? 1u : 0u;
-          const float wr = p.w ? p.w[m0 + row] : 1.f;
           const float4* xrow = reinterpret_cast<const float4*>(p.X + (int64_t)(m0 + row) * p.d);
           float* dst = acc_copy + (int64_t)bi * p.d;
           atomicAdd(&acc_copy[(int64_t)p.k * p.d + bi], wr);

@@ -53,6 +53,8 @@ STEP_SHAPES = [
     # tiles): odd and even numbers of centroid tiles, 1 to 4 feature chunks, resident and streamed
     # centroid stages, one and two sample tiles in flight
     (60_000, 64, 300), (60_000, 96, 200), (60_000, 128, 130), (70_000, 32, 600), (60_000, 20, 700),
+    # short rows with one, two and four 8-feature slices (two or three accumulators in tensor memory)
+    (30_000, 4, 200), (30_000, 12, 384), (60_000, 28, 300),
     # many clusters: labels above 32 767 and 65 535 / 128 centroid tiles per sample tile
     (2048, 8, 40_000),
 ]
