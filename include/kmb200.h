@@ -75,6 +75,17 @@ enum {
                                  workspace for the next kmb_lloyd_step (fp32 only)           */
 };
 
+/* Bits 8-9 of the `flags` of kmb_lloyd_step, kmb_assign_labels, kmb_lloyd_finalize and
+ * kmb_lloyd_plan_launch: how
+ * many TRAILING features of X and of the centroids are zero padding added by the caller (0..3; a
+ * caller that rounded d up to a multiple of 4 so that KMB_ALGO_TF32X3 accepts it).  The
+ * tensor-core step then keeps its two extra contraction features (the folded half norms) in
+ * those slots instead of widening the rows: d = 14 padded to 16 contracts over 16 features
+ * instead of 18 -> 24.  The same value must be given to the finalize call that prepares the
+ * operands and to the step that uses them.  No counterpart in the reference. */
+#define KMB_LLOYD_PAD_FEATURES(n) (((n) & 3) << 8)
+#define KMB_LLOYD_PAD_MASK (3 << 8)
+
 const char* kmb_last_error(void);
 int kmb_version(void);
 /* SM count and compute capability of `device` (host outputs). */
@@ -189,11 +200,12 @@ enum { KMB_PLAN_HAVE_PREV = 1, KMB_PLAN_OPERANDS_READY = 2 };
 int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, void* event_before_step,
                           void* event_after_step, void* event_done, void* stream);
 
-/* labels only.  Replaces make_label_assignment_fixed_window_kernel,
+/* labels only.  flags: 0 or KMB_LLOYD_PAD_FEATURES(n_pad).  Replaces
+ * make_label_assignment_fixed_window_kernel,
  * sklearn_numba_dpex/kmeans/kernels/compute_labels.py:19-185. */
 int kmb_assign_labels(int dtype, int algo, const void* X, const void* C,
                       const void* half_norms, uint32_t* labels, int64_t n, int d, int k,
-                      void* workspace, size_t workspace_bytes, void* stream);
+                      int flags, void* workspace, size_t workspace_bytes, void* stream);
 
 /* per_sample[i] = w_i * sum_f (X[i,f] - C[labels[i],f])^2 (per_sample may be NULL);
  * total (may be NULL) receives the sum over i as one element of `dtype`, summed in

@@ -55,7 +55,7 @@ _SIGNATURES = {
     "kmb_lloyd_merge_copies": (c_int, [c_int, _P, c_int, c_int64, _P, c_int, _P]),
     "kmb_lloyd_finalize": (c_int, [c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, c_int,
                                    c_int, _P, c_size_t, _P]),
-    "kmb_assign_labels": (c_int, [c_int, c_int, _P, _P, _P, _P, c_int64, c_int, c_int, _P,
+    "kmb_assign_labels": (c_int, [c_int, c_int, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P,
                                   c_size_t, _P]),
     "kmb_inertia": (c_int, [c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P, c_size_t,
                             _P]),
@@ -98,6 +98,13 @@ class LloydPlan(ctypes.Structure):
 
 _SIGNATURES["kmb_lloyd_plan_launch"] = (c_int, [POINTER(LloydPlan), c_int64, c_int, _P, _P, _P, _P])
 PLAN_HAVE_PREV, PLAN_OPERANDS_READY = 1, 2
+
+
+def pad_features_flag(n_pad):
+    """KMB_LLOYD_PAD_FEATURES(n): bits 8-9 of the flags of the step, finalize and plan calls."""
+    if not 0 <= int(n_pad) <= 3:
+        raise ValueError("the number of padding features must be 0..3")
+    return (int(n_pad) & 3) << 8
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 

@@ -86,8 +86,13 @@ struct LloydWorkspace {
 // count leaves two spare features: the sample operand carries 1.0 in features d and d + 1, the
 // centroid operands carry -h split over the same two features, and the accumulator comes out
 // as x.c - h directly (one argmax, no half-norm loads, no subtraction per element).
-__host__ __device__ inline bool lloyd_tc_folds(int d) {
-  return d % 4 == 0 && (d % 32) != 0 && (d % 32) <= 28;
+// Index of the first of the two fold features, or -1 when the step does not fold.  `pad` trailing
+// features of the rows are zero padding of the caller (0..3): two or more of them take the fold
+// features; otherwise they follow the data, which needs spare room in the last 32-feature chunk.
+__host__ __device__ inline int lloyd_tc_fold_at(int d, int pad) {
+  if (d % 4 != 0) return -1;
+  if (pad >= 2 && pad <= 3 && d >= 4) return d - pad;
+  return ((d % 32) != 0 && (d % 32) <= 28) ? d : -1;
 }
 
 // Round-to-nearest (ties away) to the 10-bit mantissa of tf32.

@@ -14,7 +14,7 @@ bool lloyd_tc_supported(int dtype, int64_t n, int d, int k);
 bool lloyd_tc_preferred(int dtype, int64_t n, int d, int k);
 int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
                  const uint32_t* prev, uint32_t* labels, float* acc, int n_copies,
-                 int64_t acc_len, int64_t n, int d, int k, bool update, bool operands_ready,
+                 int64_t acc_len, int64_t n, int d, int k, int pad, bool update, bool operands_ready,
                  void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int lloyd_tc_acc_copies(int d, int k);
 }  // namespace kmb
@@ -77,8 +77,10 @@ int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void
   KMB_REQUIRE((int64_t)k * d < (1ll << 31), "kmb_lloyd_step: k*d must be below 2^31");
   const int r = kmb_lloyd_resolve_algo(dtype, algo, n, d, k);
   if (r < 0) return r;
-  KMB_REQUIRE((flags & ~(KMB_STEP_ACC_CLEARED | KMB_STEP_OPERANDS_READY)) == 0,
+  KMB_REQUIRE((flags & ~(KMB_STEP_ACC_CLEARED | KMB_STEP_OPERANDS_READY | KMB_LLOYD_PAD_MASK)) == 0,
               "kmb_lloyd_step: unknown flag bits %d", flags);
+  const int pad = (flags & KMB_LLOYD_PAD_MASK) >> 8;
+  KMB_REQUIRE(pad < d, "kmb_lloyd_step: %d padding features in rows of %d", pad, d);
   const int64_t acc_len = kmb_lloyd_acc_len(d, k);
   const size_t esize = dtype == KMB_F32 ? 4 : 8;
   if (!(flags & KMB_STEP_ACC_CLEARED))
@@ -87,7 +89,7 @@ int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void
   if (r == KMB_ALGO_TF32X3)
     return lloyd_tc_run((const float*)X, (const float*)w, (const float*)C,
                         (const float*)half_norms, prev_labels, labels, (float*)acc, n_copies,
-                        acc_len, n, d, k, true, (flags & KMB_STEP_OPERANDS_READY) != 0, workspace,
+                        acc_len, n, d, k, pad, true, (flags & KMB_STEP_OPERANDS_READY) != 0, workspace,
                         workspace_bytes, (cudaStream_t)stream);
   return lloyd_cc_step(dtype, X, w, C, half_norms, prev_labels, labels, acc, n_copies, acc_len, n,
                        d, k, (cudaStream_t)stream);
@@ -96,8 +98,9 @@ int kmb_lloyd_step(int dtype, int algo, const void* X, const void* w, const void
 int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, void* event_before_step,
                           void* event_after_step, void* event_done, void* stream) {
   KMB_REQUIRE(plan != nullptr && it >= 0, "kmb_lloyd_plan_launch: bad arguments");
-  KMB_REQUIRE((flags & ~(KMB_PLAN_HAVE_PREV | KMB_PLAN_OPERANDS_READY)) == 0,
+  KMB_REQUIRE((flags & ~(KMB_PLAN_HAVE_PREV | KMB_PLAN_OPERANDS_READY | KMB_LLOYD_PAD_MASK)) == 0,
               "kmb_lloyd_plan_launch: unknown flag bits %d", flags);
+  const int pad_bits = flags & KMB_LLOYD_PAD_MASK;
   KMB_REQUIRE(plan->algo == KMB_ALGO_CUDA_CORE || plan->algo == KMB_ALGO_TF32X3,
               "kmb_lloyd_plan_launch: the plan must hold a resolved algo");
   cudaStream_t s = (cudaStream_t)stream;
@@ -107,12 +110,13 @@ int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, voi
   int rc = kmb_lloyd_step(plan->dtype, plan->algo, plan->X, plan->w, plan->C[c], plan->h[c],
                           (flags & KMB_PLAN_HAVE_PREV) ? plan->labels[lp] : nullptr, plan->labels[l],
                           plan->acc, plan->n_copies, plan->n, plan->d, plan->k,
-                          KMB_STEP_ACC_CLEARED | ((flags & KMB_PLAN_OPERANDS_READY) ? KMB_STEP_OPERANDS_READY : 0),
+                          KMB_STEP_ACC_CLEARED | pad_bits |
+                              ((flags & KMB_PLAN_OPERANDS_READY) ? KMB_STEP_OPERANDS_READY : 0),
                           plan->workspace, plan->workspace_bytes, stream);
   if (rc != KMB_OK) return rc;
   if (event_after_step) KMB_CHECK_CUDA(cudaEventRecord((cudaEvent_t)event_after_step, s));
   rc = kmb_lloyd_finalize(plan->dtype, plan->acc, plan->n_copies, plan->merged[l],
-                          KMB_FIN_MERGE | KMB_FIN_CLEAR_ACC | (tc ? KMB_FIN_PREPARE_TF32X3 : 0),
+                          KMB_FIN_MERGE | KMB_FIN_CLEAR_ACC | pad_bits | (tc ? KMB_FIN_PREPARE_TF32X3 : 0),
                           plan->C[c], plan->C[cn], plan->h[cn], plan->shifts, plan->empty_list[l],
                           plan->status[l], plan->k, plan->d, plan->workspace, plan->workspace_bytes,
                           stream);
@@ -122,17 +126,20 @@ int kmb_lloyd_plan_launch(const kmb_lloyd_plan* plan, int64_t it, int flags, voi
 }
 
 int kmb_assign_labels(int dtype, int algo, const void* X, const void* C, const void* half_norms,
-                      uint32_t* labels, int64_t n, int d, int k, void* workspace,
+                      uint32_t* labels, int64_t n, int d, int k, int flags, void* workspace,
                       size_t workspace_bytes, void* stream) {
   KMB_REQUIRE(X && C && half_norms && labels, "kmb_assign_labels: NULL argument");
   KMB_REQUIRE(n >= 0 && d > 0 && k > 0, "kmb_assign_labels: bad sizes");
+  KMB_REQUIRE((flags & ~KMB_LLOYD_PAD_MASK) == 0, "kmb_assign_labels: unknown flag bits %d", flags);
+  const int pad = (flags & KMB_LLOYD_PAD_MASK) >> 8;
+  KMB_REQUIRE(pad < d, "kmb_assign_labels: %d padding features in rows of %d", pad, d);
   KMB_REQUIRE((int64_t)k * d < (1ll << 31), "kmb_assign_labels: k*d must be below 2^31");
   const int r = kmb_lloyd_resolve_algo(dtype, algo, n, d, k);
   if (r < 0) return r;
   if (n == 0) return KMB_OK;
   if (r == KMB_ALGO_TF32X3)
     return lloyd_tc_run((const float*)X, nullptr, (const float*)C, (const float*)half_norms,
-                        nullptr, labels, nullptr, 1, 0, n, d, k, false, false, workspace,
+                        nullptr, labels, nullptr, 1, 0, n, d, k, pad, false, false, workspace,
                         workspace_bytes, (cudaStream_t)stream);
   return lloyd_cc_assign(dtype, X, C, half_norms, labels, n, d, k, (cudaStream_t)stream);
 }

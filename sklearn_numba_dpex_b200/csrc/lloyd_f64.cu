@@ -7,13 +7,14 @@
 // 32 x 32 warp tile needs 8 loads per 16 MMAs (4 096 FMAs): six times less shared-memory
 // traffic and eight times fewer issue slots per FMA.
 //
-// One CTA owns 128 samples and walks the centroids 64 at a time; warp (wm, wn) owns rows
-// 32 wm .. +31 and columns 32 wn .. +31 of the 128 x 64 score tile as 4 x 4 MMA tiles.  Both
-// operands are staged ROW-major (feature index fastest, the layout they have in global memory)
-// with a row pitch of BK + 4 doubles, which makes the fragment loads (8 rows x 4 consecutive
-// features per warp) free of bank conflicts.  Chunks of 16 features are fetched with vector
-// loads into registers one chunk ahead of the arithmetic; the centroids stay resident in shared
-// memory for the whole kernel when they fit.
+// One CTA of NW warps owns 16 NW samples and walks the centroids 64 at a time; warp w owns rows
+// 16 w .. +15 and ALL 64 columns of the score tile as 2 x 8 MMA tiles, so a sample row belongs to
+// one warp (four lanes) and its argmin needs no exchange between warps.  Both operands are
+// staged ROW-major (feature index fastest, the layout they have in global memory) with a row
+// pitch of BK + 4 doubles, which makes the fragment loads (8 rows x 4 consecutive features per
+// warp) free of bank conflicts.  Chunks of 16 features are fetched with vector loads into
+// registers one chunk ahead of the arithmetic; the centroids stay resident in shared memory for
+// the whole kernel when they fit.
 //
 // Argmin and update are those of the CUDA-core kernel: strict '<' in ascending centroid order
 // (lowest index wins ties, NaN never wins; kmeans/kernels/_base_kmeans_kernel_funcs.py:351-366
@@ -77,17 +78,13 @@ __device__ __forceinline__ void store_chunk_rows(const ChunkRegs<double, ROWS, F
   }
 }
 
-// WM = warps along the sample dimension: the CTA is WM x 2 warps on a (32 WM) x 64 score tile.
-// WM = 2 (128 threads, 64 samples) lets four CTAs share an SM, so that the serial phases of a
-// tile (argmin merge, label write, update) of one CTA overlap the contractions of three others.
-template <bool UPDATE, bool RESIDENT, int WM>
-__global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
-  constexpr int BM = 32 * WM, THREADS = 64 * WM, BN = F64_BN, BK = F64_BK, LD = F64_LD;
+// NW = warps of the CTA, each on a 16 x 64 score tile.  NW = 4 (128 threads, 64 samples) lets four
+// CTAs share an SM, so that the serial phases of a tile (label write, update) of one CTA overlap
+// the contractions of three others.
+template <bool UPDATE, bool RESIDENT, int NW>
+__global__ void __launch_bounds__(32 * NW, 16 / NW) lloyd_f64_kernel(F64Args a) {
+  constexpr int BM = 16 * NW, THREADS = 32 * NW, BN = F64_BN, BK = F64_BK, LD = F64_LD;
   __shared__ __align__(16) double Xs[BM * LD];
-  __shared__ __align__(16) double Cs[BN * LD];
-  __shared__ double hs[BN];
-  __shared__ double part_v[2][BM];
-  __shared__ uint32_t part_i[2][BM];
   __shared__ uint32_t lab_s[BM];
   __shared__ double red_s[32];
   __shared__ int grp_cnt[F64_MAX_GROUPS];
@@ -95,7 +92,6 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = warp % WM, wn = warp / WM;        // rows 32 wm .., columns 32 wn ..
   const int gid = lane >> 2, tig = lane & 3;       // fragment coordinates inside an 8x8x4 MMA
   const int d = a.d, k = a.k;
   const int64_t n = a.n;
@@ -105,11 +101,14 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
   const int priv_len = k * d + k;
   double* acc_copy = UPDATE ? a.acc + (int64_t)(blockIdx.x % a.n_copies) * a.acc_len : nullptr;
 
-  // dynamic shared memory: [private sums | resident centroids, chunk (ct, kc) by chunk | half norms]
+  // dynamic shared memory: [private sums | resident centroids, chunk (ct, kc) by chunk | half norms],
+  // or, when the centroids are streamed, [private sums | one staged centroid chunk | its half norms]
   double* ssum = reinterpret_cast<double*>(dyn_smem);
   const size_t priv_bytes = (UPDATE && a.smem_priv) ? (((size_t)priv_len * sizeof(double) + 15) / 16 * 16) : 0;
   double* Cres = reinterpret_cast<double*>(dyn_smem + priv_bytes);
   double* hres = Cres + (size_t)n_ctiles * n_kchunks * BN * LD;
+  double* Cs = Cres;                               // streamed form only
+  double* hs = Cres + (size_t)BN * LD;
 
   if (UPDATE && a.smem_priv) {
     for (int e = tid; e < priv_len; e += THREADS) ssum[e] = 0.0;
@@ -147,21 +146,21 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
     // previous label of the row this thread will write: fetched now, compared after the argmin
     uint32_t prev_lab = 0xffffffffu;
     if (UPDATE && a.prev != nullptr && tid < rows) prev_lab = __ldg(a.prev + m0 + tid);
-    double best[4];
-    uint32_t bi[4];
+    double best[2];
+    uint32_t bi[2];
 #pragma unroll
-    for (int mi = 0; mi < 4; ++mi) {
+    for (int mi = 0; mi < 2; ++mi) {
       best[mi] = inf_value<double>();
       bi[mi] = 0u;
     }
 
     for (int ct = 0; ct < n_ctiles; ++ct) {
       const int cn = ct * BN;
-      double acc[4][4][2];
+      double acc[2][8][2];
 #pragma unroll
-      for (int mi = 0; mi < 4; ++mi)
+      for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
+        for (int ni = 0; ni < 8; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = 0.0;
 
       for (int kc = 0; kc < n_kchunks; ++kc) {
         const bool stage_x = !(n_kchunks == 1 && ct > 0);
@@ -188,32 +187,32 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
           if (more && !RESIDENT) fetch_chunk<double, BN, BK, THREADS>(cr, a.C, (int64_t)nct * BN, k, d, nkc * BK, a.cvec);
         }
         const double* Cc = RESIDENT ? Cres + (size_t)(ct * n_kchunks + kc) * BN * LD : Cs;
-        const double* xa = Xs + (size_t)(wm * 32 + gid) * LD + tig;
-        const double* cb = Cc + (size_t)(wn * 32 + gid) * LD + tig;
+        const double* xa = Xs + (size_t)(warp * 16 + gid) * LD + tig;
+        const double* cb = Cc + (size_t)gid * LD + tig;
 #pragma unroll
         for (int k4 = 0; k4 < BK / 4; ++k4) {
-          double af[4], bf[4];
+          double af[2], bf[8];
 #pragma unroll
-          for (int mi = 0; mi < 4; ++mi) af[mi] = xa[mi * 8 * LD + k4 * 4];
+          for (int mi = 0; mi < 2; ++mi) af[mi] = xa[mi * 8 * LD + k4 * 4];
 #pragma unroll
-          for (int ni = 0; ni < 4; ++ni) bf[ni] = cb[ni * 8 * LD + k4 * 4];
+          for (int ni = 0; ni < 8; ++ni) bf[ni] = cb[ni * 8 * LD + k4 * 4];
 #pragma unroll
-          for (int mi = 0; mi < 4; ++mi)
+          for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
-            for (int ni = 0; ni < 4; ++ni) dmma884(acc[mi][ni], af[mi], bf[ni]);
+            for (int mi = 0; mi < 2; ++mi) dmma884(acc[mi][ni], af[mi], bf[ni]);
         }
       }
 
       // fold this centroid tile into the running minimum, columns in ascending order
       const double* hc = RESIDENT ? hres + cn : hs;
 #pragma unroll
-      for (int ni = 0; ni < 4; ++ni) {
+      for (int ni = 0; ni < 8; ++ni) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int col = wn * 32 + ni * 8 + 2 * tig + e;
+          const int col = ni * 8 + 2 * tig + e;
           const double hj = hc[col];
 #pragma unroll
-          for (int mi = 0; mi < 4; ++mi) {
+          for (int mi = 0; mi < 2; ++mi) {
             const double q = hj - acc[mi][ni][e];
             if (q < best[mi]) {
               best[mi] = q;
@@ -224,9 +223,9 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
       }
     }
 
-    // merge the 4 lanes that share a row, then the two column halves through shared memory
+    // merge the 4 lanes that share a row; lane tig == 0 then holds the row's label
 #pragma unroll
-    for (int mi = 0; mi < 4; ++mi) {
+    for (int mi = 0; mi < 2; ++mi) {
 #pragma unroll
       for (int o = 1; o <= 2; o <<= 1) {
         const double oq = __shfl_xor_sync(0xffffffffu, best[mi], o);
@@ -236,16 +235,7 @@ __global__ void __launch_bounds__(64 * WM, 8 / WM) lloyd_f64_kernel(F64Args a) {
           bi[mi] = oi;
         }
       }
-      if (tig == 0) {
-        part_v[wn][wm * 32 + mi * 8 + gid] = best[mi];
-        part_i[wn][wm * 32 + mi * 8 + gid] = bi[mi];
-      }
-    }
-    __syncthreads();
-    if (tid < BM) {
-      const double v0 = part_v[0][tid], v1 = part_v[1][tid];
-      const uint32_t i0 = part_i[0][tid], i1 = part_i[1][tid];
-      lab_s[tid] = (v1 < v0 || (v1 == v0 && i1 < i0)) ? i1 : i0;
+      if (tig == 0) lab_s[warp * 16 + mi * 8 + gid] = bi[mi];
     }
     __syncthreads();
 
@@ -306,8 +296,8 @@ static size_t f64_resident_bytes(int d, int k) {
   return (n_ctiles * n_kchunks * F64_BN * F64_LD + n_ctiles * F64_BN) * sizeof(double);
 }
 
-// KMB_F64_WM=4 in the environment selects the 256-thread, 128-sample CTA (A/B runs); the
-// default is the 128-thread, 64-sample CTA, four to an SM.
+// KMB_F64_WM=4 in the environment selects the 256-thread, 128-sample CTA of eight warps (A/B
+// runs); the default is the 128-thread, 64-sample CTA of four warps, four to an SM.
 static int f64_wm() {
   static int cached = -1;
   if (cached < 0) {
@@ -317,9 +307,9 @@ static int f64_wm() {
   return cached;
 }
 
-template <bool UPDATE, int WM>
+template <bool UPDATE, int NW>
 static int launch_lloyd_f64_wm(F64Args args, cudaStream_t stream) {
-  constexpr int BM = 32 * WM, THREADS = 64 * WM;
+  constexpr int BM = 16 * NW, THREADS = 32 * NW;
   const int64_t n_tiles = ceil_div(args.n, BM);
   if (n_tiles == 0) return KMB_OK;
   const size_t priv = (size_t)((int64_t)args.k * args.d + args.k) * sizeof(double);
@@ -329,11 +319,11 @@ static int launch_lloyd_f64_wm(F64Args args, cudaStream_t stream) {
   args.xvec = cc_vec_width<double>(args.X, args.d);
   args.cvec = cc_vec_width<double>(args.C, args.d);
   size_t dyn = args.smem_priv ? (priv + 15) / 16 * 16 : 0;
-  if (args.resident) dyn += res_bytes;
-  auto kern = args.resident ? lloyd_f64_kernel<UPDATE, true, WM> : lloyd_f64_kernel<UPDATE, false, WM>;
+  dyn += args.resident ? res_bytes : (size_t)(F64_BN * F64_LD + F64_BN) * sizeof(double);
+  auto kern = args.resident ? lloyd_f64_kernel<UPDATE, true, NW> : lloyd_f64_kernel<UPDATE, false, NW>;
   KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)(F64_PRIV_SMEM_MAX + F64_RES_SMEM_MAX + 16)));
-  int64_t grid = (int64_t)sm_count() * (8 / WM);
+  int64_t grid = (int64_t)sm_count() * (16 / NW);
   if (grid > n_tiles) grid = n_tiles;
   kern<<<(unsigned)grid, THREADS, dyn, stream>>>(args);
   KMB_CHECK_LAUNCH();
@@ -342,8 +332,8 @@ static int launch_lloyd_f64_wm(F64Args args, cudaStream_t stream) {
 
 template <bool UPDATE>
 static int launch_lloyd_f64(F64Args args, cudaStream_t stream) {
-  return f64_wm() == 4 ? launch_lloyd_f64_wm<UPDATE, 4>(args, stream)
-                       : launch_lloyd_f64_wm<UPDATE, 2>(args, stream);
+  return f64_wm() == 4 ? launch_lloyd_f64_wm<UPDATE, 8>(args, stream)
+                       : launch_lloyd_f64_wm<UPDATE, 4>(args, stream);
 }
 
 // KMB_F64_MMA=0 in the environment sends float64 back to the DFMA kernel (A/B runs).

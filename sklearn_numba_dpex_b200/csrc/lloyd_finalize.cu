@@ -49,6 +49,7 @@ struct FinArgs {
   int merge;             // merged is computed from the copies (else it is the input)
   int clear;             // the copies are zeroed once read
   int k, d, k_pad, d_pad;
+  int fold_at;           // first of the two fold features of the operands, or -1 (lloyd_tc_fold_at)
 };
 
 // One warp per cluster: (merge of the accumulator copies), C_new = sums / count, squared shift,
@@ -118,13 +119,14 @@ __global__ void __launch_bounds__(256) finalize_fused_kernel(FinArgs<T> a) {
         a.clo[(int64_t)j * a.d_pad + f] = 0.f;
       }
       __syncwarp();
-      if (lane == 0 && lloyd_tc_folds(d)) {
+      if (lane == 0 && a.fold_at >= 0) {
+        // after the data features: the fold features may sit in zero padding INSIDE the rows
         float fhi[2], flo[2];
         lloyd_tc_fold_values((float)(norm * 0.5), fhi, flo);
-        a.chi[(int64_t)j * a.d_pad + d] = fhi[0];
-        a.clo[(int64_t)j * a.d_pad + d] = flo[0];
-        a.chi[(int64_t)j * a.d_pad + d + 1] = fhi[1];
-        a.clo[(int64_t)j * a.d_pad + d + 1] = flo[1];
+        a.chi[(int64_t)j * a.d_pad + a.fold_at] = fhi[0];
+        a.clo[(int64_t)j * a.d_pad + a.fold_at] = flo[0];
+        a.chi[(int64_t)j * a.d_pad + a.fold_at + 1] = fhi[1];
+        a.clo[(int64_t)j * a.d_pad + a.fold_at + 1] = flo[1];
       }
     }
   } else if (a.chi != nullptr && j < a.k_pad) {
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(256) finalize_fused_kernel(FinArgs<T> a) {
     __syncwarp();
     if (lane == 0) {
       a.h_pad[j] = __int_as_float(0x7f800000);
-      if (lloyd_tc_folds(d)) a.chi[(int64_t)j * a.d_pad + d] = __int_as_float(0x7fc00000);
+      if (a.fold_at >= 0) a.chi[(int64_t)j * a.d_pad + a.fold_at] = __int_as_float(0x7fc00000);
     }
   }
   if (blockIdx.x == 0 && tid == 0) {
@@ -250,8 +252,10 @@ int kmb_lloyd_finalize(int dtype, void* acc, int n_copies, void* merged, int fla
   KMB_REQUIRE(merged && C_old && C_new && half_norms_new && shifts && empty_list && status,
               "kmb_lloyd_finalize: NULL argument");
   KMB_REQUIRE(k > 0 && d > 0, "kmb_lloyd_finalize: k and d must be positive");
-  KMB_REQUIRE((flags & ~(KMB_FIN_MERGE | KMB_FIN_CLEAR_ACC | KMB_FIN_PREPARE_TF32X3)) == 0,
+  KMB_REQUIRE((flags & ~(KMB_FIN_MERGE | KMB_FIN_CLEAR_ACC | KMB_FIN_PREPARE_TF32X3 | KMB_LLOYD_PAD_MASK)) == 0,
               "kmb_lloyd_finalize: unknown flag bits %d", flags);
+  const int pad = (flags & KMB_LLOYD_PAD_MASK) >> 8;
+  KMB_REQUIRE(pad < d, "kmb_lloyd_finalize: %d padding features in rows of %d", pad, d);
   const bool merge = flags & KMB_FIN_MERGE, clear = flags & KMB_FIN_CLEAR_ACC;
   const bool prepare = flags & KMB_FIN_PREPARE_TF32X3;
   KMB_REQUIRE(!(merge || clear) || (acc != nullptr && n_copies >= 1),
@@ -274,6 +278,7 @@ int kmb_lloyd_finalize(int dtype, void* acc, int n_copies, void* merged, int fla
     a.h_pad = prepare ? ws.h_pad : nullptr;
     a.acc_len = kmb_lloyd_acc_len(d, k); a.n_copies = n_copies; a.merge = merge; a.clear = clear;
     a.k = k; a.d = d; a.k_pad = ws.k_pad; a.d_pad = ws.d_pad;
+    a.fold_at = prepare ? lloyd_tc_fold_at(d, pad) : -1;
     const int threads = 256, warps = threads / 32;
     const int rows = prepare ? ws.k_pad : k;
     finalize_fused_kernel<T><<<(unsigned)ceil_div(rows, warps), threads, 0, (cudaStream_t)stream>>>(a);

@@ -100,6 +100,7 @@ struct TcParams {
   int round_lo;             // general kernel: round the low parts of the sample split (else truncated)
   int acc_bufs;             // quads kernel: accumulators to use when three fit (2 or 3)
   float fone;               // 1.0f, opaque to the compiler (see take_if_equal)
+  int fold_at;              // first of the two fold features (lloyd_tc_fold_at), or -1
   long long timeout_cycles; // limit of every barrier wait
   int test_stall;           // test hook: the sample-tile producer stops after its first tile
 };
@@ -426,13 +427,29 @@ __device__ __forceinline__ void argmax32_fidx(const uint32_t (&v)[32], float bas
 }
 #undef KMB_TAKE_IF_EQUAL
 
+// The sample side of the folded half norms: 1.0 in the two fold features, which are components
+// off and off + 1 (off = fold_at mod 4 = 0, 1 or 2) of one 16-byte chunk of the row.
+__device__ __forceinline__ void set_fold_ones(float4& x, int off) {
+  if (off == 0) {
+    x.x = 1.f;
+    x.y = 1.f;
+  } else if (off == 1) {
+    x.y = 1.f;
+    x.z = 1.f;
+  } else {
+    x.z = 1.f;
+    x.w = 1.f;
+  }
+}
+
 template <bool FOLD>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                 const __grid_constant__ CUtensorMap map_clo, TcParams p) {
-  // FOLD: features d and d + 1 of the padded operands carry the half norms (see lloyd_tc_folds)
-  const int d_eff = FOLD ? p.d + 2 : p.d;
-  const int fold_chunk = FOLD ? p.d / 4 : -1;      // 16-byte chunk of a row that holds them
+  // FOLD: features fold_at and fold_at + 1 of the operands carry the half norms (see lloyd_tc_fold_at)
+  const int d_eff = FOLD ? (p.fold_at + 2 > p.d ? p.fold_at + 2 : p.d) : p.d;
+  const int fold_chunk = FOLD ? p.fold_at / 4 : -1;   // 16-byte chunk of a row that holds them
+  const int fold_off = FOLD ? p.fold_at % 4 : 0;
   extern __shared__ unsigned char smem_raw[];
   TcSmem* sm = reinterpret_cast<TcSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -639,10 +656,7 @@ lloyd_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
-          if (FOLD && kc * 8 + c == fold_chunk) {   // the sample side of the folded half norms
-            x.x = 1.f;
-            x.y = 1.f;
-          }
+          if (FOLD && kc * 8 + c == fold_chunk) set_fold_ones(x, fold_off);
           // the tensor core reads the top 19 bits of each word: round the low part as well
           // instead of letting it be truncated
           const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
@@ -943,9 +957,10 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   const bool update = p.acc != nullptr;
   const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
   const bool resident = n_nt <= TC_STAGES;
-  const int d_eff = p.d + 2;                       // data features + the two fold features
+  const int d_eff = p.fold_at + 2 > p.d ? p.fold_at + 2 : p.d;   // data features and the two fold features
   const int n_ks = (d_eff + 7) / 8;                // k-steps (of 8 features) that hold data: 1..4
-  const int fold_chunk = p.d / 4;                  // 16-byte chunk of a row holding features d, d + 1
+  const int fold_chunk = p.fold_at / 4;            // 16-byte chunk of a row holding the fold features
+  const int fold_off = p.fold_at % 4;
 
   if (threadIdx.x == 0) {
     for (int a = 0; a < 2; ++a) {
@@ -1085,10 +1100,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       for (int c2 = 0; c2 < 2; ++c2) {
         const int c = cq * 2 + c2;
         float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
-        if (c == fold_chunk) {
-          x.x = 1.f;
-          x.y = 1.f;
-        }
+        if (c == fold_chunk) set_fold_ones(x, fold_off);
         const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
         const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
         hi[4 * c2 + 0] = __float_as_uint(h0); lo[4 * c2 + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
@@ -1275,30 +1287,31 @@ static int tc_small_mode() {
 }
 
 // Centroids -> zero-padded hi / lo parts (both rounded to tf32) and +inf-padded half norms.
-// With `fold` the features d and d + 1 carry -h (see lloyd_tc_folds); padding centroids get a
-// NaN there, so that their scores are NaN and never win.
+// With fold_at >= 0 the features fold_at and fold_at + 1 carry -h (see lloyd_tc_fold_at); padding
+// centroids get a NaN there, so that their scores are NaN and never win.
 __global__ void tc_split_centroids_kernel(const float* __restrict__ C, const float* __restrict__ h,
                                           float* __restrict__ chi, float* __restrict__ clo,
                                           float* __restrict__ h_pad, int k, int d, int k_pad,
-                                          int d_pad, int fold) {
+                                          int d_pad, int fold_at) {
   const int64_t total = (int64_t)k_pad * d_pad;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * blockDim.x) {
     const int j = (int)(e / d_pad), f = (int)(e % d_pad);
     float hi = 0.f, lo = 0.f;
-    if (j < k && f < d) {
-      const float c = C[(int64_t)j * d + f];
-      hi = tf32_rna(c);
-      lo = tf32_rna(c - hi);
-    } else if (fold && (f == d || f == d + 1)) {
+    if (fold_at >= 0 && (f == fold_at || f == fold_at + 1)) {
+      // the fold features: after the data, or in the caller's zero padding inside the rows
       if (j < k) {
         float fhi[2], flo[2];
         lloyd_tc_fold_values(h[j], fhi, flo);
-        hi = fhi[f - d];
-        lo = flo[f - d];
-      } else if (f == d) {
+        hi = fhi[f - fold_at];
+        lo = flo[f - fold_at];
+      } else if (f == fold_at) {
         hi = __int_as_float(0x7fc00000);
       }
+    } else if (j < k && f < d) {
+      const float c = C[(int64_t)j * d + f];
+      hi = tf32_rna(c);
+      lo = tf32_rna(c - hi);
     }
     chi[e] = hi;
     clo[e] = lo;
@@ -1366,7 +1379,7 @@ int lloyd_tc_acc_copies(int, int) { return 16; }
 
 static int tc_launch(const float* X, const float* w, const float* C, const float* h,
                      const uint32_t* prev, uint32_t* labels, float* acc, int n_copies,
-                     int64_t acc_len, float* dots, int ldd, int64_t n, int d, int k,
+                     int64_t acc_len, float* dots, int ldd, int64_t n, int d, int k, int pad,
                      bool operands_ready, void* workspace, size_t workspace_bytes,
                      cudaStream_t stream) {
   KMB_REQUIRE(lloyd_tc_supported(KMB_F32, n, d, k), "tcgen05 step: unsupported shape n=%lld d=%d k=%d",
@@ -1383,13 +1396,14 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   }
   // The time-out flag in the control block is sticky: only kmb_lloyd_workspace_init clears it.
   // The raw-product hook (dots) must see plain dot products, so it never folds.
-  const bool fold = lloyd_tc_folds(d) && dots == nullptr && h != nullptr;
+  const int fold_at = (dots == nullptr && h != nullptr) ? lloyd_tc_fold_at(d, pad) : -1;
+  const bool fold = fold_at >= 0;
   if (!operands_ready) {
     const int64_t total = (int64_t)k_pad * d_pad;
     int grid = (int)ceil_div(total, 256);
     if (grid > 1184) grid = 1184;
     tc_split_centroids_kernel<<<grid, 256, 0, stream>>>(C, h, ws.chi, ws.clo, ws.h_pad, k, d, k_pad,
-                                                        d_pad, fold ? 1 : 0);
+                                                        d_pad, fold_at);
     KMB_CHECK_LAUNCH();
   }
   CUtensorMap map_x, map_chi, map_clo;
@@ -1406,6 +1420,7 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.round_lo = tc_env_int("KMB_TC_ROUND_LO", 1);
   p.acc_bufs = tc_env_int("KMB_TQ_ACC", 3);
   p.fone = 1.0f;
+  p.fold_at = fold_at;
   // KMB_TC_TIMEOUT_MS: limit of every barrier wait (default 2 s at 2 GHz); KMB_TC_TEST_STALL=1
   // makes every CTA's sample-tile producer stop after its first tile, which is how the tests make
   // a wait run out without faulting anything.
@@ -1451,10 +1466,10 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
 
 int lloyd_tc_run(const float* X, const float* w, const float* C, const float* h,
                  const uint32_t* prev, uint32_t* labels, float* acc, int n_copies, int64_t acc_len,
-                 int64_t n, int d, int k, bool update, bool operands_ready, void* workspace,
+                 int64_t n, int d, int k, int pad, bool update, bool operands_ready, void* workspace,
                  size_t workspace_bytes, cudaStream_t stream) {
   return tc_launch(X, w, C, h, prev, labels, update ? acc : nullptr, n_copies, acc_len, nullptr, 0, n,
-                   d, k, operands_ready, workspace, workspace_bytes, stream);
+                   d, k, pad, operands_ready, workspace, workspace_bytes, stream);
 }
 
 // out[i, j] = X[i, :] . Y[j, :] with the 3xTF32 pipeline; labels go to scratch in the workspace.
@@ -1468,7 +1483,7 @@ int lloyd_tc_matmul(const float* X, const float* Y, float* out, int64_t m, int n
     return KMB_ERR_WORKSPACE;
   }
   uint32_t* labels = (uint32_t*)((unsigned char*)workspace + ws.bytes);
-  return tc_launch(X, nullptr, Y, nullptr, nullptr, labels, nullptr, 1, 0, out, n, m, kdim, n, false,
+  return tc_launch(X, nullptr, Y, nullptr, nullptr, labels, nullptr, 1, 0, out, n, m, kdim, n, 0, false,
                    workspace, workspace_bytes, stream);
 }
 

@@ -8,8 +8,7 @@
 // tile, and they never talk to each other:
 //   warp 0        TMA producer of the sample tiles (one slot per quad)
 //   warp 1        TMA producer of the centroid stages (resident when all of them fit)
-//   warps 2, 3    issue the MMAs in tile order: one accumulator buffer each when there are two
-//                 buffers, warp 2 alone when there are three (a buffer must be filled in order)
+//   warps 2, 3    issue the MMAs in tile order, alternate accumulators each
 //   warps 4 + 4 Q .. 7 + 4 Q   quad Q (Q = 0..3) owns the CTA's tiles t with t mod 4 = Q.  Warp lq of a
 //                 quad owns TMEM lanes 32 lq .. 32 lq + 31, i.e. ONE THREAD OWNS ONE SAMPLE ROW of
 //                 the tile: it splits the row into hi / lo parts in the quad's tensor-memory slot,
@@ -41,7 +40,8 @@ struct TqSmem {
   // a waiter may be at most one phase ahead of its barrier, which holds for the accumulators of
   // one quad (consumed in order) but not for a barrier shared by quads working on different tiles.
   unsigned long long acc_full[4][3];
-  unsigned long long acc_empty[3];                 // [buffer]: its four readers have it in registers
+  // [buffer][MMA warp that fills it next]: its four readers have it in registers
+  unsigned long long acc_empty[3][2];
   unsigned long long b_full[TQ_STAGES], b_empty[TQ_STAGES];
   unsigned long long drain[2];                     // [MMA warp]: its last MMAs have completed (aborting CTA only)
   long long timeout_cycles;
@@ -81,9 +81,10 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   const bool update = p.acc != nullptr;
   const int nt0 = (int)(blockIdx.x % (unsigned)n_nt);
   const bool resident = n_nt <= TQ_STAGES;
-  const int d_eff = p.d + 2;                       // data features + the two fold features
+  const int d_eff = p.fold_at + 2 > p.d ? p.fold_at + 2 : p.d;   // data features and the two fold features
   const int n_ks = (d_eff + 7) / 8;                // k-steps / 8-feature slices that hold data: 1..4
-  const int fold_chunk = p.d / 4;                  // 16-byte chunk of a row holding features d, d + 1
+  const int fold_chunk = p.fold_at / 4;            // 16-byte chunk of a row holding the fold features
+  const int fold_off = p.fold_at % 4;
   // tensor-memory layout (see the head of this file)
   const uint32_t half_cols = (n_ks <= 2) ? 16u : 32u;          // columns of the hi (or lo) part of a slot
   const uint32_t n_acc = (n_ks <= 2 && p.acc_bufs >= 3) ? 3u : 2u;
@@ -97,7 +98,8 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     for (int a = 0; a < 3; ++a) {
       for (int q = 0; q < 4; ++q) mbar_init(&sm->acc_full[q][a], 1);
-      mbar_init(&sm->acc_empty[a], 4);
+      mbar_init(&sm->acc_empty[a][0], 4);
+      mbar_init(&sm->acc_empty[a][1], 4);
     }
     for (int s = 0; s < TQ_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
@@ -156,32 +158,53 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
   } else if (warp < TQ_WORKER0) {
     // ------------------------------------------------------------------------ MMA
-    // The issuing warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i
-    // with g mod n_mma == mw into buffer g mod n_acc and commits each to the (quad, buffer)
-    // barrier of the tile's owner.  Two buffers: two warps, each the only user of its buffer.
-    // Three buffers: one warp, so that every buffer is filled and handed back in order of g.
+    // Both warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i with
+    // g & 1 == mw into buffer g mod n_acc and commits each to the (quad, buffer) barrier of the
+    // tile's owner.  A buffer is handed back through the barrier of the warp that fills it NEXT
+    // (accumulator g + n_acc), so every barrier has one waiter, which takes its phases in order.
     const uint32_t mw = (uint32_t)warp - 2u;
-    const uint32_t n_mma = (n_acc == 2u) ? 2u : 1u;
     const uint32_t ring = resident ? (uint32_t)n_nt : (uint32_t)TQ_STAGES;
     const uint32_t lap_flip = resident ? 0u : 1u;
     uint32_t g = 0, s = 0, lap = 0;
+    uint32_t e_seen = 0u;                          // bit b: parity of this warp's next wait on acc_empty[b][mw]
     bool ok = true;
+    KMB_PROF(long long m_conv = 0, m_empty = 0, m_b = 0, m_issue = 0, m_all = clock64(), mt;)
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
-    for (int t = 0; t < my_tiles && ok && mw < n_mma; ++t) {
+    for (int t = 0; t < my_tiles && ok; ++t) {
       const uint32_t q = (uint32_t)t & 3u;
       const uint32_t a_hi = tmem_base + q * 2u * half_cols, a_lo = a_hi + half_cols;
+      if (n_nt == 1 && (g & 1u) != mw) {
+        // the tile's only accumulator is the other warp's: nothing to wait for here
+        ++g;
+        if (++s == ring) {
+          s = 0;
+          lap ^= lap_flip;
+        }
+        continue;
+      }
+      KMB_PROF(mt = clock64();)
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], ((uint32_t)t >> 2) & 1u, sm, p.error_flag))) break;
+      KMB_PROF(m_conv += clock64() - mt;)
       tc_fence_after();
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
-        if (g % n_mma == mw) {
-          const uint32_t ab = g % n_acc, au = g / n_acc;       // buffer and how often it was used before
+        if ((g & 1u) == mw) {
+          const uint32_t ab = g % n_acc;                       // accumulator buffer
           const uint32_t d_tmem = tmem_base + acc_col0 + ab * TC_BN;
-          if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_empty[ab], (au & 1u) ^ 1u, sm, p.error_flag)) ||
-              !__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+          KMB_PROF(mt = clock64();)
+          if (g >= n_acc) {                                    // the buffer has been used before
+            if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_empty[ab][mw], (e_seen >> ab) & 1u, sm, p.error_flag))) {
+              ok = false;
+              break;
+            }
+            e_seen ^= 1u << ab;
+          }
+          KMB_PROF(m_empty += clock64() - mt; mt = clock64();)
+          if (!__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
             ok = false;
             break;
           }
+          KMB_PROF(m_b += clock64() - mt; mt = clock64();)
           tc_fence_after();
           const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
           const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
@@ -199,6 +222,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             umma_commit(&sm->acc_full[q][ab]);
           }
           __syncwarp();
+          KMB_PROF(m_issue += clock64() - mt;)
         }
         if (++s == ring) {
           s = 0;
@@ -206,6 +230,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
       }
     }
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0) printf("[tq prof] mma warp %u: total %lld cyc, wait x_conv %lld, acc_empty %lld, b_full %lld, issue %lld, accumulators %u\n", mw, clock64() - m_all, m_conv, m_empty, m_b, m_issue, g);)
     if (sm->abort_flag) mma_drain(&sm->drain[mw]);
   } else {
     // -------------------------------------------------------------------- workers
@@ -220,6 +245,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int n_chunks = p.d / 4;                  // 16-byte chunks of a data row (d is a multiple of 4)
     const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 2u * half_cols;
     const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / 4 + 1 : 0;
+    KMB_PROF(long long w_x = 0, c_split = 0, w_acc = 0, c_arg = 0, c_upd = 0, t_all = clock64(), tw;)
 
     for (int jt = 0; jt < my_count && ok; ++jt) {
       const int t = quad + 4 * jt;
@@ -234,7 +260,9 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
 
       // ---- split this thread's row into hi / lo parts in the quad's tensor-memory slot
+      KMB_PROF(tw = clock64();)
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_full[quad], (uint32_t)jt & 1u, sm, p.error_flag))) break;
+      KMB_PROF(w_x += clock64() - tw; tw = clock64();)
       {
         const unsigned char* rowp = sm->xstage[quad] + row * 128;
 #pragma unroll 1
@@ -244,10 +272,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           for (int c2 = 0; c2 < 2; ++c2) {
             const int c = sl * 2 + c2;
             float4 x = *reinterpret_cast<const float4*>(rowp + ((c ^ (row & 7)) << 4));
-            if (c == fold_chunk) {
-              x.x = 1.f;
-              x.y = 1.f;
-            }
+            if (c == fold_chunk) set_fold_ones(x, fold_off);
             const float h0 = tf32_round_alu(x.x), h1 = tf32_round_alu(x.y);
             const float h2 = tf32_round_alu(x.z), h3 = tf32_round_alu(x.w);
             hi[4 * c2 + 0] = __float_as_uint(h0); lo[4 * c2 + 0] = __float_as_uint(tf32_round_alu(x.x - h0));
@@ -266,6 +291,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           mbar_arrive(&sm->x_stage_free[quad]);    // the staging buffer may take the quad's next tile
         }
       }
+      KMB_PROF(c_split += clock64() - tw;)
 
       // ---- reduce every accumulator of the tile to this row's (score, index)
       float best = __int_as_float(0xff800000);
@@ -277,10 +303,12 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         const uint32_t ab = g % n_acc;
         const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
         const int cn = nt_w * TC_BN;
+        KMB_PROF(tw = clock64();)
         if (!__all_sync(0xffffffffu, tq_wait(&sm->acc_full[quad][ab], (seen >> ab) & 1u, sm, p.error_flag))) {
           ok = false;
           break;
         }
+        KMB_PROF(w_acc += clock64() - tw; tw = clock64();)
         seen ^= 1u << ab;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + acc_col0 + ab * TC_BN;
@@ -297,7 +325,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // the whole accumulator has been read: hand the buffer back before the last argmax
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->acc_empty[ab]);
+            if (lane == 0) mbar_arrive(&sm->acc_empty[ab][(g + n_acc) & 1u]);
           }
           float qv;
           if (FIDX) {
@@ -320,11 +348,13 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           best = qa;
           bi = ia;
         }
+        KMB_PROF(c_arg += clock64() - tw;)
       }
       if (FIDX) bi = (uint32_t)bif;
       if (!ok) break;
 
       // ---- label and update of this thread's own row
+      KMB_PROF(tw = clock64();)
       if (valid) {
         p.labels[m0 + row] = bi;
         if (update) {
@@ -348,7 +378,9 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           }
         }
       }
+      KMB_PROF(c_upd += clock64() - tw;)
     }
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0 && lq == 0) printf("[tq prof] quad %d: total %lld cyc, wait x_full %lld, split %lld, wait acc_full %lld, loads + argmax %lld, update %lld, tiles %d\n", quad, clock64() - t_all, w_x, c_split, w_acc, c_arg, c_upd, my_count);)
     if (update) {
       for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
       if (lane == 0 && changed != 0) atomicAdd(&acc_copy[(int64_t)p.k * p.d + p.k], (float)changed);

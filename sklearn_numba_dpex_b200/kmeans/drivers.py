@@ -19,6 +19,7 @@ from .. import dist
 from .._cabi import (ALGO_AUTO, ALGO_NAMES, FIN_CLEAR_ACC, FIN_MERGE, FIN_PREPARE_TF32X3, PLAN_HAVE_PREV,
                      PLAN_OPERANDS_READY, LloydPlan,
                      STATUS_DTYPE, STEP_ACC_CLEARED, STEP_OPERANDS_READY, KmbError, c_void_p, check,
+                     pad_features_flag,
                      check_wait_error, dtype_code, host_device_pointer, lib, lloyd_workspace, ptr,
                      stream_ptr,
                      workspace_for)
@@ -93,6 +94,8 @@ class LloydState:
         self.X = X
         self.w = sample_weight
         self.n, self.d, self.k = n, d, k
+        # zero features added above: the step keeps its two extra contraction features there
+        self._pad_flag = pad_features_flag(d - self.d_orig)
         self.algo = check(lib.kmb_lloyd_resolve_algo(self.dtype, want, n_policy, d, k),
                           "kmb_lloyd_resolve_algo")
         self.is_tc = self.algo == ALGO_NAMES["tf32x3"]
@@ -177,7 +180,7 @@ class LloydState:
     def _finalize(self, it, merge, clear):
         """One kernel: (merge of the copies,) division, shifts, next half norms, operands of
         the next tensor-core step, empty list, status record of iteration `it`."""
-        flags = (FIN_MERGE if merge else 0) | (FIN_CLEAR_ACC if clear else 0) | \
+        flags = self._pad_flag | (FIN_MERGE if merge else 0) | (FIN_CLEAR_ACC if clear else 0) | \
             (FIN_PREPARE_TF32X3 if self.is_tc else 0)
         dev = self.X.device
         check(lib.kmb_lloyd_finalize(self.dtype, ptr(self.acc), self.n_copies,
@@ -193,7 +196,7 @@ class LloydState:
     def _launch_fused(self, it):
         """The fused kernel of iteration `it`: its labels and the accumulator copies."""
         ready = self.is_tc and self._operands_slot == it % 3
-        flags = STEP_ACC_CLEARED | (STEP_OPERANDS_READY if ready else 0)
+        flags = self._pad_flag | STEP_ACC_CLEARED | (STEP_OPERANDS_READY if ready else 0)
         prev = self._labs[(it + 1) % 2] if (self.have_prev or it > 0) else None
         if self.event_hook is not None:
             self.event_hook("pre", it)
@@ -226,7 +229,7 @@ class LloydState:
             self._launch_reduce_finalize(it)
             return
         ready = self.is_tc and self._operands_slot == it % 3
-        flags = (PLAN_HAVE_PREV if (self.have_prev or it > 0) else 0) | \
+        flags = self._pad_flag | (PLAN_HAVE_PREV if (self.have_prev or it > 0) else 0) | \
             (PLAN_OPERANDS_READY if ready else 0)
         ev = self.step_events.get(it)
         stream = c_void_p(torch.cuda.current_stream(self.X.device).cuda_stream)
@@ -366,8 +369,8 @@ class LloydState:
         dev = self.X.device
         labels = self._labs[self.it % 2]          # free: the next iteration would write it
         check(lib.kmb_assign_labels(self.dtype, self.algo, ptr(self.X), ptr(self.C), ptr(self.h),
-                                    ptr(labels), self.n, self.d, self.k, ptr(self.ws),
-                                    self.ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+                                    ptr(labels), self.n, self.d, self.k, self._pad_flag,
+                                    ptr(self.ws), self.ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
         self._operands_slot = (self.it % 3) if self.is_tc else None
         total = torch.empty(1, dtype=self.X.dtype, device=dev)
         check(lib.kmb_inertia(self.dtype, ptr(self.X), ptr(self.w), ptr(self.C), ptr(labels),
@@ -662,7 +665,7 @@ def get_labels_inertia(X_t, centroids_t, sample_weight, with_inertia, algo="auto
     ws, ws_bytes = lloyd_workspace(dev, n, d, k)
     check(lib.kmb_half_l2_norm(code, ptr(C), ptr(h), k, d, stream_ptr(dev)), "kmb_half_l2_norm")
     check(lib.kmb_assign_labels(code, _algo_code(algo), ptr(X), ptr(C), ptr(h), ptr(labels), n, d,
-                                k, ptr(ws), ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
+                                k, 0, ptr(ws), ws_bytes, stream_ptr(dev)), "kmb_assign_labels")
     if lib.kmb_lloyd_resolve_algo(code, _algo_code(algo), n, d, k) == ALGO_NAMES["tf32x3"]:
         check_wait_error(ws, dev)      # before the inertia call reuses the shared buffer
     if not with_inertia:

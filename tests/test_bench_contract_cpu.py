@@ -105,7 +105,7 @@ def test_null_and_size_arguments_are_rejected_before_any_launch():
     with pytest.raises(ValueError):
         _cabi.check(lib.kmb_lloyd_step(0, 0, None, None, p, p, None, p, p, 1, 10, 4, 2, 0, None, 0, None))
     with pytest.raises(ValueError):
-        _cabi.check(lib.kmb_assign_labels(0, 0, p, p, p, None, 10, 4, 2, None, 0, None))
+        _cabi.check(lib.kmb_assign_labels(0, 0, p, p, p, None, 10, 4, 2, 0, None, 0, None))
     with pytest.raises(ValueError):                                     # unknown flag bits
         _cabi.check(lib.kmb_lloyd_step(0, 0, p, None, p, p, None, p, p, 1, 10, 4, 2, 64, p, 1 << 20, None))
     with pytest.raises(ValueError):                                     # merge without the copies

@@ -66,7 +66,7 @@ def test_fused_step_invariants_at_full_size(name):
     # label-only kernel agrees with the fused step
     lab2 = torch.empty_like(labels)
     check(lib.kmb_assign_labels(st.dtype, st.algo, ptr(st.X), ptr(C_used), ptr(st.h), ptr(lab2), n, dp,
-                                k, ptr(st.ws), st.ws_bytes, stream_ptr(dev)))
+                                k, st._pad_flag, ptr(st.ws), st.ws_bytes, stream_ptr(dev)))
     torch.cuda.synchronize()
     st.check_device_waits()
     assert int((lab2 != labels).sum()) == 0

@@ -17,7 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # shapes of test_lloyd_step_teacher_forced that reach the short-row tensor-core kernels
 SHORT_ROWS = ("n2000_d14_k256 or n40000_d8_k128 or n60000_d20_k700 or n2000_d20_k130 or "
               "n50000_d14_k127 or n30000_d4_k200 or n30000_d12_k384 or n60000_d28_k300 or "
-              "n129_d14_k9")
+              "n129_d14_k9 or n30000_d13_k200 or n40000_d30_k150 or n40000_d29_k140")
 FP64_SHAPES = ("n1000_d17_k127 or n2000_d14_k256 or n3000_d64_k300 or n60000_d20_k700 or "
                "n513_d130_k5 or n7_d3_k2")
 

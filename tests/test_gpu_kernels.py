@@ -55,6 +55,9 @@ STEP_SHAPES = [
     (60_000, 64, 300), (60_000, 96, 200), (60_000, 128, 130), (70_000, 32, 600), (60_000, 20, 700),
     # short rows with one, two and four 8-feature slices (two or three accumulators in tensor memory)
     (30_000, 4, 200), (30_000, 12, 384), (60_000, 28, 300),
+    # d padded to a multiple of 4 by the driver: the fold features go into the padding (two or
+    # three spare features), also when the padded d fills its last 32-feature chunk (30 -> 32, 62 -> 64)
+    (30_000, 13, 200), (40_000, 30, 150), (60_000, 62, 300), (40_000, 29, 140),
     # many clusters: labels above 32 767 and 65 535 / 128 centroid tiles per sample tile
     (2048, 8, 40_000),
 ]
