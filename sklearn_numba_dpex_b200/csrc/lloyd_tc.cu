@@ -99,6 +99,7 @@ struct TcParams {
   uint32_t sleep_ns;        // > 0: barrier waits may sleep this long between polls (see mbar_try_wait_sleep)
   int round_lo;             // general kernel: round the low parts of the sample split (else truncated)
   int acc_bufs;             // quads kernel: accumulators to use when three fit (2 or 3)
+  int mma_warps;            // quads kernel: warps that issue MMAs (1..TQ_MMA_WARPS)
   float fone;               // 1.0f, opaque to the compiler (see take_if_equal)
   int fold_at;              // first of the two fold features (lloyd_tc_fold_at), or -1
   long long timeout_cycles; // limit of every barrier wait
@@ -1419,6 +1420,8 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   p.sleep_ns = tc_sleep_ns();
   p.round_lo = tc_env_int("KMB_TC_ROUND_LO", 1);
   p.acc_bufs = tc_env_int("KMB_TQ_ACC", 3);
+  p.mma_warps = tc_env_int("KMB_TQ_MMA", TQ_MMA_WARPS);
+  if (p.mma_warps != 1) p.mma_warps = TQ_MMA_WARPS;
   p.fone = 1.0f;
   p.fold_at = fold_at;
   // KMB_TC_TIMEOUT_MS: limit of every barrier wait (default 2 s at 2 GHz); KMB_TC_TEST_STALL=1

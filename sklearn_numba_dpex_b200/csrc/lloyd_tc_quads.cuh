@@ -8,7 +8,9 @@
 // tile, and they never talk to each other:
 //   warp 0        TMA producer of the sample tiles (one slot per quad)
 //   warp 1        TMA producer of the centroid stages (resident when all of them fit)
-//   warps 2, 3    issue the MMAs in tile order, alternate accumulators each
+//   warps 2, 3    issue the MMAs in tile order, alternate accumulators each (TQ_MMA_WARPS; four
+//                 issuing warps measured 4 % faster by themselves, but 22 warps leave 88
+//                 registers per thread instead of 96 and the argmax then loses 13 %)
 //   warps 4 + 4 Q .. 7 + 4 Q   quad Q (Q = 0..3) owns the CTA's tiles t with t mod 4 = Q.  Warp lq of a
 //                 quad owns TMEM lanes 32 lq .. 32 lq + 31, i.e. ONE THREAD OWNS ONE SAMPLE ROW of
 //                 the tile: it splits the row into hi / lo parts in the quad's tensor-memory slot,
@@ -26,9 +28,10 @@
 
 namespace kmb {
 
-constexpr int TQ_WARPS = 20;
+constexpr int TQ_MMA_WARPS = 2;     // the issuing loops assume one or two warps (parity of g)
+constexpr int TQ_WORKER0 = 2 + TQ_MMA_WARPS;
+constexpr int TQ_WARPS = TQ_WORKER0 + 16;
 constexpr int TQ_THREADS = TQ_WARPS * 32;
-constexpr int TQ_WORKER0 = 4;
 constexpr int TQ_STAGES = 4;        // centroid stages (hi + lo = 32 KB each)
 
 struct TqSmem {
@@ -41,12 +44,13 @@ struct TqSmem {
   // one quad (consumed in order) but not for a barrier shared by quads working on different tiles.
   unsigned long long acc_full[4][3];
   // [buffer][MMA warp that fills it next]: its four readers have it in registers
-  unsigned long long acc_empty[3][2];
+  unsigned long long acc_empty[3][TQ_MMA_WARPS];
   unsigned long long b_full[TQ_STAGES], b_empty[TQ_STAGES];
-  unsigned long long drain[2];                     // [MMA warp]: its last MMAs have completed (aborting CTA only)
+  unsigned long long drain[TQ_MMA_WARPS];          // [MMA warp]: its last MMAs have completed (aborting CTA only)
   long long timeout_cycles;
   unsigned int tmem_base;
   volatile int abort_flag;
+  KMB_PROF(long long ts[16];)                      // time line of one tile (profiling build)
 };
 static_assert(sizeof(TqSmem) + 1024 <= 232448, "TqSmem exceeds the 227 KB a CTA may use");
 
@@ -68,6 +72,9 @@ __device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, 
 
 // FIDX: search the index of the maximum on the FMA pipe (see argmax32_fidx).
 template <bool FIDX>
+// Profiling build: time stamps of CTA 0's tile TQ_PROBE_TILE (a tile of quad 0).
+#define TQ_PROBE_TILE 40
+#define TQ_STAMP(cond, slot) KMB_PROF(if (blockIdx.x == 0 && lane == 0 && (cond)) sm->ts[slot] = clock64();)
 __global__ void __launch_bounds__(TQ_THREADS, 1)
 lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                       const __grid_constant__ CUtensorMap map_clo, TcParams p) {
@@ -98,15 +105,13 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     for (int a = 0; a < 3; ++a) {
       for (int q = 0; q < 4; ++q) mbar_init(&sm->acc_full[q][a], 1);
-      mbar_init(&sm->acc_empty[a][0], 4);
-      mbar_init(&sm->acc_empty[a][1], 4);
+      for (int w = 0; w < TQ_MMA_WARPS; ++w) mbar_init(&sm->acc_empty[a][w], 4);
     }
     for (int s = 0; s < TQ_STAGES; ++s) {
       mbar_init(&sm->b_full[s], 1);
       mbar_init(&sm->b_empty[s], 1);
     }
-    mbar_init(&sm->drain[0], 1);
-    mbar_init(&sm->drain[1], 1);
+    for (int w = 0; w < TQ_MMA_WARPS; ++w) mbar_init(&sm->drain[w], 1);
     sm->timeout_cycles = p.timeout_cycles;
     sm->abort_flag = 0;
     fence_barrier_init();
@@ -158,25 +163,31 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
   } else if (warp < TQ_WORKER0) {
     // ------------------------------------------------------------------------ MMA
-    // Both warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i with
-    // g & 1 == mw into buffer g mod n_acc and commits each to the (quad, buffer) barrier of the
-    // tile's owner.  A buffer is handed back through the barrier of the warp that fills it NEXT
-    // (accumulator g + n_acc), so every barrier has one waiter, which takes its phases in order.
+    // The issuing warps walk all tiles in order; warp mw issues the accumulators g = t * n_nt + i
+    // with g mod n_mma == mw into buffer g mod n_acc and commits each to the (quad, buffer)
+    // barrier of the tile's owner.  A buffer is handed back through the barrier of the warp that
+    // fills it NEXT (accumulator g + n_acc), so every barrier has one waiter, which takes its
+    // phases in order.  A warp waits for the split of a tile only when it issues for that tile.
+    // (No runtime division in these loops: every cycle of an issuing warp delays all four quads.)
     const uint32_t mw = (uint32_t)warp - 2u;
+    const uint32_t n_mma = (uint32_t)p.mma_warps;              // 1 or 2
     const uint32_t ring = resident ? (uint32_t)n_nt : (uint32_t)TQ_STAGES;
     const uint32_t lap_flip = resident ? 0u : 1u;
     uint32_t g = 0, s = 0, lap = 0;
+    uint32_t ab = 0u;                              // g mod n_acc, kept by increment and wrap
     uint32_t e_seen = 0u;                          // bit b: parity of this warp's next wait on acc_empty[b][mw]
+    uint32_t b_seen = 0u;                          // bit s: this warp has seen centroid stage s complete
     bool ok = true;
-    KMB_PROF(long long m_conv = 0, m_empty = 0, m_b = 0, m_issue = 0, m_all = clock64(), mt;)
+    KMB_PROF(long long m_conv = 0, m_empty = 0, m_b = 0, m_issue = 0, m_fence = 0, m_mma = 0, m_all = clock64(), mt, mt2;)
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
-    for (int t = 0; t < my_tiles && ok; ++t) {
+    for (int t = 0; t < my_tiles && ok && mw < n_mma; ++t) {
       const uint32_t q = (uint32_t)t & 3u;
       const uint32_t a_hi = tmem_base + q * 2u * half_cols, a_lo = a_hi + half_cols;
-      if (n_nt == 1 && (g & 1u) != mw) {
+      if (n_nt == 1 && n_mma == 2u && (g & 1u) != mw) {
         // the tile's only accumulator is the other warp's: nothing to wait for here
         ++g;
+        if (++ab == n_acc) ab = 0u;
         if (++s == ring) {
           s = 0;
           lap ^= lap_flip;
@@ -185,11 +196,12 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
       KMB_PROF(mt = clock64();)
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], ((uint32_t)t >> 2) & 1u, sm, p.error_flag))) break;
-      KMB_PROF(m_conv += clock64() - mt;)
+      KMB_PROF(m_conv += clock64() - mt; mt2 = clock64();)
+      TQ_STAMP(t == TQ_PROBE_TILE, mw == 0 ? 2 : 6)
       tc_fence_after();
+      KMB_PROF(m_fence += clock64() - mt2;)
       for (int i = 0; i < n_nt && ok; ++i, ++g) {
-        if ((g & 1u) == mw) {
-          const uint32_t ab = g % n_acc;                       // accumulator buffer
+        if (n_mma == 1u || (g & 1u) == mw) {
           const uint32_t d_tmem = tmem_base + acc_col0 + ab * TC_BN;
           KMB_PROF(mt = clock64();)
           if (g >= n_acc) {                                    // the buffer has been used before
@@ -200,12 +212,19 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             e_seen ^= 1u << ab;
           }
           KMB_PROF(m_empty += clock64() - mt; mt = clock64();)
-          if (!__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
-            ok = false;
-            break;
+          TQ_STAMP(t == TQ_PROBE_TILE, i == 0 ? 3 : 7)
+          // resident centroid stages complete once: after this warp has seen a stage it skips the poll
+          if (!(resident && ((b_seen >> s) & 1u))) {
+            if (!__all_sync(0xffffffffu, tq_wait(&sm->b_full[s], lap, sm, p.error_flag))) {
+              ok = false;
+              break;
+            }
+            b_seen |= 1u << s;
           }
           KMB_PROF(m_b += clock64() - mt; mt = clock64();)
+          TQ_STAMP(t == TQ_PROBE_TILE && i == 0, 4)
           tc_fence_after();
+          KMB_PROF(m_fence += clock64() - mt; mt2 = clock64();)
           const uint64_t b_hi = b_hi0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
           const uint64_t b_lo = b_lo0 + (uint64_t)(s * (TC_ATOM_BYTES >> 4));
           if (elect_one()) {
@@ -219,18 +238,21 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               }
             }
             if (!resident) umma_commit(&sm->b_empty[s]);
+            KMB_PROF(m_mma += clock64() - mt2;)
             umma_commit(&sm->acc_full[q][ab]);
           }
           __syncwarp();
           KMB_PROF(m_issue += clock64() - mt;)
+          TQ_STAMP(t == TQ_PROBE_TILE, i == 0 ? 5 : 8)
         }
+        if (++ab == n_acc) ab = 0u;
         if (++s == ring) {
           s = 0;
           lap ^= lap_flip;
         }
       }
     }
-    KMB_PROF(if (blockIdx.x == 0 && lane == 0) printf("[tq prof] mma warp %u: total %lld cyc, wait x_conv %lld, acc_empty %lld, b_full %lld, issue %lld, accumulators %u\n", mw, clock64() - m_all, m_conv, m_empty, m_b, m_issue, g);)
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0) printf("[tq prof] mma warp %u: total %lld cyc, wait x_conv %lld, acc_empty %lld, b_full %lld, issue %lld (fences %lld, elected lane's MMAs %lld), accumulators %u\n", mw, clock64() - m_all, m_conv, m_empty, m_b, m_issue, m_fence, m_mma, g);)
     if (sm->abort_flag) mma_drain(&sm->drain[mw]);
   } else {
     // -------------------------------------------------------------------- workers
@@ -245,6 +267,11 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int n_chunks = p.d / 4;                  // 16-byte chunks of a data row (d is a multiple of 4)
     const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 2u * half_cols;
     const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / 4 + 1 : 0;
+    const uint32_t n_mma = (uint32_t)p.mma_warps;
+    // buffer of the first accumulator of this quad's current tile: (t * n_nt) mod n_acc, advanced
+    // by (4 * n_nt) mod n_acc from tile to tile
+    uint32_t ab0 = ((uint32_t)quad * (uint32_t)n_nt) % n_acc;
+    const uint32_t ab_step = (4u * (uint32_t)n_nt) % n_acc;
     KMB_PROF(long long w_x = 0, c_split = 0, w_acc = 0, c_arg = 0, c_upd = 0, t_all = clock64(), tw;)
 
     for (int jt = 0; jt < my_count && ok; ++jt) {
@@ -263,6 +290,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       KMB_PROF(tw = clock64();)
       if (!__all_sync(0xffffffffu, tq_wait(&sm->x_full[quad], (uint32_t)jt & 1u, sm, p.error_flag))) break;
       KMB_PROF(w_x += clock64() - tw; tw = clock64();)
+      TQ_STAMP(t == TQ_PROBE_TILE && lq == 0, 0)
       {
         const unsigned char* rowp = sm->xstage[quad] + row * 128;
 #pragma unroll 1
@@ -292,15 +320,18 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
       }
       KMB_PROF(c_split += clock64() - tw;)
+      TQ_STAMP(t == TQ_PROBE_TILE && lq == 0, 1)
 
       // ---- reduce every accumulator of the tile to this row's (score, index)
       float best = __int_as_float(0xff800000);
       uint32_t bi = 0;
       float bif = 0.f;                             // FIDX: the index is carried as a float
       const uint32_t g0 = (uint32_t)t * (uint32_t)n_nt;
-      for (int i = 0; i < n_nt; ++i) {
+      uint32_t ab = ab0;
+      ab0 += ab_step;
+      if (ab0 >= n_acc) ab0 -= n_acc;
+      for (int i = 0; i < n_nt; ++i, ab = (ab + 1u == n_acc) ? 0u : ab + 1u) {
         const uint32_t g = g0 + (uint32_t)i;
-        const uint32_t ab = g % n_acc;
         const int nt_w = (nt0 + i < n_nt) ? nt0 + i : nt0 + i - n_nt;
         const int cn = nt_w * TC_BN;
         KMB_PROF(tw = clock64();)
@@ -309,6 +340,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           break;
         }
         KMB_PROF(w_acc += clock64() - tw; tw = clock64();)
+        TQ_STAMP(t == TQ_PROBE_TILE && lq == 0 && i < 2, i == 0 ? 9 : 11)
         seen ^= 1u << ab;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + acc_col0 + ab * TC_BN;
@@ -325,7 +357,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // the whole accumulator has been read: hand the buffer back before the last argmax
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->acc_empty[ab][(g + n_acc) & 1u]);
+            if (lane == 0) mbar_arrive(&sm->acc_empty[ab][n_mma == 2u ? ((g + n_acc) & 1u) : 0u]);
           }
           float qv;
           if (FIDX) {
@@ -349,6 +381,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           bi = ia;
         }
         KMB_PROF(c_arg += clock64() - tw;)
+        TQ_STAMP(t == TQ_PROBE_TILE && lq == 0 && i < 2, i == 0 ? 10 : 12)
       }
       if (FIDX) bi = (uint32_t)bif;
       if (!ok) break;
@@ -379,7 +412,9 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
       }
       KMB_PROF(c_upd += clock64() - tw;)
+      TQ_STAMP(t == TQ_PROBE_TILE && lq == 0, 13)
     }
+    KMB_PROF(if (blockIdx.x == 0 && lane == 0 && lq == 0 && quad == 0 && my_tiles > TQ_PROBE_TILE) { const long long z = sm->ts[0]; printf("[tq prof] tile %d time line (cycles after its sample tile arrived): split done %lld | mma warp 0: saw split %lld, buffer free %lld, centroids ready %lld, issued %lld | mma warp 1: saw split %lld, buffer free %lld, issued %lld | worker: acc 0 complete %lld, read %lld, acc 1 complete %lld, read %lld, update done %lld\n", TQ_PROBE_TILE, sm->ts[1] - z, sm->ts[2] - z, sm->ts[3] - z, sm->ts[4] - z, sm->ts[5] - z, sm->ts[6] - z, sm->ts[7] - z, sm->ts[8] - z, sm->ts[9] - z, sm->ts[10] - z, sm->ts[11] - z, sm->ts[12] - z, sm->ts[13] - z); })
     KMB_PROF(if (blockIdx.x == 0 && lane == 0 && lq == 0) printf("[tq prof] quad %d: total %lld cyc, wait x_full %lld, split %lld, wait acc_full %lld, loads + argmax %lld, update %lld, tiles %d\n", quad, clock64() - t_all, w_x, c_split, w_acc, c_arg, c_upd, my_count);)
     if (update) {
       for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(0xffffffffu, changed, o);
