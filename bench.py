@@ -424,6 +424,9 @@ def run_gpu_arm(args, cfg):
     elapsed_ms, kernel_ms = float(t[0]), float(t[1])
     ms_per_step = elapsed_ms / steps_run
     value = 1e3 / ms_per_step
+    # the events bracket the fused kernel of every timed iteration: a kernel time that is not a
+    # plausible share of the iteration means they were not recorded around it
+    assert 0.2 * ms_per_step < kernel_ms <= 1.02 * ms_per_step, (kernel_ms, ms_per_step)
 
     # ---- end to end through the plugin: host buffers in, host results out
     e2e = None

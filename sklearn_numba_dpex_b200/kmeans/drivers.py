@@ -200,11 +200,17 @@ class LloydState:
         prev = self._labs[(it + 1) % 2] if (self.have_prev or it > 0) else None
         if self.event_hook is not None:
             self.event_hook("pre", it)
+        ev = self.step_events.get(it)
+        stream = torch.cuda.current_stream(self.X.device)
+        if ev:
+            ev[0].record(stream)
         check(lib.kmb_lloyd_step(self.dtype, self.algo, ptr(self.X), ptr(self.w),
                                  ptr(self._Cs[it % 3]), ptr(self._hs[it % 3]), ptr(prev),
                                  ptr(self._labs[it % 2]), ptr(self.acc), self.n_copies, self.n,
                                  self.d, self.k, flags, ptr(self.ws), self.ws_bytes,
                                  stream_ptr(self.X.device)), "kmb_lloyd_step")
+        if ev:
+            ev[1].record(stream)
         if self.event_hook is not None:
             self.event_hook("post", it)
         self.kernel_launches += 1 + (1 if self.is_tc and not ready else 0)
