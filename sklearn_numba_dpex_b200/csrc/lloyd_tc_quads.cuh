@@ -30,19 +30,19 @@ namespace kmb {
 
 constexpr int TQ_MMA_WARPS = 2;     // the issuing loops assume one or two warps (parity of g)
 constexpr int TQ_WORKER0 = 2 + TQ_MMA_WARPS;
-constexpr int TQ_WARPS = TQ_WORKER0 + 16;
-constexpr int TQ_THREADS = TQ_WARPS * 32;
+constexpr int TQ_MAX_QUADS = 5;
+constexpr int tq_threads(int nq) { return (TQ_WORKER0 + 4 * nq) * 32; }
 constexpr int TQ_STAGES = 4;        // centroid stages (hi + lo = 32 KB each)
 
 struct TqSmem {
-  unsigned char xstage[4][TC_ATOM_BYTES];          // [quad]
+  unsigned char xstage[TQ_MAX_QUADS][TC_ATOM_BYTES];          // [quad]
   unsigned char bhi[TQ_STAGES][TC_ATOM_BYTES];
   unsigned char blo[TQ_STAGES][TC_ATOM_BYTES];
-  unsigned long long x_full[4], x_conv[4], x_stage_free[4];   // [quad]
+  unsigned long long x_full[TQ_MAX_QUADS], x_conv[TQ_MAX_QUADS], x_stage_free[TQ_MAX_QUADS];   // [quad]
   // [quad][buffer]: an accumulator of the quad's tile is complete.  One barrier per quad AND buffer:
   // a waiter may be at most one phase ahead of its barrier, which holds for the accumulators of
   // one quad (consumed in order) but not for a barrier shared by quads working on different tiles.
-  unsigned long long acc_full[4][3];
+  unsigned long long acc_full[TQ_MAX_QUADS][3];
   // [buffer][MMA warp that fills it next]: its four readers have it in registers
   unsigned long long acc_empty[3][TQ_MMA_WARPS];
   unsigned long long b_full[TQ_STAGES], b_empty[TQ_STAGES];
@@ -70,12 +70,14 @@ __device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, 
   }
 }
 
-// FIDX: search the index of the maximum on the FMA pipe (see argmax32_fidx).
-template <bool FIDX>
 // Profiling build: time stamps of CTA 0's tile TQ_PROBE_TILE (a tile of quad 0).
 #define TQ_PROBE_TILE 40
 #define TQ_STAMP(cond, slot) KMB_PROF(if (blockIdx.x == 0 && lane == 0 && (cond)) sm->ts[slot] = clock64();)
-__global__ void __launch_bounds__(TQ_THREADS, 1)
+// FIDX: search the index of the maximum on the FMA pipe (see argmax32_fidx).  NQ: quads of worker
+// warps = sample tiles in flight (4, or 5 when the rows need at most two k-steps: five 32-column
+// sample slots leave room for two accumulators, five 64-column slots would leave one).
+template <bool FIDX, int NQ>
+__global__ void __launch_bounds__(tq_threads(NQ), 1)
 lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,
                       const __grid_constant__ CUtensorMap map_clo, TcParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -94,17 +96,17 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   const int fold_off = p.fold_at % 4;
   // tensor-memory layout (see the head of this file)
   const uint32_t half_cols = (n_ks <= 2) ? 16u : 32u;          // columns of the hi (or lo) part of a slot
-  const uint32_t n_acc = (n_ks <= 2 && p.acc_bufs >= 3) ? 3u : 2u;
-  const uint32_t acc_col0 = 8u * half_cols;                    // four slots of 2 * half_cols columns
+  const uint32_t acc_col0 = (uint32_t)NQ * 2u * half_cols;     // NQ slots of 2 * half_cols columns
+  const uint32_t n_acc = (acc_col0 + 3u * TC_BN <= (uint32_t)TC_TMEM_COLS && p.acc_bufs >= 3) ? 3u : 2u;
 
   if (threadIdx.x == 0) {
-    for (int a = 0; a < 4; ++a) {
+    for (int a = 0; a < NQ; ++a) {
       mbar_init(&sm->x_full[a], 1);
       mbar_init(&sm->x_conv[a], 4);
       mbar_init(&sm->x_stage_free[a], 4);
     }
     for (int a = 0; a < 3; ++a) {
-      for (int q = 0; q < 4; ++q) mbar_init(&sm->acc_full[q][a], 1);
+      for (int q = 0; q < NQ; ++q) mbar_init(&sm->acc_full[q][a], 1);
       for (int w = 0; w < TQ_MMA_WARPS; ++w) mbar_init(&sm->acc_empty[a][w], 4);
     }
     for (int s = 0; s < TQ_STAGES; ++s) {
@@ -125,20 +127,20 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
 
-  // CTA-local tile t (global tile blockIdx.x + t * gridDim.x) belongs to quad t & 3 and is the
-  // (t >> 2)-th tile of that quad.
+  // CTA-local tile t (global tile blockIdx.x + t * gridDim.x) belongs to quad t mod NQ and is the
+  // (t / NQ)-th tile of that quad.
   if (warp == 0) {
     // ---------------------------------------------------------------- sample tiles
     if (lane == 0) {
       int t = 0;
       for (; t < my_tiles; ++t) {
-        const int q = t & 3;
+        const int q = t % NQ;
         if (p.test_stall != 0 && t >= 1) break;    // test hook: a sample tile that never arrives
-        if (!tq_wait(&sm->x_stage_free[q], ((uint32_t)(t >> 2) & 1u) ^ 1u, sm, p.error_flag)) break;
+        if (!tq_wait(&sm->x_stage_free[q], ((uint32_t)(t / NQ) & 1u) ^ 1u, sm, p.error_flag)) break;
         mbar_expect_tx(&sm->x_full[q], TC_ATOM_BYTES);
         tma_load_2d(sm->xstage[q], &map_x, 0, ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM, &sm->x_full[q]);
       }
-      if (sm->abort_flag) drain_ring(sm->x_full, 4u, (uint32_t)t);
+      if (sm->abort_flag) drain_ring(sm->x_full, (uint32_t)NQ, (uint32_t)t);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- centroid stages
@@ -182,7 +184,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const uint64_t b_hi0 = make_sdesc(smem_u32(sm->bhi[0]));
     const uint64_t b_lo0 = make_sdesc(smem_u32(sm->blo[0]));
     for (int t = 0; t < my_tiles && ok && mw < n_mma; ++t) {
-      const uint32_t q = (uint32_t)t & 3u;
+      const uint32_t q = (uint32_t)(t % NQ);
       const uint32_t a_hi = tmem_base + q * 2u * half_cols, a_lo = a_hi + half_cols;
       if (n_nt == 1 && n_mma == 2u && (g & 1u) != mw) {
         // the tile's only accumulator is the other warp's: nothing to wait for here
@@ -195,7 +197,7 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         continue;
       }
       KMB_PROF(mt = clock64();)
-      if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], ((uint32_t)t >> 2) & 1u, sm, p.error_flag))) break;
+      if (!__all_sync(0xffffffffu, tq_wait(&sm->x_conv[q], (uint32_t)(t / NQ) & 1u, sm, p.error_flag))) break;
       KMB_PROF(m_conv += clock64() - mt; mt2 = clock64();)
       TQ_STAMP(t == TQ_PROBE_TILE, mw == 0 ? 2 : 6)
       tc_fence_after();
@@ -266,16 +268,16 @@ lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     bool ok = true;
     const int n_chunks = p.d / 4;                  // 16-byte chunks of a data row (d is a multiple of 4)
     const uint32_t slot_addr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)quad * 2u * half_cols;
-    const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / 4 + 1 : 0;
+    const int my_count = (my_tiles > quad) ? (my_tiles - 1 - quad) / NQ + 1 : 0;
     const uint32_t n_mma = (uint32_t)p.mma_warps;
     // buffer of the first accumulator of this quad's current tile: (t * n_nt) mod n_acc, advanced
     // by (4 * n_nt) mod n_acc from tile to tile
     uint32_t ab0 = ((uint32_t)quad * (uint32_t)n_nt) % n_acc;
-    const uint32_t ab_step = (4u * (uint32_t)n_nt) % n_acc;
+    const uint32_t ab_step = ((uint32_t)NQ * (uint32_t)n_nt) % n_acc;
     KMB_PROF(long long w_x = 0, c_split = 0, w_acc = 0, c_arg = 0, c_upd = 0, t_all = clock64(), tw;)
 
     for (int jt = 0; jt < my_count && ok; ++jt) {
-      const int t = quad + 4 * jt;
+      const int t = quad + NQ * jt;
       const int m0 = ((int)blockIdx.x + t * (int)gridDim.x) * TC_BM;   // first row of the tile
       const bool valid = m0 + row < (int)p.n;
       // previous label and weight of this row: fetched now, used once the new label is known
