@@ -381,8 +381,8 @@ __device__ __forceinline__ void argmax32(const uint32_t (&v)[32], const float4 (
 // argmax32 for folded half norms with the index carried as a float (exact: indices < 2^24) and
 // the index search split between the pipes: per score one comparison on the integer pipe (half
 // rate) and one predicated multiply on the FMA pipe, instead of a comparison and a select both on
-// the integer pipe.  Two independent chains (scores 0..15 and 16..31) walk down from the top
-// index so that the lowest equal index is written last; 32 NaNs give (-inf, some index), which
+// the integer pipe.  Four independent chains (scores 0..7, 8..15, 16..23, 24..31) walk down from
+// their top index so that the lowest equal index of each is written last; 32 NaNs give (-inf, some index), which
 // never wins a strict comparison.
 __device__ __forceinline__ void argmax32_fidx(const uint32_t (&v)[32], float basef, float one,
                                               float& out_v, float& out_if) {
@@ -390,41 +390,41 @@ __device__ __forceinline__ void argmax32_fidx(const uint32_t (&v)[32], float bas
 #pragma unroll
   for (int j = 0; j < 32; ++j) q[j] = __uint_as_float(v[j]);
   const float m = max32(q);
-  float lo = 3.0e38f, hi = 3.0e38f;
-  KMB_TAKE_IF_EQUAL(hi, q[31], "41F80000");
-  KMB_TAKE_IF_EQUAL(lo, q[15], "41700000");
-  KMB_TAKE_IF_EQUAL(hi, q[30], "41F00000");
-  KMB_TAKE_IF_EQUAL(lo, q[14], "41600000");
-  KMB_TAKE_IF_EQUAL(hi, q[29], "41E80000");
-  KMB_TAKE_IF_EQUAL(lo, q[13], "41500000");
-  KMB_TAKE_IF_EQUAL(hi, q[28], "41E00000");
-  KMB_TAKE_IF_EQUAL(lo, q[12], "41400000");
-  KMB_TAKE_IF_EQUAL(hi, q[27], "41D80000");
-  KMB_TAKE_IF_EQUAL(lo, q[11], "41300000");
-  KMB_TAKE_IF_EQUAL(hi, q[26], "41D00000");
-  KMB_TAKE_IF_EQUAL(lo, q[10], "41200000");
-  KMB_TAKE_IF_EQUAL(hi, q[25], "41C80000");
-  KMB_TAKE_IF_EQUAL(lo, q[9], "41100000");
-  KMB_TAKE_IF_EQUAL(hi, q[24], "41C00000");
-  KMB_TAKE_IF_EQUAL(lo, q[8], "41000000");
-  KMB_TAKE_IF_EQUAL(hi, q[23], "41B80000");
-  KMB_TAKE_IF_EQUAL(lo, q[7], "40E00000");
-  KMB_TAKE_IF_EQUAL(hi, q[22], "41B00000");
-  KMB_TAKE_IF_EQUAL(lo, q[6], "40C00000");
-  KMB_TAKE_IF_EQUAL(hi, q[21], "41A80000");
-  KMB_TAKE_IF_EQUAL(lo, q[5], "40A00000");
-  KMB_TAKE_IF_EQUAL(hi, q[20], "41A00000");
-  KMB_TAKE_IF_EQUAL(lo, q[4], "40800000");
-  KMB_TAKE_IF_EQUAL(hi, q[19], "41980000");
-  KMB_TAKE_IF_EQUAL(lo, q[3], "40400000");
-  KMB_TAKE_IF_EQUAL(hi, q[18], "41900000");
-  KMB_TAKE_IF_EQUAL(lo, q[2], "40000000");
-  KMB_TAKE_IF_EQUAL(hi, q[17], "41880000");
-  KMB_TAKE_IF_EQUAL(lo, q[1], "3F800000");
-  KMB_TAKE_IF_EQUAL(hi, q[16], "41800000");
-  KMB_TAKE_IF_EQUAL(lo, q[0], "00000000");
+  float i0 = 3.0e38f, i1 = 3.0e38f, i2 = 3.0e38f, i3 = 3.0e38f;
+  KMB_TAKE_IF_EQUAL(i3, q[31], "41F80000");
+  KMB_TAKE_IF_EQUAL(i2, q[23], "41B80000");
+  KMB_TAKE_IF_EQUAL(i1, q[15], "41700000");
+  KMB_TAKE_IF_EQUAL(i0, q[7], "40E00000");
+  KMB_TAKE_IF_EQUAL(i3, q[30], "41F00000");
+  KMB_TAKE_IF_EQUAL(i2, q[22], "41B00000");
+  KMB_TAKE_IF_EQUAL(i1, q[14], "41600000");
+  KMB_TAKE_IF_EQUAL(i0, q[6], "40C00000");
+  KMB_TAKE_IF_EQUAL(i3, q[29], "41E80000");
+  KMB_TAKE_IF_EQUAL(i2, q[21], "41A80000");
+  KMB_TAKE_IF_EQUAL(i1, q[13], "41500000");
+  KMB_TAKE_IF_EQUAL(i0, q[5], "40A00000");
+  KMB_TAKE_IF_EQUAL(i3, q[28], "41E00000");
+  KMB_TAKE_IF_EQUAL(i2, q[20], "41A00000");
+  KMB_TAKE_IF_EQUAL(i1, q[12], "41400000");
+  KMB_TAKE_IF_EQUAL(i0, q[4], "40800000");
+  KMB_TAKE_IF_EQUAL(i3, q[27], "41D80000");
+  KMB_TAKE_IF_EQUAL(i2, q[19], "41980000");
+  KMB_TAKE_IF_EQUAL(i1, q[11], "41300000");
+  KMB_TAKE_IF_EQUAL(i0, q[3], "40400000");
+  KMB_TAKE_IF_EQUAL(i3, q[26], "41D00000");
+  KMB_TAKE_IF_EQUAL(i2, q[18], "41900000");
+  KMB_TAKE_IF_EQUAL(i1, q[10], "41200000");
+  KMB_TAKE_IF_EQUAL(i0, q[2], "40000000");
+  KMB_TAKE_IF_EQUAL(i3, q[25], "41C80000");
+  KMB_TAKE_IF_EQUAL(i2, q[17], "41880000");
+  KMB_TAKE_IF_EQUAL(i1, q[9], "41100000");
+  KMB_TAKE_IF_EQUAL(i0, q[1], "3F800000");
+  KMB_TAKE_IF_EQUAL(i3, q[24], "41C00000");
+  KMB_TAKE_IF_EQUAL(i2, q[16], "41800000");
+  KMB_TAKE_IF_EQUAL(i1, q[8], "41000000");
+  KMB_TAKE_IF_EQUAL(i0, q[0], "00000000");
   out_v = (m == m) ? m : __int_as_float(0xff800000);
-  out_if = fminf(lo, hi);
+  out_if = fminf(fminf(i0, i1), fminf(i2, i3));
 }
 #undef KMB_TAKE_IF_EQUAL
 
@@ -1255,6 +1255,7 @@ lloyd_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 }  // namespace kmb
 
 #include "lloyd_tc_quads.cuh"
+#include "lloyd_tc_quads_ss.cuh"
 
 namespace kmb {
 
@@ -1434,6 +1435,18 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
   const int64_t n_tiles = ceil_div(n, TC_BM);
   int64_t grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
+  if (fold && d_pad == TC_KC && tc_small_mode() == 3 && (fold_at + 2 > d ? fold_at + 2 : d) <= 16 &&
+      k_pad / TC_BN <= TS2_STAGES && tc_env_int("KMB_TQ_SS", 0) != 0) {
+    // KMB_TQ_SS=1: rows of at most 16 contraction features with all centroid stages resident go
+    // to the kernel that reads the sample operand from shared memory (two sample stages per
+    // quad); it measured 2 % slower than the kernel below
+    const size_t smem = sizeof(Ts2Smem) + 1024;
+    KMB_CHECK_CUDA(cudaFuncSetAttribute(lloyd_tc_quads_ss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    lloyd_tc_quads_ss_kernel<<<(unsigned)grid, tq_threads(4), smem, stream>>>(map_x, map_chi, map_clo, p);
+    KMB_CHECK_LAUNCH();
+    return KMB_OK;
+  }
   if (fold && d_pad == TC_KC && tc_small_mode() == 3) {
     // short rows: four quads, each owning whole sample tiles
     const size_t smem = sizeof(TqSmem) + 1024;

@@ -67,11 +67,14 @@ CHILD = textwrap.dedent("""
 """)
 
 
-@pytest.mark.parametrize("d,small", [(64, None), (128, None), (16, "3"), (28, "3"), (16, "1")],
-                         ids=["general_d64", "general_d128", "quads_d16", "quads_d28", "sixteen_d16"])
+@pytest.mark.parametrize("d,small", [(64, None), (128, None), (16, "3"), (28, "3"), (16, "1"), (16, "ss")],
+                         ids=["general_d64", "general_d128", "quads_d16", "quads_d28", "sixteen_d16",
+                              "quads_ss_d16"])
 def test_wait_that_runs_out_is_reported_and_the_context_survives(d, small):
     env = dict(os.environ)
-    if small is not None:
+    if small == "ss":
+        env["KMB_TQ_SS"] = "1"
+    elif small is not None:
         env["KMB_TC_SMALL"] = small
     proc = subprocess.run([sys.executable, "-c", CHILD, str(d)], cwd=ROOT, env=env,
                           capture_output=True, text=True, timeout=600)

@@ -25,8 +25,8 @@ VARIANTS = [
     # (environment, dtype the switch concerns, -k selection)
     ({"KMB_TC_SMALL": "0"}, "float32", SHORT_ROWS),       # general kernel with folded half norms
     ({"KMB_TC_SMALL": "1"}, "float32", SHORT_ROWS),       # sixteen workers on every tile
+    ({"KMB_TQ_SS": "1"}, "float32", SHORT_ROWS),          # rows of <= 16 features: sample operand from shared memory
     ({"KMB_TQ_FIDX": "0"}, "float32", SHORT_ROWS),        # quads: index search on the integer pipe
-    ({"KMB_TQ_FIDX": "1"}, "float32", SHORT_ROWS),        # quads: index search split between the pipes
     ({"KMB_TQ_ACC": "2"}, "float32", SHORT_ROWS),         # quads: two accumulators even when three fit
     ({"KMB_TQ_MMA": "1"}, "float32", SHORT_ROWS),         # quads: one MMA-issuing warp instead of two
     ({"KMB_TQ_QUADS": "5"}, "float32", SHORT_ROWS),       # quads: five quads where they fit

@@ -57,11 +57,11 @@ def _rank_main(rank, world, port, queue):
         ws = torch.as_tensor(w[start:stop]).to(dev)
         out = []
 
-        # --- Lloyd, teacher-forced: every round starts both runs from the SAME centres and does
+        # --- Lloyd, teacher-forced: every pass of the loop below starts both runs from the SAME centres and does
         # one iteration.  fp32 atomics make the cluster sums differ in the last bits from run to
         # run, and on this data a sample that sits on a boundary then sends a free-running loop
         # into one of two end states 24 labels apart (also between two single-GPU runs), so a
-        # free-running comparison is only made loosely at the end.  Round 1 relocates the two
+        # free-running comparison is only made loosely at the end.  The first pass relocates the two
         # empty clusters across shards.
         centres = torch.as_tensor(init).to(dev)
         for rnd in range(3):
