@@ -345,34 +345,52 @@ kpp_sample_kernel(const T* __restrict__ M, const double* __restrict__ bsum,
     found_s = ~0ull;
   }
   __syncthreads();
-  // --- level 1: first block whose inclusive prefix >= r
-  for (int64_t c0 = 0; c0 < nb; c0 += KPP_THREADS) {
-    const int64_t j = c0 + tid;
-    scan_s[tid] = (j < nb) ? bs[j] : 0.0;
+  // --- level 1: first block whose inclusive prefix >= r.  Every thread sums one contiguous
+  // segment of the block sums, one scan of the KPP_THREADS segment totals finds the segment in
+  // which the prefix first reaches r, and its thread walks that segment.
+  const int64_t seg = (nb + KPP_THREADS - 1) / KPP_THREADS;
+  const int64_t s0 = (int64_t)tid * seg, s1 = (s0 + seg < nb) ? s0 + seg : nb;
+  double mine = 0.0;
+  for (int64_t j = s0; j < s1; ++j) mine += bs[j];
+  scan_s[tid] = mine;
+  __syncthreads();
+  for (int o = 1; o < KPP_THREADS; o <<= 1) {
+    const double add = (tid >= o) ? scan_s[tid - o] : 0.0;
     __syncthreads();
-    for (int o = 1; o < KPP_THREADS; o <<= 1) {
-      const double add = (tid >= o) ? scan_s[tid - o] : 0.0;
-      __syncthreads();
-      scan_s[tid] += add;
-      __syncthreads();
-    }
-    const double incl = carry_s + scan_s[tid];
-    const double excl = (tid == 0) ? carry_s : carry_s + scan_s[tid - 1];
-    if (j < nb && incl >= r && !(excl >= r)) atomicMin(&found_s, (unsigned long long)j);
-    __syncthreads();
-    if (found_s != ~0ull) break;
-    if (tid == 0) carry_s += scan_s[KPP_THREADS - 1];
+    scan_s[tid] += add;
     __syncthreads();
   }
+  unsigned long long my_hit = ~0ull;
+  double my_before = 0.0;
+  {
+    const double incl = scan_s[tid];
+    const double excl = (tid == 0) ? 0.0 : scan_s[tid - 1];
+    if (s0 < s1 && incl >= r && !(excl >= r)) {
+      // this thread's segment: walk it from the prefix before it
+      double run = excl;
+      int64_t hit = s1 - 1;                        // rounding can leave r just past the last prefix
+      for (int64_t j = s0; j < s1; ++j) {
+        if (run + bs[j] >= r) {
+          hit = j;
+          break;
+        }
+        run += bs[j];
+      }
+      my_hit = (unsigned long long)hit;
+      my_before = run;                             // prefix before block `hit`
+      // with non-monotone prefixes (negative weights) several segments can qualify: lowest wins
+      atomicMin(&found_s, my_hit);
+    }
+  }
+  __syncthreads();
+  if (my_hit != ~0ull && found_s == my_hit) carry_s = my_before;
+  __syncthreads();
   if (found_s == ~0ull) {  // r beyond the last prefix: the running sum never reaches it
     if (tid == 0) cand[blockIdx.x] = (int32_t)(n - 1);
     return;
   }
   const int64_t blk = (int64_t)found_s;
-  // prefix before the block: carry_s (chunks before) + exclusive part inside the chunk
-  __syncthreads();
-  const int in_chunk = (int)(blk % KPP_THREADS);
-  const double before = carry_s + (in_chunk == 0 ? 0.0 : scan_s[in_chunk - 1]);
+  const double before = carry_s;                   // prefix before the block
   __syncthreads();
   // --- level 2: elements of block blk, KPP_THREADS at a time
   const int64_t e0 = blk * KPP_BLOCK;

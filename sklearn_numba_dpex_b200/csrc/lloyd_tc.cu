@@ -1451,15 +1451,10 @@ static int tc_launch(const float* X, const float* w, const float* C, const float
     // short rows: four quads, each owning whole sample tiles
     const size_t smem = sizeof(TqSmem) + 1024;
     // KMB_TQ_FIDX=0 keeps the whole index search on the integer pipe (A/B runs)
-    // KMB_TQ_QUADS=5 runs five quads where they fit (rows of at most two k-steps); measured
-    // slower than four (0.334 ms against 0.308 ms on n = 5 M, d = 14, k = 256)
-    const int d_eff = fold_at + 2 > d ? fold_at + 2 : d;
-    const bool five = d_eff <= 16 && tc_env_int("KMB_TQ_QUADS", 4) == 5;
     const bool fidx = tc_env_int("KMB_TQ_FIDX", 1) != 0;
-    auto kern = five ? (fidx ? lloyd_tc_quads_kernel<true, 5> : lloyd_tc_quads_kernel<false, 5>)
-                     : (fidx ? lloyd_tc_quads_kernel<true, 4> : lloyd_tc_quads_kernel<false, 4>);
+    auto kern = fidx ? lloyd_tc_quads_kernel<true, 4> : lloyd_tc_quads_kernel<false, 4>;
     KMB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)grid, tq_threads(five ? 5 : 4), smem, stream>>>(map_x, map_chi, map_clo, p);
+    kern<<<(unsigned)grid, tq_threads(4), smem, stream>>>(map_x, map_chi, map_clo, p);
     KMB_CHECK_LAUNCH();
     return KMB_OK;
   }

@@ -30,7 +30,7 @@ namespace kmb {
 
 constexpr int TQ_MMA_WARPS = 2;     // the issuing loops assume one or two warps (parity of g)
 constexpr int TQ_WORKER0 = 2 + TQ_MMA_WARPS;
-constexpr int TQ_MAX_QUADS = 5;
+constexpr int TQ_MAX_QUADS = 4;
 constexpr int tq_threads(int nq) { return (TQ_WORKER0 + 4 * nq) * 32; }
 constexpr int TQ_STAGES = 4;        // centroid stages (hi + lo = 32 KB each)
 
@@ -74,8 +74,9 @@ __device__ __forceinline__ bool tq_wait(void* bar, uint32_t parity, TqSmem* sm, 
 #define TQ_PROBE_TILE 40
 #define TQ_STAMP(cond, slot) KMB_PROF(if (blockIdx.x == 0 && lane == 0 && (cond)) sm->ts[slot] = clock64();)
 // FIDX: search the index of the maximum on the FMA pipe (see argmax32_fidx).  NQ: quads of worker
-// warps = sample tiles in flight (4, or 5 when the rows need at most two k-steps: five 32-column
-// sample slots leave room for two accumulators, five 64-column slots would leave one).
+// warps = sample tiles in flight (4; five, which fit when the rows need at most two k-steps,
+// measured 9 % slower).  Keeping the rows in shared memory from the split to the update instead
+// of fetching them again from L2 measured no gain either: the update's time is its reductions.
 template <bool FIDX, int NQ>
 __global__ void __launch_bounds__(tq_threads(NQ), 1)
 lloyd_tc_quads_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_chi,

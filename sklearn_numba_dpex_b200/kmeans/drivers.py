@@ -780,6 +780,7 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     s = stream_ptr(dev)
 
     if not sharded:
+        pots64 = torch.empty(t, dtype=torch.float64, device=dev)
         check(lib.kmb_kpp_init(code, ptr(X), ptr(w), first, None, ptr(M[0]), ptr(bsum[0]),
                                ptr(centers), ptr(indices), n, d, s), "kmb_kpp_init")
         check(lib.kmb_kpp_select(code, ptr(bsum[0]), None, 1, nb, None, ptr(best), ptr(total), None,
@@ -793,7 +794,10 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
                   "kmb_gather_rows")
             check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(cand_rows), ptr(M[cur]), ptr(best),
                                    ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
-            check(lib.kmb_kpp_select(code, ptr(bsum[nxt]), None, t, nb, ptr(pots), ptr(best),
+            # the t potentials by t CTAs, then the single-CTA choice (the select kernel alone
+            # would walk all t x nb block sums with one CTA: 40 us of a 270 us round at n = 2.5 M)
+            check(lib.kmb_kpp_potentials(ptr(bsum[nxt]), t, nb, ptr(pots64), s), "kmb_kpp_potentials")
+            check(lib.kmb_kpp_select(code, None, ptr(pots64), t, nb, ptr(pots), ptr(best),
                                      ptr(total), ptr(cand_rows), ptr(cand), ptr(centers),
                                      ptr(indices), c, d, s), "kmb_kpp_select")
             cur = nxt

@@ -29,7 +29,6 @@ VARIANTS = [
     ({"KMB_TQ_FIDX": "0"}, "float32", SHORT_ROWS),        # quads: index search on the integer pipe
     ({"KMB_TQ_ACC": "2"}, "float32", SHORT_ROWS),         # quads: two accumulators even when three fit
     ({"KMB_TQ_MMA": "1"}, "float32", SHORT_ROWS),         # quads: one MMA-issuing warp instead of two
-    ({"KMB_TQ_QUADS": "5"}, "float32", SHORT_ROWS),       # quads: five quads where they fit
     ({"KMB_TC_ROUND_LO": "0"}, "float32", "n60000_d64_k300 or n60000_d128_k130"),
     ({"KMB_F64_WM": "4"}, "float64", FP64_SHAPES),        # float64 MMA step, 128-sample CTAs
     ({"KMB_F64_WM": "2"}, "float64", FP64_SHAPES),        # float64 MMA step, 64-sample CTAs
