@@ -82,6 +82,32 @@ def test_errors_map_to_exceptions():
                                        ctypes.c_void_p(16), 1 << 20, None))
 
 
+def test_padding_features_flag_is_checked_before_any_launch():
+    """KMB_LLOYD_PAD_FEATURES: bits 8-9 of the flags of the step, assign, finalize and plan calls.
+    The argument checks run on the host, so they can be exercised without a GPU."""
+    from sklearn_numba_dpex_b200 import _cabi
+
+    assert [_cabi.pad_features_flag(n) for n in range(4)] == [0, 256, 512, 768]
+    with pytest.raises(ValueError):
+        _cabi.pad_features_flag(4)
+    p = ctypes.c_void_p(256)
+    lib = _cabi.lib
+    # three padding features in rows of two: rejected by every entry point that takes the flag
+    with pytest.raises(ValueError, match="padding features"):
+        _cabi.check(lib.kmb_lloyd_step(0, _cabi.ALGO_CUDA_CORE, p, p, p, p, p, p, p, 1, 10, 2, 2,
+                                       _cabi.pad_features_flag(3), p, 1 << 20, None))
+    with pytest.raises(ValueError, match="padding features"):
+        _cabi.check(lib.kmb_assign_labels(0, _cabi.ALGO_CUDA_CORE, p, p, p, p, 10, 2, 2,
+                                          _cabi.pad_features_flag(2), p, 1 << 20, None))
+    with pytest.raises(ValueError, match="padding features"):
+        _cabi.check(lib.kmb_lloyd_finalize(0, p, 1, p, _cabi.FIN_MERGE | _cabi.pad_features_flag(3), p, p,
+                                           p, p, p, p, 2, 2, p, 1 << 20, None))
+    # unknown bits are still rejected
+    with pytest.raises(ValueError, match="unknown flag bits"):
+        _cabi.check(lib.kmb_lloyd_step(0, _cabi.ALGO_CUDA_CORE, p, p, p, p, p, p, p, 1, 10, 2, 2,
+                                       1 << 12, p, 1 << 20, None))
+
+
 def test_engine_rejects_cpu_only_process():
     import torch
 
