@@ -171,6 +171,71 @@ col_sums_flat_kernel(const T* __restrict__ X, double* __restrict__ partial, int6
   }
 }
 
+// One aligned 16-byte read-only load: four floats or two doubles.
+__device__ __forceinline__ void load_vec16(float (&dst)[4], const float* src) {
+  const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+  dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+__device__ __forceinline__ void load_vec16(double (&dst)[2], const double* src) {
+  const double2 v = __ldg(reinterpret_cast<const double2*>(src));
+  dst[0] = v.x; dst[1] = v.y;
+}
+
+// The same loads from memory that the kernel also writes (no read-only path).
+__device__ __forceinline__ void load_vec16_rw(float (&dst)[4], const float* src) {
+  const float4 v = *reinterpret_cast<const float4*>(src);
+  dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+__device__ __forceinline__ void load_vec16_rw(double (&dst)[2], const double* src) {
+  const double2 v = *reinterpret_cast<const double2*>(src);
+  dst[0] = v.x; dst[1] = v.y;
+}
+
+// Rows that are whole 16-byte chunks (d a multiple of VEC = 16 / sizeof(T), at most RS_THREADS
+// chunks per row, aligned base): the same flat sweep with 16-byte loads.  A thread strides by a
+// multiple of the row length in chunks, so it always meets the same VEC features, and keeps one
+// float64 sum for each of them; two loads are in flight per thread.
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+col_sums_vec_kernel(const T* __restrict__ X, double* __restrict__ partial, int64_t n, int d, int slots) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  __shared__ double sh[VEC][RS_THREADS];
+  const int t = threadIdx.x;
+  const int cpr = d / VEC;                         // chunks per row
+  double s[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) s[v] = 0.0;
+  const int64_t total = n * (int64_t)cpr;
+  if (t < slots) {
+    const int64_t step = (int64_t)gridDim.x * slots;
+    int64_t e = (int64_t)blockIdx.x * slots + t;
+    for (; e + step < total; e += 2 * step) {
+      T a[VEC], b[VEC];
+      load_vec16(a, X + e * VEC);
+      load_vec16(b, X + (e + step) * VEC);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) s[v] += (double)a[v];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) s[v] += (double)b[v];
+    }
+    if (e < total) {
+      T a[VEC];
+      load_vec16(a, X + e * VEC);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) s[v] += (double)a[v];
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) sh[v][t] = s[v];
+  __syncthreads();
+  if (t < d) {
+    const int c = t / VEC, v = t % VEC;            // feature t = chunk c of a row, component v
+    double acc = 0.0;
+    for (int u = c; u < slots; u += cpr) acc += sh[v][u];
+    partial[(int64_t)t * gridDim.x + blockIdx.x] = acc;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(RS_THREADS)
 sum_kernel(const T* __restrict__ v, int64_t len, int square, double* __restrict__ partial) {
@@ -191,6 +256,50 @@ add_row_vector_kernel(T* __restrict__ X, int64_t total, int d, const T* __restri
   for (int64_t e = (int64_t)blockIdx.x * RS_THREADS + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * RS_THREADS)
     X[e] = X[e] + sign * vec[e % d];
+}
+
+__device__ __forceinline__ void store_vec16(float* dst, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_vec16(double* dst, const double (&v)[2]) {
+  *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
+}
+
+// The same update for rows that are whole 16-byte chunks: a thread strides by a multiple of the
+// row length in chunks, so it always meets the same features, whose part of the vector it keeps
+// in registers; 16-byte loads and stores, two chunks in flight, no division in the loop.
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS)
+add_row_vector_vec_kernel(T* __restrict__ X, int64_t n, int d, const T* __restrict__ vec, T sign, int slots) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int t = threadIdx.x;
+  if (t >= slots) return;
+  const int cpr = d / VEC;
+  const int64_t total = n * (int64_t)cpr;
+  T add[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) add[v] = sign * vec[(t % cpr) * VEC + v];
+  const int64_t step = (int64_t)gridDim.x * slots;
+  int64_t e = (int64_t)blockIdx.x * slots + t;
+  for (; e + step < total; e += 2 * step) {
+    T a[VEC], b[VEC];
+    load_vec16_rw(a, X + e * VEC);
+    load_vec16_rw(b, X + (e + step) * VEC);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      a[v] = a[v] + add[v];
+      b[v] = b[v] + add[v];
+    }
+    store_vec16(X + e * VEC, a);
+    store_vec16(X + (e + step) * VEC, b);
+  }
+  if (e < total) {
+    T a[VEC];
+    load_vec16_rw(a, X + e * VEC);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) a[v] = a[v] + add[v];
+    store_vec16(X + e * VEC, a);
+  }
 }
 
 // One block per relocated cluster (kmeans/kernels/utils.py:21-76 of the reference).
@@ -331,9 +440,14 @@ int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* 
   KMB_REQUIRE(X && out && n >= 0 && d > 0, "kmb_col_sums: bad arguments");
   cudaStream_t s = (cudaStream_t)stream;
   int grid;
-  const bool flat = d <= 32;
+  const int vec = dtype == KMB_F32 ? 4 : 2;
+  const bool vec_ok = d % vec == 0 && d / vec <= RS_THREADS && d <= RS_THREADS && ((uintptr_t)X & 15) == 0;
+  const int vslots = vec_ok ? (RS_THREADS / (d / vec)) * (d / vec) : 0;
+  const bool flat = !vec_ok && d <= 32;
   const int slots = flat ? (RS_THREADS / d) * d : 0;
-  if (flat) {
+  if (vec_ok) {
+    grid = scan_grid((int64_t)vslots * 8, n * (int64_t)(d / vec) > 0 ? n * (int64_t)(d / vec) : 1);
+  } else if (flat) {
     grid = scan_grid(slots, n * (int64_t)d > 0 ? n * (int64_t)d : 1);
   } else {
     grid = scan_grid(64, n > 0 ? n : 1);
@@ -344,7 +458,9 @@ int kmb_col_sums(int dtype, const void* X, int64_t n, int d, double* out, void* 
     return KMB_ERR_WORKSPACE;
   }
   KMB_DISPATCH_DTYPE(dtype, {
-    if (flat) {
+    if (vec_ok) {
+      col_sums_vec_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (double*)workspace, n, d, vslots);
+    } else if (flat) {
       col_sums_flat_kernel<T><<<grid, RS_THREADS, 0, s>>>((const T*)X, (double*)workspace, n, d, slots);
     } else {
       const int64_t rpb = ceil_div(n > 0 ? n : 1, grid);
@@ -381,10 +497,19 @@ int kmb_add_row_vector(int dtype, void* X, int64_t n, int d, const void* vec, do
   KMB_REQUIRE(X && vec && n >= 0 && d > 0, "kmb_add_row_vector: bad arguments");
   if (n == 0) return KMB_OK;
   const int64_t total = n * (int64_t)d;
-  const int grid = scan_grid(RS_THREADS * 4, total);
+  const int vw = dtype == KMB_F32 ? 4 : 2;
+  const bool vec_ok = d % vw == 0 && d / vw <= RS_THREADS && ((uintptr_t)X & 15) == 0;
   KMB_DISPATCH_DTYPE(dtype, {
-    add_row_vector_kernel<T><<<grid, RS_THREADS, 0, (cudaStream_t)stream>>>((T*)X, total, d,
-                                                                            (const T*)vec, (T)sign);
+    if (vec_ok) {
+      const int cpr = d / vw, slots = (RS_THREADS / cpr) * cpr;
+      const int grid = scan_grid((int64_t)slots * 8, n * (int64_t)cpr);
+      add_row_vector_vec_kernel<T><<<grid, RS_THREADS, 0, (cudaStream_t)stream>>>((T*)X, n, d, (const T*)vec,
+                                                                                  (T)sign, slots);
+    } else {
+      const int grid = scan_grid(RS_THREADS * 4, total);
+      add_row_vector_kernel<T><<<grid, RS_THREADS, 0, (cudaStream_t)stream>>>((T*)X, total, d,
+                                                                              (const T*)vec, (T)sign);
+    }
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;
