@@ -181,6 +181,70 @@ __device__ __forceinline__ void load_vec16(double (&dst)[2], const double* src) 
   dst[0] = v.x; dst[1] = v.y;
 }
 
+// Inertia for rows that are whole aligned 16-byte chunks, at most 32 of them: G lanes (the
+// power of two >= chunks per row) share a row, each with one chunk of the row and the same chunk
+// of the row's centroid, so both reads are coalesced, nothing is staged, and a warp has
+// 4 x 32 / G rows in flight.  The squared differences are summed over the lane's chunk in
+// ascending feature order and then over the lanes by a shuffle tree.
+constexpr int INL_THREADS = 256;
+constexpr int INL_UNROLL = 4;
+template <typename T>
+__global__ void __launch_bounds__(INL_THREADS)
+inertia_lanes_kernel(const T* __restrict__ X, const T* __restrict__ w, const T* __restrict__ C,
+                     const uint32_t* __restrict__ labels, T* __restrict__ per_sample,
+                     double* __restrict__ partial, int64_t n, int d, int k, int G) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  __shared__ double red[32];
+  const int cpr = d / VEC;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int li = lane & (G - 1), sub = lane / G, rpw = 32 / G;
+  const int64_t n_warps = (int64_t)gridDim.x * (INL_THREADS / 32);
+  const int64_t rows_per_step = (int64_t)rpw * INL_UNROLL;
+  double acc = 0.0;
+  for (int64_t r0 = ((int64_t)blockIdx.x * (INL_THREADS / 32) + warp) * rows_per_step; r0 < n;
+       r0 += n_warps * rows_per_step) {
+    T xv[INL_UNROLL][VEC], cv[INL_UNROLL][VEC];
+    bool valid[INL_UNROLL];
+    uint32_t lab[INL_UNROLL];
+#pragma unroll
+    for (int u = 0; u < INL_UNROLL; ++u) {
+      const int64_t i = r0 + (int64_t)u * rpw + sub;
+      valid[u] = i < n;
+      lab[u] = valid[u] ? __ldg(labels + i) : 0u;
+      if (lab[u] >= (uint32_t)k) lab[u] = 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < INL_UNROLL; ++u) {
+      const int64_t i = r0 + (int64_t)u * rpw + sub;
+      if (valid[u] && li < cpr) {
+        load_vec16(xv[u], X + i * (int64_t)d + li * VEC);
+        load_vec16(cv[u], C + (int64_t)lab[u] * d + li * VEC);
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) xv[u][j] = cv[u][j] = T(0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < INL_UNROLL; ++u) {
+      T sq = T(0);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const T diff = xv[u][j] - cv[u][j];
+        sq = fma(diff, diff, sq);
+      }
+      for (int o = G >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      const int64_t i = r0 + (int64_t)u * rpw + sub;
+      if (valid[u] && li == 0) {
+        const T v = sq * (w ? w[i] : T(1));
+        if (per_sample) per_sample[i] = v;
+        acc += (double)v;
+      }
+    }
+  }
+  const double tot = block_sum(acc, red);
+  if (threadIdx.x == 0 && partial) partial[blockIdx.x] = tot;
+}
+
 // The same loads from memory that the kernel also writes (no read-only path).
 __device__ __forceinline__ void load_vec16_rw(float (&dst)[4], const float* src) {
   const float4 v = *reinterpret_cast<const float4*>(src);
@@ -415,6 +479,33 @@ int kmb_inertia(int dtype, const void* X, const void* w, const void* C, const ui
                 (size_t)grid * sizeof(double), workspace_bytes);
       return KMB_ERR_WORKSPACE;
     }
+  }
+  // rows of whole aligned chunks, at most 32 of them: the lanes-per-row kernel, nothing staged
+  if (vec && (((uintptr_t)C & 15) == 0) && d / vecn <= 32 && n > 0) {
+    int GL = 1;
+    while (GL < d / vecn) GL <<= 1;
+    const int64_t rows_per_cta = (int64_t)(INL_THREADS / 32) * (32 / GL) * INL_UNROLL;
+    int64_t g2 = ceil_div(n, rows_per_cta);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (g2 > cap) g2 = cap;
+    if (g2 > RS_MAX_BLOCKS) g2 = RS_MAX_BLOCKS;
+    if (total && (workspace == nullptr || workspace_bytes < (size_t)g2 * sizeof(double))) {
+      set_error("kmb_inertia: workspace of %zu bytes needed, %zu given", (size_t)g2 * sizeof(double),
+                workspace_bytes);
+      return KMB_ERR_WORKSPACE;
+    }
+    KMB_DISPATCH_DTYPE(dtype, {
+      inertia_lanes_kernel<T><<<(unsigned)g2, INL_THREADS, 0, s>>>(
+          (const T*)X, (const T*)w, (const T*)C, labels, (T*)per_sample,
+          total ? (double*)workspace : nullptr, n, d, k, GL);
+      KMB_CHECK_LAUNCH();
+      if (total) {
+        sum_partials_kernel<T><<<1, 256, 0, s>>>((const double*)workspace, (int)g2, (int)g2, (T*)total,
+                                                 nullptr);
+        KMB_CHECK_LAUNCH();
+      }
+    });
+    return KMB_OK;
   }
   KMB_DISPATCH_DTYPE(dtype, {
     const int aligned = vec ? 1 : 0;
