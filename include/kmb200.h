@@ -76,13 +76,13 @@ enum {
 };
 
 /* Bits 8-9 of the `flags` of kmb_lloyd_step, kmb_assign_labels, kmb_lloyd_finalize and
- * kmb_lloyd_plan_launch: how
- * many TRAILING features of X and of the centroids are zero padding added by the caller (0..3; a
- * caller that rounded d up to a multiple of 4 so that KMB_ALGO_TF32X3 accepts it).  The
- * tensor-core step then keeps its two extra contraction features (the folded half norms) in
- * those slots instead of widening the rows: d = 14 padded to 16 contracts over 16 features
- * instead of 18 -> 24.  The same value must be given to the finalize call that prepares the
- * operands and to the step that uses them.  No counterpart in the reference. */
+ * kmb_lloyd_plan_launch: how many TRAILING features of X and of the centroids are zero padding
+ * added by the caller (0..3; a caller that rounded d up to a multiple of 4 so that
+ * KMB_ALGO_TF32X3 accepts it).  The tensor-core step then keeps its two extra contraction
+ * features (the folded half norms) in those slots instead of widening the rows: d = 14 padded to
+ * 16 contracts over 16 features instead of 18 -> 24.  The same value must be given to the
+ * finalize call that prepares the operands and to the step that uses them; the padding features
+ * of X and of every centroid must really be zero.  No counterpart in the reference. */
 #define KMB_LLOYD_PAD_FEATURES(n) (((n) & 3) << 8)
 #define KMB_LLOYD_PAD_MASK (3 << 8)
 
