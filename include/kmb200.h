@@ -312,6 +312,31 @@ int kmb_kpp_select(int dtype, const double* bsum, const double* pots_in, int t, 
                    const int32_t* cand, void* centers, int32_t* indices, int c, int d,
                    void* stream);
 
+/* Row-sharded seeding, two glue kernels of a round (the reference seeds on one device: no
+ * counterpart; they stand where drivers.py:897-908 picks candidates and potentials on the host).
+ *
+ * kmb_kpp_pick_owned: every shard searched its own rows for each of the t thresholds
+ * r[tau] = u[tau] * total (product in dtype, compared in float64); the valid answer is that of
+ * the OWNER, the first shard whose inclusive prefix ends[w] reaches r (the last shard when
+ * rounding leaves none).  `gathered` is the all-gather over the shards of (t, d + 1) blocks: a
+ * candidate row followed by its LOCAL row id (the int32's bit pattern in a float32 column, its
+ * value in a float64 one).  Writes cand_global[tau] = id + rows_offset[owner] and
+ * rows_global (t, d).
+ *
+ * kmb_kpp_select_shards: kmb_kpp_select on shard_pots (n_shards, t), the all-gather of every
+ * shard's float64 potentials: pots[tau] = sum over the shards in ascending order; the choice is
+ * committed as kmb_kpp_select commits it; ends_out[w] = inclusive prefix over the shards of the
+ * chosen candidate's potentials and *offset_out = the exclusive prefix of shard `shard`, which
+ * is what the next round's kmb_kpp_sample and kmb_kpp_pick_owned take. */
+int kmb_kpp_pick_owned(int dtype, const void* gathered, int n_shards, int t, int d,
+                       const double* ends, const void* u, const void* total,
+                       const int64_t* rows_offset, int32_t* cand_global, void* rows_global,
+                       void* stream);
+int kmb_kpp_select_shards(int dtype, const double* shard_pots, int n_shards, int shard, int t,
+                          void* pots, int32_t* best, void* total, const void* cand_rows,
+                          const int32_t* cand, void* centers, int32_t* indices, int c, int d,
+                          double* ends_out, double* offset_out, void* stream);
+
 /* ---- data preparation (kmeans/drivers.py:436-589) --------------------------------- */
 /* out[f] = sum_i X[i,f] in float64 (d doubles). Replaces make_sum_reduction_2d_kernel
  * axis=1 (common/reductions.py:214-393) at drivers.py:478. */

@@ -71,6 +71,9 @@ _SIGNATURES = {
     "kmb_gather_rows": (c_int, [c_int, _P, _P, c_int, c_int, _P, _P]),
     "kmb_kpp_step": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, _P]),
     "kmb_kpp_potentials": (c_int, [_P, c_int, c_int64, _P, _P]),
+    "kmb_kpp_pick_owned": (c_int, [c_int, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
+    "kmb_kpp_select_shards": (c_int, [c_int, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int,
+                                      c_int, _P, _P, _P]),
     "kmb_kpp_select": (c_int, [c_int, _P, _P, c_int, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int,
                                c_int, _P]),
     "kmb_col_sums": (c_int, [c_int, _P, c_int64, c_int, _P, _P, c_size_t, _P]),

@@ -477,6 +477,72 @@ kpp_select_kernel(const double* __restrict__ bsum, const double* __restrict__ po
       centers[(int64_t)c * d + f] = cand_rows[(int64_t)best_s * d + f];
 }
 
+// Row shards: one block per trial picks the owner shard's candidate out of the gathered ones.
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_pick_owned_kernel(const T* __restrict__ gathered, int n_shards, int t, int d,
+                      const double* __restrict__ ends, const T* __restrict__ u,
+                      const T* __restrict__ total, const int64_t* __restrict__ rows_offset,
+                      int32_t* __restrict__ cand_global, T* __restrict__ rows_global) {
+  const int tau = blockIdx.x;
+  const double r = (double)(u[tau] * total[0]);
+  int owner = 0;
+  for (int w = 0; w < n_shards; ++w) owner += (ends[w] < r) ? 1 : 0;
+  if (owner > n_shards - 1) owner = n_shards - 1;
+  const T* src = gathered + ((int64_t)owner * t + tau) * (d + 1);
+  for (int f = threadIdx.x; f < d; f += KPP_THREADS) rows_global[(int64_t)tau * d + f] = src[f];
+  if (threadIdx.x == 0) {
+    int32_t id;
+    if (sizeof(T) == 4) {
+      id = __float_as_int((float)src[d]);          // the column carries the id's bit pattern
+    } else {
+      id = (int32_t)src[d];
+    }
+    cand_global[tau] = (int32_t)((int64_t)id + rows_offset[owner]);
+  }
+}
+
+// Row shards, single CTA: potentials summed over the shards in ascending order, argmin (lowest
+// trial on ties), commit of the centre, and the prefix of the chosen candidate's shares.
+template <typename T>
+__global__ void __launch_bounds__(KPP_THREADS)
+kpp_select_shards_kernel(const double* __restrict__ shard_pots, int n_shards, int shard, int t,
+                         T* __restrict__ pots, int32_t* __restrict__ best, T* __restrict__ total,
+                         const T* __restrict__ cand_rows, const int32_t* __restrict__ cand,
+                         T* __restrict__ centers, int32_t* __restrict__ indices, int c, int d,
+                         double* __restrict__ ends_out, double* __restrict__ offset_out) {
+  __shared__ int best_s;
+  if (threadIdx.x == 0) {
+    int bi = 0;
+    T bv = T(0);
+    for (int tau = 0; tau < t; ++tau) {
+      double tot = 0.0;
+      for (int w = 0; w < n_shards; ++w) tot += shard_pots[(int64_t)w * t + tau];
+      const T pv = (T)tot;
+      if (pots) pots[tau] = pv;
+      if (tau == 0 || pv < bv) {
+        bv = pv;
+        bi = tau;
+      }
+    }
+    best_s = bi;
+    *best = bi;
+    *total = bv;
+    if (indices && cand) indices[c] = cand[bi];
+    double run = 0.0, mine = 0.0;
+    for (int w = 0; w < n_shards; ++w) {
+      if (w == shard) mine = run;
+      run += shard_pots[(int64_t)w * t + bi];
+      if (ends_out) ends_out[w] = run;
+    }
+    if (offset_out) *offset_out = mine;
+  }
+  __syncthreads();
+  if (centers && cand_rows)
+    for (int f = threadIdx.x; f < d; f += KPP_THREADS)
+      centers[(int64_t)c * d + f] = cand_rows[(int64_t)best_s * d + f];
+}
+
 // pots[tau] = sum_b bsum[tau, b] in float64, fixed order; one block per trial.
 __global__ void __launch_bounds__(KPP_THREADS)
 kpp_potentials_kernel(const double* __restrict__ bsum, int64_t nb, double* __restrict__ pots) {
@@ -625,6 +691,38 @@ int kmb_kpp_select(int dtype, const double* bsum, const double* pots_in, int t, 
     kpp_select_kernel<T><<<1, KPP_THREADS, 0, (cudaStream_t)stream>>>(
         bsum, pots_in, t, nb, (T*)pots, best, (T*)total, (const T*)cand_rows, cand, (T*)centers,
         indices, c, d);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_kpp_pick_owned(int dtype, const void* gathered, int n_shards, int t, int d,
+                       const double* ends, const void* u, const void* total,
+                       const int64_t* rows_offset, int32_t* cand_global, void* rows_global,
+                       void* stream) {
+  KMB_REQUIRE(gathered && ends && u && total && rows_offset && cand_global && rows_global,
+              "kmb_kpp_pick_owned: NULL argument");
+  KMB_REQUIRE(n_shards > 0 && t > 0 && t <= KPP_MAX_T && d > 0, "kmb_kpp_pick_owned: bad sizes");
+  KMB_DISPATCH_DTYPE(dtype, {
+    kpp_pick_owned_kernel<T><<<t, KPP_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)gathered, n_shards, t, d, ends, (const T*)u, (const T*)total, rows_offset,
+        cand_global, (T*)rows_global);
+    KMB_CHECK_LAUNCH();
+  });
+  return KMB_OK;
+}
+
+int kmb_kpp_select_shards(int dtype, const double* shard_pots, int n_shards, int shard, int t,
+                          void* pots, int32_t* best, void* total, const void* cand_rows,
+                          const int32_t* cand, void* centers, int32_t* indices, int c, int d,
+                          double* ends_out, double* offset_out, void* stream) {
+  KMB_REQUIRE(shard_pots && best && total, "kmb_kpp_select_shards: NULL argument");
+  KMB_REQUIRE(n_shards > 0 && shard >= 0 && shard < n_shards && t > 0 && t <= KPP_MAX_T && c >= 0 && d > 0,
+              "kmb_kpp_select_shards: bad sizes");
+  KMB_DISPATCH_DTYPE(dtype, {
+    kpp_select_shards_kernel<T><<<1, KPP_THREADS, 0, (cudaStream_t)stream>>>(
+        shard_pots, n_shards, shard, t, (T*)pots, best, (T*)total, (const T*)cand_rows, cand,
+        (T*)centers, indices, c, d, ends_out, offset_out);
     KMB_CHECK_LAUNCH();
   });
   return KMB_OK;

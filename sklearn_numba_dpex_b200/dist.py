@@ -161,9 +161,22 @@ def pick_owned_candidates(thresholds, ends, cand_local, rows_local, rows_offset)
     d = int(rows_local.shape[1])
     owner = torch.clamp((ends.reshape(1, -1) < thresholds.reshape(-1, 1).to(ends.dtype)).sum(dim=1),
                         max=world - 1)
-    all_cand = all_gather_same(cand_local.reshape(1, t)).to(torch.int64)      # (world, t)
-    all_rows = all_gather_same(rows_local.reshape(1, t, d))                    # (world, t, d)
-    cand_global = (torch.gather(all_cand, 0, owner.reshape(1, t))[0] + rows_offset[owner])
-    rows_global = torch.gather(all_rows, 0, owner.reshape(1, t, 1).expand(1, t, d))[0]
-    return cand_global.to(torch.int32).contiguous(), rows_global.contiguous()
+    # ONE collective for ids and rows: the ids travel as an extra column of the rows (bit pattern
+    # of the int32 in a float32 column, exact value in a float64 one)
+    dt = rows_local.dtype
+    ids32 = cand_local.to(torch.int32).reshape(t, 1)
+    id_col = ids32.view(torch.float32) if dt == torch.float32 else ids32.to(dt)
+    packed = all_gather_same(torch.cat([rows_local, id_col], dim=1).reshape(1, t, d + 1))   # (world, t, d + 1)
+    picked = torch.gather(packed, 0, owner.reshape(1, t, 1).expand(1, t, d + 1))[0]        # (t, d + 1)
+    ids = picked[:, d].contiguous()
+    ids = ids.view(torch.int32) if dt == torch.float32 else ids.to(torch.int32)
+    cand_global = ids.to(torch.int64) + rows_offset[owner]
+    return cand_global.to(torch.int32).contiguous(), picked[:, :d].contiguous()
+
+
+def prefix_from_shares(shares):
+    """(ends, offset) of `shard_prefix` from shares that every rank already holds: `shares` is a
+    float64 tensor (world,), rank r's share of a global sum, identical on all ranks."""
+    ends = torch.cumsum(shares, 0)
+    return ends, ends[rank()] - shares[rank()]
 

@@ -804,7 +804,7 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
         return centers.T, indices
 
     # ---- row shards: every rank scans its own rows; per round one all-gather of the local
-    # potentials and candidates and one all-reduce of the t candidate potentials, no host sync
+    # candidates (row + id) and one of the local potentials, two glue kernels, no host sync
     world, me = dist.world_size(), dist.rank()
     first_row = torch.zeros(d, dtype=dt, device=dev)
     if row0 <= first < row0 + n:
@@ -819,25 +819,35 @@ def kmeans_plusplus(X_t, sample_weight, n_clusters, random_state):
     total.copy_(glob.to(dt))
     rows_off = torch.tensor([sum(counts[:r]) for r in range(world)], dtype=torch.int64, device=dev)
     cur = 0
+    ends0, my_offset = dist.shard_prefix(local_tot)                  # float64
+    ends = ends0.contiguous().clone()                                # (world,) inclusive prefix of the shares
+    offset = my_offset.reshape(1).contiguous().clone()               # this shard's exclusive prefix
+    cand_glob = torch.empty(t, dtype=torch.int32, device=dev)
+    rows_glob = torch.empty((t, d), dtype=dt, device=dev)
     for c in range(1, k):
         nxt = 1 - cur
-        ends, my_offset = dist.shard_prefix(local_tot)               # float64
-        offset = my_offset.reshape(1).contiguous()                    # float64, as the kernel's scan
         check(lib.kmb_kpp_sample(code, ptr(M[cur]), ptr(bsum[cur]), ptr(best), ptr(total),
                                  ptr(u[c - 1]), ptr(offset), t, ptr(cand), n, s), "kmb_kpp_sample")
         check(lib.kmb_gather_rows(code, ptr(X), ptr(cand), t, d, ptr(cand_rows), s),
               "kmb_gather_rows")
-        # owner of trial tau: first shard whose inclusive prefix reaches r = u * total
-        r = (u[c - 1] * total[0]).to(torch.float64)
-        cand_glob, rows_glob = dist.pick_owned_candidates(r, ends, cand, cand_rows, rows_off)
+        # ONE all-gather of (row, local id) per trial; the owner of trial tau (first shard whose
+        # inclusive prefix reaches r = u * total) is picked out of it by one kernel
+        id_col = cand.view(torch.float32) if dt == torch.float32 else cand.to(dt)
+        gathered = dist.all_gather_same(torch.cat([cand_rows, id_col.reshape(t, 1)], dim=1)
+                                        .reshape(1, t, d + 1))
+        check(lib.kmb_kpp_pick_owned(code, ptr(gathered), world, t, d, ptr(ends), ptr(u[c - 1]),
+                                     ptr(total), ptr(rows_off), ptr(cand_glob), ptr(rows_glob), s),
+              "kmb_kpp_pick_owned")
         check(lib.kmb_kpp_step(code, ptr(X), ptr(w), ptr(rows_glob), ptr(M[cur]), ptr(best),
                                ptr(M[nxt]), ptr(bsum[nxt]), n, d, t, s), "kmb_kpp_step")
         check(lib.kmb_kpp_potentials(ptr(bsum[nxt]), t, nb, ptr(pots64), s), "kmb_kpp_potentials")
-        local_pots = pots64.clone()
-        dist.all_reduce_sum_(pots64)
-        check(lib.kmb_kpp_select(code, None, ptr(pots64), t, nb, ptr(pots), ptr(best), ptr(total),
-                                 ptr(rows_glob), ptr(cand_glob), ptr(centers), ptr(indices), c, d,
-                                 s), "kmb_kpp_select")
-        local_tot = local_pots.gather(0, best.to(torch.int64))
+        # one all-gather of every shard's t potentials serves two purposes: their sum over the
+        # shards (the same fixed order on every rank) is what the choice is made on, and the
+        # chosen candidate's column holds the shares the next round's sampler needs
+        shard_pots = dist.all_gather_same(pots64.reshape(1, t))      # (world, t)
+        check(lib.kmb_kpp_select_shards(code, ptr(shard_pots), world, me, t, ptr(pots), ptr(best),
+                                        ptr(total), ptr(rows_glob), ptr(cand_glob), ptr(centers),
+                                        ptr(indices), c, d, ptr(ends), ptr(offset), s),
+              "kmb_kpp_select_shards")
         cur = nxt
     return centers.T, indices
