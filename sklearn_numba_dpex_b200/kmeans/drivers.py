@@ -132,6 +132,7 @@ class LloydState:
         self._operands_slot = None               # centroid slot whose split operands sit in ws
         self.kernel_launches = 0
         self.event_hook = None                   # callable(kind, it) around the fused kernel
+        self._calm = False                       # the last finished iteration had no empty cluster
         check(lib.kmb_half_l2_norm(self.dtype, ptr(self.C), ptr(self.h), k, d, stream_ptr(dev)),
               "kmb_half_l2_norm")
         self.kernel_launches += 1
@@ -318,6 +319,7 @@ class LloydState:
         if n_empty > 0:
             self._relocate(n_empty)
             _, _, shift = self._wait_status(self.it)
+        self._calm = n_empty == 0
         self.it += 1
         return n_empty, changed, shift
 
@@ -327,9 +329,10 @@ class LloydState:
         unchanged, armed after the second iteration as in the reference).  Returns a dict with
         n_iter, strict, shift, n_relocation_events, n_empty_max.
 
-        Pipelined: iteration i + 1 is enqueued BEFORE the status of iteration i is read, so the
-        GPU never idles while the host decides; it is run again only when iteration i had to
-        relocate empty clusters, and simply ignored when iteration i ended the loop.  With a
+        Pipelined: iteration i + 1 is enqueued BEFORE the status of iteration i is read (once an
+        iteration without empty clusters has been seen), so the GPU never idles while the host
+        decides; it is run again only when iteration i had to relocate empty clusters, and simply
+        ignored when iteration i ended the loop.  With a
         callback (verbose mode) the loop runs unpipelined.  `stop_on_strict=False` keeps iterating
         after the labels have stopped changing (the benchmark times a fixed number of steps)."""
         T = np.float32 if self.X.dtype == torch.float32 else np.float64
@@ -341,7 +344,10 @@ class LloydState:
             if not launched:
                 self._launch(self.it)
             launched = False
-            speculate = pipelined and n_iter + 1 < max_iter
+            # speculate only when the last known iteration had no empty cluster: a relocation
+            # throws the speculative iteration away, a whole pass over the samples (the first
+            # iterations from a random-row init usually relocate)
+            speculate = pipelined and n_iter + 1 < max_iter and self._calm
             if speculate:
                 self._launch(self.it + 1)
             n_empty, changed, shift_total = self._wait_status(self.it)
@@ -354,6 +360,7 @@ class LloydState:
                 speculate = False
             events += int(n_empty > 0)
             n_empty_max = max(n_empty_max, n_empty)
+            self._calm = n_empty == 0
             self.it += 1
             launched = speculate
             n_iter += 1
