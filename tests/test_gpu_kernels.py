@@ -468,3 +468,69 @@ def test_run_can_ignore_strict_convergence_and_counts_steps():
     st.run(3, -1.0, stop_on_strict=False)
     st.event_hook = None
     assert seen == [("pre", 25), ("post", 25), ("pre", 26), ("post", 26), ("pre", 27), ("post", 27)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sharded_seeding_glue_kernels(dtype):
+    """kmb_kpp_pick_owned and kmb_kpp_select_shards (the two glue kernels of a row-sharded
+    k-means++ round) on gathered buffers made up here for four shards, against numpy."""
+    from sklearn_numba_dpex_b200._cabi import check, dtype_code, lib, ptr, stream_ptr
+
+    rng = np.random.default_rng(11)
+    world, t, d, c = 4, 6, 10, 3
+    tdt = torch.float32 if dtype == np.float32 else torch.float64
+    code = dtype_code(tdt)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    s = stream_ptr(dev)
+
+    # ---- pick_owned: shares -> ends; thresholds on, before and after shard boundaries
+    shares = rng.uniform(1.0, 3.0, size=world)
+    ends = np.cumsum(shares)
+    total = dtype(ends[-1])
+    u = np.array([0.0, shares[0] / ends[-1], 0.3, 0.55, 0.999, 1.5], dtype=dtype)   # last one beyond every prefix
+    rows = rng.standard_normal((world, t, d)).astype(dtype)
+    ids = rng.integers(0, 1000, size=(world, t)).astype(np.int32)
+    rows_off = np.array([0, 1000, 2000, 3000], dtype=np.int64)
+    id_col = ids.view(np.float32) if dtype == np.float32 else ids.astype(dtype)
+    gathered = np.concatenate([rows, id_col[:, :, None]], axis=2)
+    r = (u * total).astype(np.float64)
+    owner = np.minimum((ends[None, :] < r[:, None]).sum(axis=1), world - 1)
+    want_ids = ids[owner, np.arange(t)].astype(np.int64) + rows_off[owner]
+    want_rows = rows[owner, np.arange(t)]
+    cand = torch.empty(t, dtype=torch.int32, device=dev)
+    out_rows = torch.empty((t, d), dtype=tdt, device=dev)
+    g_d, e_d, u_d = _dev(gathered), _dev(ends), _dev(u)          # kept alive until the results are read
+    t_d, o_d = _dev(np.array([total], dtype=dtype)), _dev(rows_off)
+    check(lib.kmb_kpp_pick_owned(code, ptr(g_d), world, t, d, ptr(e_d), ptr(u_d), ptr(t_d), ptr(o_d),
+                                 ptr(cand), ptr(out_rows), s), "kmb_kpp_pick_owned")
+    assert_array_equal(cand.cpu().numpy(), want_ids)
+    assert_array_equal(out_rows.cpu().numpy(), want_rows)
+
+    # ---- select_shards: potentials summed over the shards, lowest trial on ties
+    shard_pots = rng.uniform(1.0, 2.0, size=(world, t))
+    shard_pots[:, 4] = shard_pots[:, 1]                  # a tie between trials 1 and 4 ...
+    shard_pots[:, 1] *= 0.25                             # ... made the minimum
+    shard_pots[:, 4] *= 0.25
+    pots_want = shard_pots.sum(axis=0).astype(dtype)
+    best_want = int(np.argmin(pots_want))
+    assert best_want == 1
+    pots = torch.empty(t, dtype=tdt, device=dev)
+    best = torch.zeros(1, dtype=torch.int32, device=dev)
+    tot = torch.empty(1, dtype=tdt, device=dev)
+    centers = torch.zeros((5, d), dtype=tdt, device=dev)
+    indices = torch.full((5,), -1, dtype=torch.int32, device=dev)
+    ends_out = torch.empty(world, dtype=torch.float64, device=dev)
+    off_out = torch.empty(1, dtype=torch.float64, device=dev)
+    sp_d = _dev(shard_pots)
+    for shard in (0, 2):
+        check(lib.kmb_kpp_select_shards(code, ptr(sp_d), world, shard, t, ptr(pots), ptr(best),
+                                        ptr(tot), ptr(out_rows), ptr(cand), ptr(centers), ptr(indices), c, d,
+                                        ptr(ends_out), ptr(off_out), s), "kmb_kpp_select_shards")
+        assert_allclose(pots.cpu().numpy(), pots_want, rtol=1e-6 if dtype == np.float32 else 1e-15)
+        assert int(best.cpu()) == best_want
+        assert_allclose(float(tot.cpu()), pots_want[best_want], rtol=1e-6 if dtype == np.float32 else 1e-15)
+        assert_array_equal(centers.cpu().numpy()[c], want_rows[best_want])
+        assert int(indices.cpu()[c]) == int(want_ids[best_want])
+        col = shard_pots[:, best_want]
+        assert_allclose(ends_out.cpu().numpy(), np.cumsum(col), rtol=1e-15)
+        assert_allclose(float(off_out.cpu()), np.cumsum(col)[shard] - col[shard], rtol=1e-14, atol=1e-15)
